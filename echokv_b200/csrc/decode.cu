@@ -1,0 +1,113 @@
+// C ABI of split-K paged decode attention: argument checks and kernel selection.
+#include "decode_generic.cuh"
+
+using namespace echokv;
+
+namespace echokv {
+int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
+                      int64_t num_seqs, cudaStream_t st, bool* handled);
+
+// out[q_rows[seq], head] = splits merged in split order (kernels/decode.py:226-262).
+__global__ void decode_merge_kernel(DecodeArgs A, int BS, int D) {
+  const int seq = blockIdx.x, head = blockIdx.y;
+  const int64_t seq_len = A.lens[seq];
+  if (seq_len == 0) return;  // CUDA-graph padding: leave the row alone
+  const int n_blocks = (int)((seq_len + BS - 1) / BS);
+  const int bps = max(A.bps_min, (n_blocks + A.num_splits - 1) / A.num_splits);
+  const int used = (n_blocks + bps - 1) / bps;
+  const int64_t base = ((int64_t)seq * A.Hq + head) * A.num_splits;
+  float mt = -INFINITY;
+  for (int s = 0; s < used; ++s) mt = fmaxf(mt, A.ml[(base + s) * 2]);
+  const int64_t o_row = A.q_rows ? A.q_rows[seq] : seq;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float a = 0.f, lt = 0.f;
+    for (int s = 0; s < used; ++s) {
+      const float w = exp2f(A.ml[(base + s) * 2] - mt);
+      a += A.acc[(base + s) * D + d] * w;
+      lt += A.ml[(base + s) * 2 + 1] * w;
+    }
+    st_dt(A.out, A.out_dt, o_row * A.o_s0 + (int64_t)head * A.o_s1 + d, a / lt);
+  }
+}
+
+}  // namespace echokv
+
+template <int GQ>
+static int launch_generic_gq(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
+                             dim3 grid, cudaStream_t st) {
+  switch (L.D) {
+    case 64: decode_generic_kernel<GQ, 2><<<grid, DG_WARPS * 32, 0, st>>>(L, R, pages, A); break;
+    case 128: decode_generic_kernel<GQ, 4><<<grid, DG_WARPS * 32, 0, st>>>(L, R, pages, A); break;
+    case 256:
+      if constexpr (GQ <= 8) {
+        decode_generic_kernel<GQ, 8><<<grid, DG_WARPS * 32, 0, st>>>(L, R, pages, A);
+        break;
+      } else {
+        return set_error(ECHOKV_E_UNSUPPORTED, "decode: head_size 256 supports at most 8 query heads per KV head");
+      }
+    default: return set_error(ECHOKV_E_UNSUPPORTED, "decode: head_size %d is not one of 64/128/256", L.D);
+  }
+  return ECHOKV_OK;
+}
+
+extern "C" {
+
+int64_t echokv_decode_scratch_bytes(int64_t num_seqs, int32_t num_q_heads, int32_t head_size, int32_t num_splits) {
+  if (num_seqs <= 0 || num_q_heads <= 0 || head_size <= 0 || num_splits <= 0) return 0;
+  return num_seqs * num_q_heads * (int64_t)num_splits * (head_size + 2) * (int64_t)sizeof(float);
+}
+
+int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                  const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype, const int64_t* q_rows,
+                  const int32_t* block_table, int64_t bt_s0, const int64_t* bt_rows, const int64_t* lens,
+                  void* scratch, int64_t scratch_bytes, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
+                  float softmax_scale, int32_t num_splits, int32_t blocks_per_split, int64_t num_seqs,
+                  int32_t num_q_heads, void* stream) {
+  if (num_seqs <= 0) return ECHOKV_OK;
+  LayoutDev L;
+  ResidualDev R;
+  int rc = make_layout(layout, pages, &L);
+  if (rc) return rc;
+  rc = make_residual(residual, &R);
+  if (rc) return rc;
+  if (!query || !block_table || !lens || !scratch || !out) return set_error(ECHOKV_E_ARGUMENT, "decode: null pointer");
+  if (num_splits < 1 || blocks_per_split < 1) return set_error(ECHOKV_E_ARGUMENT, "decode: num_splits and blocks_per_split must be >= 1");
+  if (num_q_heads % L.H) return set_error(ECHOKV_E_ARGUMENT, "decode: %d query heads not a multiple of %d KV heads", num_q_heads, L.H);
+  if (q_dtype < 0 || q_dtype > 2 || out_dtype < 0 || out_dtype > 2) return set_error(ECHOKV_E_ARGUMENT, "decode: bad dtype");
+  if (scratch_bytes < echokv_decode_scratch_bytes(num_seqs, num_q_heads, L.D, num_splits) ||
+      (reinterpret_cast<uintptr_t>(scratch) & 15))
+    return set_error(ECHOKV_E_ARGUMENT, "decode: scratch too small (%lld bytes) or misaligned", (long long)scratch_bytes);
+  const int gqa = num_q_heads / L.H;
+  if (gqa > 16) return set_error(ECHOKV_E_UNSUPPORTED, "decode: %d query heads per KV head (max 16)", gqa);
+
+  DecodeArgs A;
+  A.q = query; A.q_s0 = q_s0; A.q_s1 = q_s1; A.q_dt = q_dtype; A.q_rows = q_rows;
+  A.bt = block_table; A.bt_s0 = bt_s0; A.bt_rows = bt_rows; A.lens = lens;
+  A.acc = (float*)scratch;
+  A.ml = A.acc + num_seqs * num_q_heads * (int64_t)num_splits * L.D;
+  A.out = out; A.o_s0 = o_s0; A.o_s1 = o_s1; A.out_dt = out_dtype;
+  A.scale_log2e = softmax_scale * 1.4426950408889634f;
+  A.num_splits = num_splits; A.bps_min = blocks_per_split; A.gqa = gqa; A.Hq = num_q_heads;
+  cudaStream_t st = (cudaStream_t)stream;
+  const uint8_t* pg = (const uint8_t*)pages->base;
+
+  bool handled = false;
+  rc = launch_decode_mma(L, R, pg, A, num_seqs, st, &handled);
+  if (rc) return rc;
+  if (!handled) {
+    dim3 grid((unsigned)num_seqs, (unsigned)L.H, (unsigned)num_splits);
+    if (gqa == 1) rc = launch_generic_gq<1>(L, R, pg, A, grid, st);
+    else if (gqa == 2) rc = launch_generic_gq<2>(L, R, pg, A, grid, st);
+    else if (gqa <= 4) rc = launch_generic_gq<4>(L, R, pg, A, grid, st);
+    else if (gqa <= 8) rc = launch_generic_gq<8>(L, R, pg, A, grid, st);
+    else rc = launch_generic_gq<16>(L, R, pg, A, grid, st);
+    if (rc) return rc;
+    rc = check_launch("decode");
+    if (rc) return rc;
+  }
+  dim3 mgrid((unsigned)num_seqs, (unsigned)num_q_heads);
+  decode_merge_kernel<<<mgrid, L.D < 128 ? L.D : 128, 0, st>>>(A, L.BS, L.D);
+  return check_launch("decode merge");
+}
+
+}  // extern "C"

@@ -1,0 +1,249 @@
+// Read-side dequantization kernels: arbitrary token gather (the store's oracle read), dense
+// dequantization of whole contexts for chunked prefill, and LRU demotion to INT2.
+#include "common.cuh"
+
+namespace echokv {
+
+// Dequantize 8 channels [d0, d0+8) of head h of token (blk, off): K and V as float.
+// Mirrors TieredKVCache.gather (echokv_vllm/tiered_cache.py:451-478) / load_kv_tile
+// (kernels/common.py:50-109): K comes from the residual when the token's group is the
+// block's open group.  `zero_unopened`: blocks with tier 0 give zeros (gather) instead of
+// being read as INT2 (the attention kernels).
+__device__ __forceinline__ void dequant8(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, int64_t blk,
+                                         int off, int h, int d0, bool zero_unopened, float (&k)[8], float (&v)[8]) {
+  const uint8_t* page = pages + blk * L.PS;
+  int bits = page[0];
+  if (bits == 0) {
+    if (zero_unopened) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) k[i] = v[i] = 0.f;
+      return;
+    }
+    bits = 2;
+  }
+  const int64_t ro = row_offset(pages, L, blk, off, bits);
+  const int side_bytes = (L.H * L.D * bits) / 8;
+  const int head_bytes = (L.D * bits) / 8;
+  const uint8_t* krow = pages + ro + h * head_bytes;
+  const uint8_t* vrow = krow + side_bytes;
+  // V: per-token stats per group of VG channels
+  const int g = d0 / L.VG;
+  const int64_t ve = ((int64_t)off * L.H + h) * L.NG + g;
+  const float vs = __half2float(reinterpret_cast<const __half*>(page + L.o_vs)[ve]);
+  const float vm = __half2float(reinterpret_cast<const __half*>(page + L.o_vm)[ve]);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __fadd_rn(__fmul_rn((float)extract_code(vrow, d0 + i, bits), vs), vm);
+  // K
+  const int grp = off / L.KG;
+  const int64_t slot = R.block_res[blk];
+  if (slot >= 0 && R.res_group[slot] == grp) {
+    const int64_t o = slot * R.s_slot + (int64_t)(off % L.KG) * R.s_pos + h * R.s_head + d0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) k[i] = ld_dt(R.base, R.dtype, o + i);
+  } else {
+    const int64_t ke = ((int64_t)grp * L.H + h) * L.D + d0;
+    const __half* ks = reinterpret_cast<const __half*>(page + L.o_ks) + ke;
+    const __half* km = reinterpret_cast<const __half*>(page + L.o_km) + ke;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      k[i] = __fadd_rn(__fmul_rn((float)extract_code(krow, d0 + i, bits), __half2float(ks[i])), __half2float(km[i]));
+  }
+}
+
+__global__ void gather_kernel(LayoutDev L, ResidualDev R, const uint8_t* __restrict__ pages,
+                              const int64_t* __restrict__ blk, const int64_t* __restrict__ off, int64_t n,
+                              float* __restrict__ k_out, float* __restrict__ v_out) {
+  const int cpt = (L.H * L.D) / 8;  // chunks per token
+  const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (idx >= n * cpt) return;
+  const int64_t i = idx / cpt;
+  const int c = (int)(idx % cpt);
+  const int h = (c * 8) / L.D, d0 = (c * 8) % L.D;
+  float k[8], v[8];
+  dequant8(L, R, pages, blk[i], (int)off[i], h, d0, true, k, v);
+  float* ko = k_out + (i * L.H + h) * L.D + d0;
+  float* vo = v_out + (i * L.H + h) * L.D + d0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { ko[j] = k[j]; vo[j] = v[j]; }
+}
+
+// One CTA per work item (request, block index, dense row, ctx) -- kernels/prefill.py:329-369.
+template <typename T>
+__global__ void __launch_bounds__(256)
+dequant_dense_kernel(LayoutDev L, ResidualDev R, const uint8_t* __restrict__ pages, const int32_t* __restrict__ work,
+                     const int32_t* __restrict__ bt, int64_t bt_s0, T* __restrict__ k_out, T* __restrict__ v_out,
+                     int64_t o_s0, int64_t o_s1) {
+  const int32_t* w = work + blockIdx.x * 4;
+  const int req = w[0], bi = w[1], ctx = w[3];
+  const int64_t row0 = w[2];
+  const int64_t blk = bt[(int64_t)req * bt_s0 + bi];
+  const int nvalid = min(L.BS, ctx - bi * L.BS);
+  const int cpt = (L.H * L.D) / 8;
+  for (int idx = threadIdx.x; idx < nvalid * cpt; idx += blockDim.x) {
+    const int t = idx / cpt, c = idx % cpt;
+    const int h = (c * 8) / L.D, d0 = (c * 8) % L.D;
+    float k[8], v[8];
+    dequant8(L, R, pages, blk, t, h, d0, false, k, v);
+    const int64_t o = (row0 + t) * o_s0 + h * o_s1 + d0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { Elem<T>::st(k_out, o + j, k[j]); Elem<T>::st(v_out, o + j, v[j]); }
+  }
+}
+
+// Demotion, phase 2: requantize a block's dequantized contents (scratch: K then V, float
+// [n, BS, H, D]) to INT2 into chunk 0 of its own page (tiered_cache.py:322-340).
+__global__ void __launch_bounds__(256)
+demote_requant_kernel(LayoutDev L, uint8_t* __restrict__ pages, const int64_t* __restrict__ victims, int64_t n,
+                      const float* __restrict__ scratch) {
+  const int64_t b = victims[blockIdx.x];
+  const float* ksrc = scratch + (int64_t)blockIdx.x * L.BS * L.H * L.D;
+  const float* vsrc = scratch + (n + blockIdx.x) * (int64_t)L.BS * L.H * L.D;
+  uint8_t* page = pages + b * L.PS;
+  const float levels = 3.f;
+  const int bits = 2;
+  const int side_bytes = (L.H * L.D * bits) / 8, head_bytes = (L.D * bits) / 8;
+  const int64_t row_bytes = 2 * side_bytes;
+  uint8_t* data = page + L.o_data;  // INT2: every token row lives in chunk 0 of the own page
+  if (threadIdx.x == 0) page[0] = 2;
+  // K: per channel over each group of KG tokens
+  const int cph = (L.H * L.D) / 8;
+  for (int idx = threadIdx.x; idx < L.KGPB * cph; idx += blockDim.x) {
+    const int grp = idx / cph, c = idx % cph;
+    const int h = (c * 8) / L.D, d0 = (c * 8) % L.D;
+    float mn[8], mx[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { mn[k] = INFINITY; mx[k] = -INFINITY; }
+    for (int p = 0; p < L.KG; ++p) {
+      const float* x = ksrc + ((int64_t)(grp * L.KG + p) * L.H + h) * L.D + d0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { mn[k] = fminf(mn[k], x[k]); mx[k] = fmaxf(mx[k], x[k]); }
+    }
+    __align__(16) __half s16[8], m16[8];
+    float sc[8], m[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      group_stats(mn[k], mx[k], levels, s16[k], m16[k]);
+      sc[k] = __half2float(s16[k]); m[k] = __half2float(m16[k]);
+    }
+    const int64_t e = ((int64_t)grp * L.H + h) * L.D + d0;
+    *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(page + L.o_ks) + e) = *reinterpret_cast<uint4*>(s16);
+    *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(page + L.o_km) + e) = *reinterpret_cast<uint4*>(m16);
+    for (int p = 0; p < L.KG; ++p) {
+      const int t = grp * L.KG + p;
+      const float* x = ksrc + ((int64_t)t * L.H + h) * L.D + d0;
+      uint32_t q[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) q[k] = quant_code(x[k], m[k], sc[k], levels);
+      store_packed8(data + t * row_bytes + h * head_bytes + (d0 * bits) / 8, pack8(q, bits), bits);
+    }
+  }
+  // V: per token, groups of VG channels
+  for (int idx = threadIdx.x; idx < L.BS * L.H * L.NG; idx += blockDim.x) {
+    const int t = idx / (L.H * L.NG), r = idx % (L.H * L.NG);
+    const int h = r / L.NG, g = r % L.NG;
+    const float* x = vsrc + ((int64_t)t * L.H + h) * L.D + g * L.VG;
+    float mn = INFINITY, mx = -INFINITY;
+    for (int c = 0; c < L.VG; ++c) { mn = fminf(mn, x[c]); mx = fmaxf(mx, x[c]); }
+    __half s16, m16;
+    group_stats(mn, mx, levels, s16, m16);
+    const float sc = __half2float(s16), m = __half2float(m16);
+    const int64_t e = ((int64_t)t * L.H + h) * L.NG + g;
+    reinterpret_cast<__half*>(page + L.o_vs)[e] = s16;
+    reinterpret_cast<__half*>(page + L.o_vm)[e] = m16;
+    uint8_t* dst = data + t * row_bytes + side_bytes + h * head_bytes + (g * L.VG * bits) / 8;
+    for (int c = 0; c < L.VG; c += 8) {
+      uint32_t q[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) q[k] = quant_code(x[c + k], m, sc, levels);
+      store_packed8(dst + (c * bits) / 8, pack8(q, bits), bits);
+    }
+  }
+}
+
+__global__ void demote_index_kernel(const int64_t* victims, int64_t n, int BS, int64_t* blk, int64_t* off) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= n * BS) return;
+  blk[i] = victims[i / BS];
+  off[i] = i % BS;
+}
+
+}  // namespace echokv
+
+using namespace echokv;
+
+extern "C" {
+
+int echokv_gather(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                  const int64_t* blk, const int64_t* off, int64_t n, float* k_out, float* v_out, void* stream) {
+  if (n <= 0) return ECHOKV_OK;
+  LayoutDev L;
+  ResidualDev R;
+  int rc = make_layout(layout, pages, &L);
+  if (rc) return rc;
+  rc = make_residual(residual, &R);
+  if (rc) return rc;
+  if (!blk || !off || !k_out || !v_out) return set_error(ECHOKV_E_ARGUMENT, "gather: null pointer");
+  const int64_t total = n * (L.H * L.D / 8);
+  gather_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      L, R, (const uint8_t*)pages->base, blk, off, n, k_out, v_out);
+  return check_launch("gather");
+}
+
+int echokv_dequant_dense(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                         const int32_t* work, int64_t n_work, const int32_t* block_table, int64_t bt_s0, void* k_out,
+                         void* v_out, int64_t out_s0, int64_t out_s1, int32_t out_dtype, void* stream) {
+  if (n_work <= 0) return ECHOKV_OK;
+  LayoutDev L;
+  ResidualDev R;
+  int rc = make_layout(layout, pages, &L);
+  if (rc) return rc;
+  rc = make_residual(residual, &R);
+  if (rc) return rc;
+  if (!work || !block_table || !k_out || !v_out) return set_error(ECHOKV_E_ARGUMENT, "dequant_dense: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH(T)                                                                                              \
+  dequant_dense_kernel<T><<<(unsigned)n_work, 256, 0, st>>>(L, R, (const uint8_t*)pages->base, work, block_table, \
+                                                           bt_s0, (T*)k_out, (T*)v_out, out_s0, out_s1)
+  switch (out_dtype) {
+    case ECHOKV_DT_F32: LAUNCH(float); break;
+    case ECHOKV_DT_F16: LAUNCH(__half); break;
+    case ECHOKV_DT_BF16: LAUNCH(__nv_bfloat16); break;
+    default: return set_error(ECHOKV_E_ARGUMENT, "dequant_dense: bad dtype %d", out_dtype);
+  }
+#undef LAUNCH
+  return check_launch("dequant_dense");
+}
+
+int64_t echokv_demote_scratch_bytes(const echokv_layout* layout, int64_t n) {
+  if (!layout || n <= 0) return 0;
+  const int64_t tok = n * layout->block_size;
+  // dequantized K and V (float) + the (blk, off) index of every token
+  return tok * layout->num_kv_heads * layout->head_size * 2 * (int64_t)sizeof(float) + tok * 2 * (int64_t)sizeof(int64_t);
+}
+
+int echokv_demote_blocks(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                         const int64_t* victims, int64_t n, void* scratch, int64_t scratch_bytes, void* stream) {
+  if (n <= 0) return ECHOKV_OK;
+  LayoutDev L;
+  ResidualDev R;
+  int rc = make_layout(layout, pages, &L);
+  if (rc) return rc;
+  rc = make_residual(residual, &R);
+  if (rc) return rc;
+  if (!victims || !scratch) return set_error(ECHOKV_E_ARGUMENT, "demote_blocks: null pointer");
+  if (scratch_bytes < echokv_demote_scratch_bytes(layout, n) || (reinterpret_cast<uintptr_t>(scratch) & 15))
+    return set_error(ECHOKV_E_ARGUMENT, "demote_blocks: scratch too small or misaligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t tok = n * L.BS;
+  float* kf = (float*)scratch;
+  float* vf = kf + tok * L.H * L.D;
+  int64_t* bi = (int64_t*)(vf + tok * L.H * L.D);
+  int64_t* oi = bi + tok;
+  demote_index_kernel<<<(unsigned)((tok + 255) / 256), 256, 0, st>>>(victims, n, L.BS, bi, oi);
+  const int64_t total = tok * (L.H * L.D / 8);
+  gather_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(L, R, (const uint8_t*)pages->base, bi, oi, tok, kf, vf);
+  demote_requant_kernel<<<(unsigned)n, 256, 0, st>>>(L, (uint8_t*)pages->base, victims, n, kf);
+  return check_launch("demote_blocks");
+}
+
+}  // extern "C"

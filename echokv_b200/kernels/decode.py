@@ -1,0 +1,85 @@
+"""Launcher of split-K paged decode attention (``csrc/decode*.cu``).
+
+Same call surface as the reference's ``echokv_vllm/kernels/decode.py``
+``decode_attention`` (:44-92).  There is no PyTorch path.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from echokv_b200 import _native as N
+
+BLOCKS_PER_SPLIT = 16
+
+
+class _Scratch:
+    """Per-device split-partials buffer, grown on demand and reused (a stable address lets a
+    captured CUDA graph replay it)."""
+
+    def __init__(self) -> None:
+        self.buf: dict[torch.device, torch.Tensor] = {}
+
+    def get(self, device, nbytes: int) -> torch.Tensor:
+        cur = self.buf.get(device)
+        if cur is None or cur.numel() < nbytes:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("decode scratch must be sized before CUDA-graph capture (run one eager step first)")
+            cur = self.buf[device] = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        return cur
+
+
+_scratch = _Scratch()
+
+
+def decode_attention(store, query: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
+                     softmax_scale: float, blocks_per_split: int = BLOCKS_PER_SPLIT,
+                     q_rows: torch.Tensor | None = None, bt_rows: torch.Tensor | None = None,
+                     out: torch.Tensor | None = None, max_len: int | None = None,
+                     num_splits: int | None = None) -> torch.Tensor:
+    """Attention of one query token per sequence over each sequence's cache.
+
+    Sequence ``i`` uses query row ``q_rows[i]`` and block-table row ``bt_rows[i]``
+    (default: row ``i``) with cache length ``seq_lens[i]``.  Without ``out``
+    returns float32 ``[S, Hq, D]``; with ``out`` writes sequence ``i`` to
+    ``out[q_rows[i]]`` in ``out``'s dtype; length-0 sequences (CUDA-graph padding)
+    leave their row untouched.  Each sequence is cut into at most ``num_splits``
+    splits of ``max(blocks_per_split, ceil(blocks / num_splits))`` blocks -- a
+    function of the sequence alone, so results are batch-invariant.
+    """
+    L = store.layout
+    N.require_cuda(query, block_table, seq_lens, out)
+    if query.dim() != 3 or query.shape[2] != L.head_size:
+        raise ValueError("query must be [T, Hq, D]")
+    if query.stride(2) != 1:
+        query = query.contiguous()
+    hq = query.shape[1]
+    s = seq_lens.shape[0]
+    dev = query.device
+    if block_table.dtype != torch.int32 or block_table.stride(1) != 1:
+        block_table = block_table.to(torch.int32).contiguous()
+    lens = seq_lens if seq_lens.dtype == torch.long and seq_lens.is_contiguous() else seq_lens.long().contiguous()
+    if q_rows is not None and (q_rows.dtype != torch.long or not q_rows.is_contiguous()):
+        q_rows = q_rows.long().contiguous()
+    if bt_rows is not None and (bt_rows.dtype != torch.long or not bt_rows.is_contiguous()):
+        bt_rows = bt_rows.long().contiguous()
+    if out is None:
+        out = torch.empty(query.shape[0], hq, L.head_size, device=dev, dtype=torch.float32)
+    if out.stride(2) != 1:
+        raise ValueError("out must have a contiguous last dim")
+    if num_splits is None:
+        width = block_table.shape[1]
+        max_blocks = width if max_len is None else min(width, -(-max_len // L.block_size))
+        num_splits = max(1, -(-max_blocks // blocks_per_split))
+    if s == 0:
+        return out
+    nbytes = N.lib.echokv_decode_scratch_bytes(s, hq, L.head_size, num_splits)
+    scratch = _scratch.get(dev, nbytes)
+    N.check(N.lib.echokv_decode(
+        store.c_layout, store.c_pages, store.c_res,
+        query.data_ptr(), query.stride(0), query.stride(1), N.dtype_code(query.dtype), N.ptr(q_rows),
+        block_table.data_ptr(), block_table.stride(0), N.ptr(bt_rows), lens.data_ptr(),
+        scratch.data_ptr(), scratch.numel(),
+        out.data_ptr(), out.stride(0), out.stride(1), N.dtype_code(out.dtype),
+        float(softmax_scale), int(num_splits), int(blocks_per_split), s, hq, N.stream_ptr(dev)))
+    return out

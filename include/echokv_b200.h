@@ -1,0 +1,190 @@
+/*
+ * echokv_b200 -- C ABI of the B200 (sm_100a) kernels for paged attention over a
+ * per-layer mixed-precision (INT8 / INT4 / INT2) KV cache.
+ *
+ * Every entry point replaces one Python-level kernel launcher of the reference
+ * plugin (paths below are relative to the reference project).  All device entry
+ * points are asynchronous on `stream` (a cudaStream_t passed as void*), never
+ * synchronise with the host, never allocate, and return 0 on success or a
+ * negative ECHOKV_E_* code (the message is available from echokv_last_error()).
+ * Pointers are plain device pointers; strides are in ELEMENTS of the pointed-to
+ * type unless a name ends in _bytes.  Element types are given as ECHOKV_DT_*.
+ *
+ * Page byte layout (echokv_vllm/tiered_cache.py:13-25, :120-147), one page per
+ * vLLM block of `block_size` tokens:
+ *   [0, block_size)          header: [0] tier (0 never opened, else 2/4/8),
+ *                            [1] bitmask of K groups sealed early,
+ *                            [4:16] three int32 ids of extra pool chunks
+ *   v_scale, v_min           fp16 [block_size, H, D / v_group] each
+ *   k_scale, k_min           fp16 [block_size / k_group, H, D] each
+ *   data                     mem_bits / 2 chunks of block_size*H*D/2 bytes;
+ *                            token rows are [K codes of all heads | V codes of
+ *                            all heads]; chunk j holds tokens [j*tpc, (j+1)*tpc),
+ *                            tpc = 2*block_size/bits; chunk 0 is in the block's
+ *                            own page, chunk j>0 is pool chunk id table[j-1]
+ *                            (page = id / chunks_per_page, slot = id % ...).
+ */
+#ifndef ECHOKV_B200_H
+#define ECHOKV_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ECHOKV_ABI_VERSION 1
+
+enum {
+  ECHOKV_OK = 0,
+  ECHOKV_E_LAYOUT = -1,      /* layout rejected (same rules as TieredLayout.__post_init__) */
+  ECHOKV_E_UNSUPPORTED = -2, /* shape / dtype the kernels are not built for */
+  ECHOKV_E_ARGUMENT = -3,    /* null pointer, negative size, misaligned stride */
+  ECHOKV_E_CUDA = -4         /* a CUDA runtime call failed */
+};
+
+enum { ECHOKV_DT_F32 = 0, ECHOKV_DT_F16 = 1, ECHOKV_DT_BF16 = 2 };
+
+/* TieredLayout (echokv_vllm/tiered_cache.py:76-97). */
+typedef struct echokv_layout {
+  int32_t num_kv_heads;
+  int32_t head_size;
+  int32_t block_size;
+  int32_t mem_bits; /* 2, 4, 6 or 8 */
+  int32_t k_group;
+  int32_t v_group;
+} echokv_layout;
+
+/* Derived byte offsets (TieredLayout.offsets / per_token_bytes, tiered_cache.py:99-147). */
+typedef struct echokv_layout_info {
+  int64_t o_v_scale, o_v_min, o_k_scale, o_k_min, o_data, page_bytes;
+  int64_t chunk_bytes, per_token_bytes;
+  int32_t chunks_per_page, k_groups_per_block, v_groups, reserved;
+} echokv_layout_info;
+
+/* A layer's slice of the paged pool: uint8 [num_blocks, >= page_bytes], row stride
+ * `page_stride_bytes` (16-byte aligned; may exceed the page for layer-interleaved
+ * pools) -- TieredKVCache.__init__ (tiered_cache.py:157-171). */
+typedef struct echokv_pages {
+  void* base;
+  int64_t page_stride_bytes;
+  int64_t num_blocks;
+} echokv_pages;
+
+/* Residual buffer [slots + 1, k_group, H, D] in the model dtype
+ * (backend.py:535-537) and the shared block -> slot map (write_plan.py:255-256). */
+typedef struct echokv_residual {
+  void* base;
+  int32_t dtype;
+  int32_t reserved;
+  int64_t s_slot, s_pos, s_head;  /* element strides; the last dim is contiguous */
+  const int64_t* block_res;       /* [num_blocks] residual slot of the block's open K group, -1 none */
+  const int64_t* res_group;       /* [slots + 1] which K group a slot holds */
+} echokv_residual;
+
+int echokv_abi_version(void);
+const char* echokv_last_error(void);
+
+/* Host only. Validates like TieredLayout.__post_init__ and fills `out`. */
+int echokv_layout_describe(const echokv_layout* layout, echokv_layout_info* out);
+
+/* header[blocks[i]] = headers[i] (16 bytes each) -- TieredKVCache.write_headers
+ * (tiered_cache.py:305-307). `blocks` int64 [n], `headers` uint8 [n,16], both on the device. */
+int echokv_write_headers(const echokv_pages* pages, const int64_t* blocks, const uint8_t* headers,
+                         int64_t n, void* stream);
+
+/* dst[idx[i]] = val[i] -- SharedState.apply_res_map (write_plan.py:266-271). */
+int echokv_scatter_i64(int64_t* dst, const int64_t* idx, const int64_t* val, int64_t n, void* stream);
+
+/* Quantize-on-write of a step's token rows -- write_tokens / _write_tokens_kernel
+ * (kernels/write.py:29-36, :171-229).  key/value [n_rows, H, D] of `kv_dtype`
+ * (row stride s0, head stride s1, unit stride in D).  `tok` int64 [4, >= n_rows] with
+ * row stride tok_s0: slot (-1 skip), residual slot or -1, sealed flag, K_ref ring row or -1.
+ * `kref` float32 [W, H, D] or NULL. */
+int echokv_write_tokens(const echokv_layout* layout, const echokv_pages* pages,
+                        const void* key, int64_t k_s0, int64_t k_s1,
+                        const void* value, int64_t v_s0, int64_t v_s1, int32_t kv_dtype,
+                        const int64_t* tok, int64_t tok_s0, const echokv_residual* residual,
+                        float* kref, int64_t kref_s0, int64_t kref_s1,
+                        int64_t n_rows, void* stream);
+
+/* Per-channel quantization of completed K groups -- finalize_k / _finalize_k_kernel
+ * (kernels/write.py:39-50, :231-287).  `fin` int64 [>= n_launch, 3 + k_group]:
+ * block, group, residual slot or -1, then the key row of each position or -1 (take it
+ * from the residual).  Rows >= *fin_count are skipped (graph-captured full-grid launch). */
+int echokv_finalize_k(const echokv_layout* layout, const echokv_pages* pages,
+                      const void* key, int64_t k_s0, int64_t k_s1, int32_t kv_dtype,
+                      const int64_t* fin, const int64_t* fin_count,
+                      const echokv_residual* residual, int64_t n_launch, void* stream);
+
+/* Seal an evicted residual slot: quantize its first `fill` keys against their own
+ * stats into group `group` of `block` at `bits`, set header byte 1 to `sealed_mask`
+ * -- TieredKVCache._seal (tiered_cache.py:379-394). */
+int echokv_seal_group(const echokv_layout* layout, const echokv_pages* pages,
+                      const echokv_residual* residual, int64_t slot, int64_t block, int32_t group,
+                      int32_t fill, int32_t bits, int32_t sealed_mask, void* stream);
+
+/* Requantize full INT4/INT8 blocks to INT2 in place -- TieredKVCache._demote_lru
+ * (tiered_cache.py:309-346).  `victims` int64 [n] on the device; `scratch` holds the blocks'
+ * dequantized contents between the read and the rewrite (echokv_demote_scratch_bytes). */
+int64_t echokv_demote_scratch_bytes(const echokv_layout* layout, int64_t n);
+int echokv_demote_blocks(const echokv_layout* layout, const echokv_pages* pages,
+                         const echokv_residual* residual, const int64_t* victims, int64_t n,
+                         void* scratch, int64_t scratch_bytes, void* stream);
+
+/* Dequantized K and V, float32 [n, H, D], of tokens (blk[i], off[i]) -- TieredKVCache.gather
+ * (tiered_cache.py:451-478). Blocks never opened give zeros. */
+int echokv_gather(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                  const int64_t* blk, const int64_t* off, int64_t n, float* k_out, float* v_out, void* stream);
+
+/* Bytes of scratch echokv_decode needs for its split partials: acc float32
+ * [S, Hq, num_splits, D] then (m, l) float32 [S, Hq, num_splits, 2]
+ * (kernels/decode.py:306-307 allocates the same two tensors per call). */
+int64_t echokv_decode_scratch_bytes(int64_t num_seqs, int32_t num_q_heads, int32_t head_size, int32_t num_splits);
+
+/* Split-K paged decode attention + merge -- decode_attention / _decode_triton
+ * (kernels/decode.py:44-92, :283-345).  Sequence i uses query row q_rows[i], block-table
+ * row bt_rows[i], cache length lens[i] (0 = CUDA-graph padding: its output row is left
+ * untouched) and writes out[q_rows[i]].  q_rows / bt_rows may be NULL (identity).
+ * Split rule (decode.py:166-172): n_blocks = ceil(len / BS); bps = max(blocks_per_split,
+ * ceil(n_blocks / num_splits)); split s covers blocks [s*bps, min((s+1)*bps, n_blocks)). */
+int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                  const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype, const int64_t* q_rows,
+                  const int32_t* block_table, int64_t bt_s0, const int64_t* bt_rows, const int64_t* lens,
+                  void* scratch, int64_t scratch_bytes,
+                  void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
+                  float softmax_scale, int32_t num_splits, int32_t blocks_per_split,
+                  int64_t num_seqs, int32_t num_q_heads, void* stream);
+
+/* Dequantize whole contexts into dense [total_ctx, H, D] K and V of `out_dtype`
+ * -- dequant_dense / _dequant_kernel (kernels/prefill.py:90-115, :329-369).
+ * `work` int32 [n_work, 4]: request (block-table row), block index, dense row of the
+ * block's first token, context length. */
+int echokv_dequant_dense(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                         const int32_t* work, int64_t n_work, const int32_t* block_table, int64_t bt_s0,
+                         void* k_out, void* v_out, int64_t out_s0, int64_t out_s1, int32_t out_dtype, void* stream);
+
+/* Chunked-prefill attention of query chunks over their whole stored context, bottom-right
+ * causal -- prefill_attention (kernels/prefill.py:170-207, oracle :210-236).  `chunks`
+ * int32 [n_chunks, 4]: q_start, q_end, ctx, block-table row.  query/out [T, Hq, D]. */
+int echokv_prefill(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                   const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype,
+                   const int32_t* chunks, int64_t n_chunks, int32_t max_chunk_len,
+                   const int32_t* block_table, int64_t bt_s0,
+                   void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
+                   float softmax_scale, int32_t num_q_heads, void* stream);
+
+/* Canary attention-KL estimator, batched over layers -- canary_kl (canary.py:59-89).
+ * query [L, nq, Hq, D] of q_dtype, kref float32 [L, W, H, D] oldest key first (ring
+ * already unrolled: row (ring_pos + i) % W when ring_fill == W).  Scores the last
+ * floor(fill / k_group) * k_group keys at 2, 4 and 8 bits; out float32 [L, 3]. */
+int echokv_canary_kl(const void* query, int32_t q_dtype, int64_t q_sl, int64_t q_sq, int64_t q_sh,
+                     const float* kref, int64_t k_sl, int64_t k_sw, int64_t k_sh,
+                     int32_t ring_pos, int32_t ring_fill, int32_t window,
+                     int32_t num_layers, int32_t nq, int32_t num_q_heads, int32_t num_kv_heads,
+                     int32_t head_size, int32_t k_group, float softmax_scale, float* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ECHOKV_B200_H */

@@ -1,0 +1,137 @@
+"""Host logic without a GPU: the write planner and the chunk pool against the oracle's plain
+restatement (itself pinned to the reference) on seeded request traffic, the layout arithmetic
+through the C ABI, and that the shared library exports every declared symbol."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import echokv_oracle as O
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def traffic(seed, bs, n_blocks, n_req, steps):
+    """Slot mappings of a continuous-batching run: requests prefill in chunks, decode one token
+    per step, finish and hand their blocks back; rows arrive in shuffled order with padding."""
+    rng = np.random.default_rng(seed)
+    free = list(rng.permutation(n_blocks))
+    reqs = {}
+    nxt = 0
+    for _ in range(steps):
+        while len(reqs) < n_req and len(free) > 6:
+            reqs[nxt] = dict(blocks=[], pos=0, prompt=int(rng.integers(1, 3 * bs)), total=int(rng.integers(2, 5 * bs)))
+            nxt += 1
+        slots = []
+        for rid in list(reqs):
+            r = reqs[rid]
+            n = int(min(r["prompt"] - r["pos"], rng.integers(1, 2 * bs))) if r["pos"] < r["prompt"] else 1
+            for _ in range(n):
+                if r["pos"] % bs == 0:
+                    if not free:
+                        break
+                    r["blocks"].append(free.pop())
+                if r["pos"] // bs >= len(r["blocks"]):
+                    break
+                slots.append(int(r["blocks"][r["pos"] // bs]) * bs + r["pos"] % bs)
+                r["pos"] += 1
+            if r["pos"] >= max(r["total"], r["prompt"]) or rng.random() < 0.03:
+                free.extend(r["blocks"])
+                del reqs[rid]
+        slots = np.array(slots + [-1] * int(rng.integers(0, 4)), dtype=np.int64)
+        yield slots[rng.permutation(slots.size)] if rng.random() < 0.5 else slots
+
+
+@pytest.mark.parametrize("seed,bs,g,slots", [(0, 64, 32, 6), (1, 16, 16, 5), (2, 32, 16, 40), (3, 128, 32, 3)])
+def test_planner_matches_oracle(seed, bs, g, slots):
+    from echokv_b200.write_plan import WritePlanner
+
+    mine, ref = WritePlanner(bs, g, slots, 8), O.Planner(bs, g, slots, 8)
+    for sm in traffic(seed, bs, 48, 6, 150):
+        try:
+            b = ref.plan(sm)
+        except RuntimeError:
+            with pytest.raises(RuntimeError):
+                mine.plan(sm)
+            return
+        a = mine.plan(sm)
+        assert a.n_rows == b.n_rows and a.step == b.step
+        for x, y in ((a.tok_slot, b.tok_slot), (a.tok_res, b.tok_res), (a.tok_sealed, b.tok_sealed),
+                     (a.tok_kref, b.tok_kref), (a.fin, b.fin), (a.open_np, b.open_blocks),
+                     (a.touched_np, b.touched), (a.touched_fill, b.touched_fill), (a.touched_count, b.touched_count)):
+            assert np.array_equal(x, y)
+        assert [(e.slot, e.block, e.group, e.fill) for e in a.evictions] == \
+               [(e.slot, e.block, e.group, e.fill) for e in b.evictions]
+        assert dict(zip(a.res_map_block.tolist(), a.res_map_value.tolist())) == b.res_map
+        assert dict(zip(a.res_group_slot.tolist(), a.res_group_value.tolist())) == b.grp_map
+        assert (mine.kref_pos, mine.kref_fill, mine.free, mine.sealed) == (ref.kref_pos, ref.kref_fill, ref.free, ref.sealed)
+
+
+def test_chunk_pool_matches_oracle_order():
+    from echokv_b200.tiered_cache import ChunkPool
+
+    rng = np.random.default_rng(5)
+    n, kc = 40, 4
+    pool = ChunkPool(n, kc)
+    ost = O.Store(O.Layout(2, 64, 64, 8), n, residual_slots=2)
+    assert pool.free == ost.free
+    for _ in range(60):
+        blocks = np.unique(rng.integers(0, n, size=int(rng.integers(1, 6))))
+        target = int(rng.choice([2, 4, 8]))
+        for b in blocks.tolist():
+            pool.release(b, 0)
+        tiers = pool.allot(blocks, target)
+        _, hdr = ost.open_blocks(blocks, target)  # no full blocks: nothing to demote
+        assert np.array_equal(pool.headers(blocks), hdr) and np.array_equal(tiers, ost.tag_h[blocks])
+        assert pool.free == ost.free
+
+
+def test_layout_matches_oracle_and_c_abi():
+    from echokv_b200 import _native as N
+    from echokv_b200.tiered_cache import TieredLayout
+
+    for h, d, bs, mem, kg, vg in [(8, 128, 32, 4, 32, 32), (2, 64, 64, 8, 32, 32), (1, 128, 256, 2, 32, 32),
+                                  (4, 96, 32, 6, 32, 32), (8, 128, 16, 8, 16, 32), (2, 128, 16, 4, 16, 32)]:
+        L, Lo = TieredLayout(h, d, bs, mem, kg, vg), O.Layout(h, d, bs, mem, kg, vg)
+        info = N.describe(h, d, bs, mem, kg, vg)
+        assert L.offsets == Lo.offsets and L.page_bytes == Lo.page_bytes == info.page_bytes
+        assert (info.o_v_scale, info.o_v_min, info.o_k_scale, info.o_k_min, info.o_data) == tuple(
+            Lo.offsets[k] for k in ("v_scale", "v_min", "k_scale", "k_min", "data"))
+        assert TieredLayout.per_token_bytes(h, d, mem, kg, vg) == O.Layout.per_token_bytes(h, d, mem, kg, vg) \
+            == info.per_token_bytes
+        assert bs * info.per_token_bytes >= info.page_bytes
+        assert L.chunk_bytes == info.chunk_bytes and L.chunks_per_page == info.chunks_per_page
+    for bad in (dict(block_size=8, mem_bits=4), dict(block_size=32, mem_bits=5), dict(block_size=48, mem_bits=4)):
+        with pytest.raises(ValueError):
+            TieredLayout(num_kv_heads=2, head_size=64, **bad)
+        with pytest.raises(ValueError):
+            N.describe(2, 64, bad["block_size"], bad["mem_bits"], 32, 32)
+
+
+def test_library_exports_every_declared_symbol():
+    from echokv_b200 import _native as N
+
+    header = (ROOT / "include" / "echokv_b200.h").read_text()
+    declared = set(re.findall(r"\b(echokv_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = ctypes.CDLL(str(N.LIB_PATH))
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} is declared in include/echokv_b200.h but not exported"
+    assert declared == set(N.EXPORTS)
+    assert lib.echokv_abi_version() == 1
+
+
+def test_product_has_no_cpu_path():
+    import torch
+
+    from echokv_b200._util import to_device
+    from echokv_b200.tiered_cache import TieredKVCache, TieredLayout
+
+    L = TieredLayout(num_kv_heads=2, head_size=64, block_size=64, mem_bits=4)
+    with pytest.raises(RuntimeError):
+        TieredKVCache(L, torch.zeros(4, 64 * TieredLayout.per_token_bytes(2, 64, 4), dtype=torch.uint8))
+    with pytest.raises(RuntimeError):
+        to_device(torch.zeros(1), "cpu")
