@@ -51,7 +51,7 @@ def finalize_k(store, key: torch.Tensor, meta, full_grid: bool = False) -> None:
     count, so the host never needs the count (CUDA-graph capture).
     """
     n = meta.n_rows if full_grid else meta.n_fin
-    if not n:
+    if not n or meta.fin.numel() == 0:  # an empty ``fin`` buffer can only mean a count of 0
         return
     N.require_cuda(key, meta.fin)
     key = _rows_hd(key, "key")
