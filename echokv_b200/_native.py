@@ -83,7 +83,10 @@ for _name, _args in _SIGS.items():
     fn.argtypes = _args
     fn.restype = C.c_int
 
-EXPORTS = sorted(list(_SIGS) + ["echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
+lib.echokv_set_decode_path.argtypes = [C.c_int]
+lib.echokv_set_decode_path.restype = C.c_int
+
+EXPORTS = sorted(list(_SIGS) + ["echokv_set_decode_path", "echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
                                 "echokv_demote_scratch_bytes"])
 
 

@@ -1,13 +1,727 @@
-// Tensor-core split-K paged decode attention (selected by echokv_decode when the shape fits).
+// Tensor-core split-K paged decode attention for sm_100a.
+//
+// One CTA per (sequence, split).  A producer warp streams 16-token tiles of the split's blocks
+// into a shared-memory ring with bulk asynchronous copies (cp.async.bulk + mbarrier
+// complete_tx): every token's [K codes | V codes] row goes to a row padded by 16 bytes (so
+// ldmatrix over 8 token rows is bank-conflict free), plus the tile's V stats and its K group's
+// per-channel stats.  16 consumer warps = H heads x TS token sets; set s takes tiles s, s+TS, ...
+// Per tile a warp
+//   * folds the K group's per-channel scale into the query (q' = q * k_scale, fp16) and adds the
+//     constant q . k_min through extra MMA k-steps, so packed K codes feed the tensor cores as
+//     plain integers:  S^T[t, g] = sum_d code[t, d] * q'[g, d] + sum_d k_min[d] * q[g, d];
+//   * unpacks codes to fp16 with mask-or-magic-number tricks (1024 + c etc.) and an exact
+//     subtract, straight from ldmatrix fragments (non-transposed for K, transposed for V so that
+//     register pairs run along tokens);
+//   * keeps an online softmax per query head over tokens (the M dimension) with warp shuffles,
+//     transposes P with movmatrix and accumulates O^T[d, g] += V^T[d, t] * P[t, g]; V's per-token
+//     scale is folded into P per V group (INT8/INT4) or into the codes (INT2), V's min and the
+//     softmax denominator come from one more MMA against [v_min | ones].
+// Accumulator registers map to channels in a tier-specific order (it follows how ldmatrix deals
+// out packed codes); when consecutive blocks differ in tier the warp re-maps its accumulators
+// through shared memory.  Token sets are merged in set order and splits in split order, so a
+// sequence's result depends on its own length only.
 #include "decode_generic.cuh"
 
 namespace echokv {
+namespace mma {
+
+constexpr int D = 128;          // head size of this kernel
+constexpr int NG = 4;           // V groups per head (v_group 32)
+constexpr int TILE = 16;        // tokens per tile
+constexpr int CONSUMER_WARPS = 16;
+constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int MAX_STAGES = 24;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;  // bounded spin on every mbarrier wait
+
+struct StageInfo {
+  int bits;      // tier of the tile's block (0 mapped to 2)
+  int n_valid;   // valid tokens in the tile (1..16)
+  int in_res;    // K of this tile comes from the residual buffer
+  int pos0;      // position of the tile's first token inside its K group
+  long long res_slot;
+};
+
+struct Params {
+  LayoutDev L;
+  ResidualDev R;
+  const uint8_t* pages;
+  DecodeArgs A;
+  int H, TS, NS, max_bits;
+  int stage_bytes, o_vs, o_vm, o_ks, o_km;  // stage layout (bytes from the stage base)
+  int* status;                             // device status word (0 ok), may be null
+};
+
+// ---- PTX helpers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Returns false if the barrier did not flip within the iteration limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t a = smem_u32(bar);
+  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t movm_t(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+template <uint32_t MASK, uint32_t MAGIC>
+__device__ __forceinline__ uint32_t and_or(uint32_t w) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(w), "n"(MASK), "n"(MAGIC));  // (w & MASK) | MAGIC
+  return d;
+}
+__device__ __forceinline__ uint32_t hsub2u(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t hmul2u(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+constexpr uint32_t H2_1024 = 0x64006400u, H2_256 = 0x5c005c00u, H2_64 = 0x54005400u, H2_16 = 0x4c004c00u;
+constexpr uint32_t H2_ONE = 0x3c003c00u;
+
+// ---- unpacking packed codes to fp16 pairs ------------------------------------------------------
+// A 32-bit word of packed codes yields `PAIRS` half2 values; pair i holds the codes at the element
+// positions documented per tier (the two halves are `STRIDE` elements apart).
+//   INT8: 4 codes  -> pairs (0,1) (2,3)
+//   INT4: 8 codes  -> pairs (0,4) (1,5) (2,6) (3,7)
+//   INT2: 16 codes -> pairs (0,8) (1,9) ... (7,15)
+template <int BITS> struct Unpack;
+template <> struct Unpack<8> {
+  static constexpr int PAIRS = 2;
+  __device__ static void run(uint32_t w, uint32_t (&o)[2]) {
+    o[0] = hsub2u(prmt(w, 0x64646464u, 0x4140u), H2_1024);
+    o[1] = hsub2u(prmt(w, 0x64646464u, 0x4342u), H2_1024);
+  }
+  // word = [a.c0 a.c1 | b.c0 b.c1] (two tokens): pairs (a.c0,b.c0) (a.c1,b.c1)
+  __device__ static void run_t(uint32_t w, uint32_t (&o)[2]) {
+    o[0] = hsub2u(prmt(w, 0x64646464u, 0x4240u), H2_1024);
+    o[1] = hsub2u(prmt(w, 0x64646464u, 0x4341u), H2_1024);
+  }
+};
+template <> struct Unpack<4> {
+  static constexpr int PAIRS = 4;
+  __device__ static void run(uint32_t w, uint32_t (&o)[4]) {
+    o[0] = hsub2u(and_or<0x000f000fu, H2_1024>(w), H2_1024);
+    o[1] = hsub2u(and_or<0x00f000f0u, H2_64>(w), H2_64);
+    const uint32_t v = w >> 8;
+    o[2] = hsub2u(and_or<0x000f000fu, H2_1024>(v), H2_1024);
+    o[3] = hsub2u(and_or<0x00f000f0u, H2_64>(v), H2_64);
+  }
+};
+template <> struct Unpack<2> {
+  static constexpr int PAIRS = 8;
+  __device__ static void run(uint32_t w, uint32_t (&o)[8]) {
+    o[0] = hsub2u(and_or<0x00030003u, H2_1024>(w), H2_1024);
+    o[1] = hsub2u(and_or<0x000c000cu, H2_256>(w), H2_256);
+    o[2] = hsub2u(and_or<0x00300030u, H2_64>(w), H2_64);
+    o[3] = hsub2u(and_or<0x00c000c0u, H2_16>(w), H2_16);
+    const uint32_t v = w >> 8;
+    o[4] = hsub2u(and_or<0x00030003u, H2_1024>(v), H2_1024);
+    o[5] = hsub2u(and_or<0x000c000cu, H2_256>(v), H2_256);
+    o[6] = hsub2u(and_or<0x00300030u, H2_64>(v), H2_64);
+    o[7] = hsub2u(and_or<0x00c000c0u, H2_16>(v), H2_16);
+  }
+};
+
+// Channel held by accumulator row (mt, r, half) for blocks of tier BITS.
+template <int BITS>
+__device__ __forceinline__ int acc_channel(int mt, int r, int half) {
+  if constexpr (BITS == 8) return 16 * mt + 2 * r + half;
+  else if constexpr (BITS == 4) return 32 * (mt >> 1) + 4 * r + 2 * (mt & 1) + half;
+  else return 64 * (mt >> 2) + 8 * r + 2 * (mt & 3) + half;
+}
+
+// Shared-memory geometry of the query block: [H][8 query rows][D] fp16, rows padded by 64 bytes so
+// that the 128-bit fragment loads of two neighbouring rows fall into different bank halves.
+constexpr int Q_ROW_BYTES = D * 2 + 64;
+constexpr int REMAP_ROW = D + 4;                      // floats per query head in the canonical layout
+constexpr int REMAP_BYTES = 8 * REMAP_ROW * 4;
+constexpr int SET_EXTRA = 8 + 8 + 8 * NG;             // per (set, head): m[8], l[8], bias[8][NG]
+
+struct WarpState {
+  float acc[8][4];  // O^T tiles: [m-tile][c0..c3], channel order depends on `bits`
+  float bl[4];      // [0],[1]: sum_t p * v_min for V group r (lanes r < NG); [2],[3]: sum_t p
+  float m0, m1;     // running max (log2 domain) of query heads 2j and 2j+1
+  int bits;         // tier whose channel order `acc` is in (0: none yet)
+};
+
+template <int BITS>
+__device__ __forceinline__ void store_canonical(const WarpState& w, float* buf, int r, int j) {
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt) {
+    const int c0 = acc_channel<BITS>(mt, r, 0), c1 = acc_channel<BITS>(mt, r, 1);
+    buf[(2 * j) * REMAP_ROW + c0] = w.acc[mt][0];
+    buf[(2 * j + 1) * REMAP_ROW + c0] = w.acc[mt][1];
+    buf[(2 * j) * REMAP_ROW + c1] = w.acc[mt][2];
+    buf[(2 * j + 1) * REMAP_ROW + c1] = w.acc[mt][3];
+  }
+}
+template <int BITS>
+__device__ __forceinline__ void load_canonical(WarpState& w, const float* buf, int r, int j) {
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt) {
+    const int c0 = acc_channel<BITS>(mt, r, 0), c1 = acc_channel<BITS>(mt, r, 1);
+    w.acc[mt][0] = buf[(2 * j) * REMAP_ROW + c0];
+    w.acc[mt][1] = buf[(2 * j + 1) * REMAP_ROW + c0];
+    w.acc[mt][2] = buf[(2 * j) * REMAP_ROW + c1];
+    w.acc[mt][3] = buf[(2 * j + 1) * REMAP_ROW + c1];
+  }
+}
+__device__ __forceinline__ void store_any(const WarpState& w, float* buf, int r, int j) {
+  if (w.bits == 8) store_canonical<8>(w, buf, r, j);
+  else if (w.bits == 4) store_canonical<4>(w, buf, r, j);
+  else store_canonical<2>(w, buf, r, j);
+}
+
+// Everything a consumer warp needs to address one staged tile.
+struct TileView {
+  uint32_t rows;      // shared address of token row 0 ([K codes | V codes], stride row_stride)
+  uint32_t vs, vm;    // V scale / min of the tile: fp16 [16][H][NG]
+  uint32_t ks, km;    // K scale / min of the tile's group: fp16 [H][D]
+  int row_stride, side_bytes, head_bytes;
+};
+
+// ---- Q.K^T for one tile: scores c[4] = S^T[token r / r+8][query head 2j / 2j+1] (log2 domain) -----
+template <int BITS>
+__device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t q_lane, int h, int lane, float (&c)[4]) {
+  const int j = lane & 3;
+  const uint32_t ks = tv.ks + h * D * 2, km = tv.km + h * D * 2;
+  // ldmatrix row address of this lane: matrix (lane / 8): token (lane % 8) + 8 * (matrix & 1), piece + (matrix >> 1)
+  const int mi = lane >> 3;
+  const uint32_t krow = tv.rows + ((lane & 7) + 8 * (mi & 1)) * tv.row_stride + h * tv.head_bytes + (mi >> 1) * 16;
+  if constexpr (BITS == 8) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // pieces 2i, 2i+1 (16 channels each)
+      uint32_t R[4];
+      ldsm_x4(R, krow + i * 32);
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int p = 2 * i + e;
+        const uint32_t off = (16 * p + 4 * j) * 2;
+        uint2 qw, sw, mw;
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(qw.x), "=r"(qw.y) : "r"(q_lane + off));
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(sw.x), "=r"(sw.y) : "r"(ks + off));
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(mw.x), "=r"(mw.y) : "r"(km + off));
+        mma16816(c, mw.x, mw.x, mw.y, mw.y, qw.x, qw.y);
+        uint32_t a[2], b[2];
+        Unpack<8>::run(R[2 * e], a);
+        Unpack<8>::run(R[2 * e + 1], b);
+        mma16816(c, a[0], b[0], a[1], b[1], hmul2u(qw.x, sw.x), hmul2u(qw.y, sw.y));
+      }
+    }
+  } else if constexpr (BITS == 4) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {  // pieces 2i, 2i+1 (32 channels each)
+      uint32_t R[4];
+      ldsm_x4(R, krow + i * 32);
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int p = 2 * i + e;
+        const uint32_t off = (32 * p + 8 * j) * 2;
+        uint32_t W[4], S[4], M[4], Z[4];
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(W[0]), "=r"(W[1]), "=r"(W[2]), "=r"(W[3]) : "r"(q_lane + off));
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(S[0]), "=r"(S[1]), "=r"(S[2]), "=r"(S[3]) : "r"(ks + off));
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(M[0]), "=r"(M[1]), "=r"(M[2]), "=r"(M[3]) : "r"(km + off));
+        mma16816(c, M[0], M[0], M[1], M[1], W[0], W[1]);
+        mma16816(c, M[2], M[2], M[3], M[3], W[2], W[3]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) Z[k] = hmul2u(W[k], S[k]);
+        uint32_t a[4], b[4];
+        Unpack<4>::run(R[2 * e], a);
+        Unpack<4>::run(R[2 * e + 1], b);
+        mma16816(c, a[0], b[0], a[1], b[1], prmt(Z[0], Z[2], 0x5410u), prmt(Z[0], Z[2], 0x7632u));
+        mma16816(c, a[2], b[2], a[3], b[3], prmt(Z[1], Z[3], 0x5410u), prmt(Z[1], Z[3], 0x7632u));
+      }
+    }
+  } else {
+    uint32_t R[4];
+    ldsm_x4(R, krow);  // pieces 0, 1 (64 channels each)
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+      const uint32_t off = (64 * p + 16 * j) * 2;
+      uint32_t W[8], S[8], M[8], Z[8];
+#pragma unroll
+      for (int v = 0; v < 2; ++v) {
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(W[4 * v]), "=r"(W[4 * v + 1]), "=r"(W[4 * v + 2]), "=r"(W[4 * v + 3]) : "r"(q_lane + off + 16 * v));
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(S[4 * v]), "=r"(S[4 * v + 1]), "=r"(S[4 * v + 2]), "=r"(S[4 * v + 3]) : "r"(ks + off + 16 * v));
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(M[4 * v]), "=r"(M[4 * v + 1]), "=r"(M[4 * v + 2]), "=r"(M[4 * v + 3]) : "r"(km + off + 16 * v));
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) mma16816(c, M[2 * k], M[2 * k], M[2 * k + 1], M[2 * k + 1], W[2 * k], W[2 * k + 1]);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) Z[k] = hmul2u(W[k], S[k]);
+      uint32_t a[8], b[8];
+      Unpack<2>::run(R[2 * p], a);
+      Unpack<2>::run(R[2 * p + 1], b);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        mma16816(c, a[2 * k], b[2 * k], a[2 * k + 1], b[2 * k + 1], prmt(Z[k], Z[k + 4], 0x5410u), prmt(Z[k], Z[k + 4], 0x7632u));
+    }
+  }
+}
+
+// K of the tile comes from the residual buffer (the block's open group): fp16(k) straight into the
+// A fragments, unscaled query as B.  Lane (r, j) takes channels 16p + 4j + {0..3} of rows r, r + 8.
+__device__ __forceinline__ uint32_t res_pair(const ResidualDev& R, int64_t e) {
+  if (R.dtype == ECHOKV_DT_F16) return *reinterpret_cast<const uint32_t*>(reinterpret_cast<const __half*>(R.base) + e);
+  float x, y;
+  if (R.dtype == ECHOKV_DT_BF16) {
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const __nv_bfloat16*>(R.base) + e);
+    x = __uint_as_float(u << 16);
+    y = __uint_as_float(u & 0xffff0000u);
+  } else {
+    const float2 f = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(R.base) + e);
+    x = f.x; y = f.y;
+  }
+  return pack_h2(x, y);
+}
+__device__ __forceinline__ void qk_residual(const ResidualDev& R, const StageInfo& si, uint32_t q_lane, int h, int lane,
+                                            float (&c)[4]) {
+  const int r = lane >> 2, j = lane & 3;
+  const bool v0 = r < si.n_valid, v1 = r + 8 < si.n_valid;
+  const int64_t e0 = si.res_slot * R.s_slot + (int64_t)(si.pos0 + r) * R.s_pos + h * R.s_head;
+  const int64_t e1 = e0 + 8 * R.s_pos;
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    const int ch = 16 * p + 4 * j;
+    uint2 qw;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(qw.x), "=r"(qw.y) : "r"(q_lane + ch * 2));
+    const uint32_t a0 = v0 ? res_pair(R, e0 + ch) : 0u, a2 = v0 ? res_pair(R, e0 + ch + 2) : 0u;
+    const uint32_t a1 = v1 ? res_pair(R, e1 + ch) : 0u, a3 = v1 ? res_pair(R, e1 + ch + 2) : 0u;
+    mma16816(c, a0, a1, a2, a3, qw.x, qw.y);
+  }
+}
+
+// ---- P.V for one tile --------------------------------------------------------------------------
+// pb0 / pb1: B fragments of P (tokens 2j,2j+1 / 2j+8,2j+9 of query head n = lane / 4), fp16.
+template <int BITS>
+__device__ __forceinline__ void pv_codes(const TileView& tv, int H, int h, int lane, uint32_t pb0, uint32_t pb1,
+                                         WarpState& w) {
+  const int r = lane >> 2, j = lane & 3;
+  // V scale of this lane's four tokens, all NG groups: vs2lo[G] = {vs[2j][G], vs[2j+1][G]}, vs2hi[G] likewise +8
+  uint32_t vlo[NG], vhi[NG];
+  {
+    uint2 t0, t1, t2, t3;
+    const uint32_t base = tv.vs + (uint32_t)((2 * j) * H + h) * NG * 2;
+    const uint32_t tok = (uint32_t)H * NG * 2;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t0.x), "=r"(t0.y) : "r"(base));
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t1.x), "=r"(t1.y) : "r"(base + tok));
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t2.x), "=r"(t2.y) : "r"(base + 8 * tok));
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t3.x), "=r"(t3.y) : "r"(base + 9 * tok));
+    vlo[0] = prmt(t0.x, t1.x, 0x5410u); vlo[1] = prmt(t0.x, t1.x, 0x7632u);
+    vlo[2] = prmt(t0.y, t1.y, 0x5410u); vlo[3] = prmt(t0.y, t1.y, 0x7632u);
+    vhi[0] = prmt(t2.x, t3.x, 0x5410u); vhi[1] = prmt(t2.x, t3.x, 0x7632u);
+    vhi[2] = prmt(t2.y, t3.y, 0x5410u); vhi[3] = prmt(t2.y, t3.y, 0x7632u);
+  }
+  const int mi = lane >> 3;
+  const uint32_t vrow = tv.rows + ((lane & 7) + 8 * (mi & 1)) * tv.row_stride + tv.side_bytes + h * tv.head_bytes + (mi >> 1) * 16;
+  if constexpr (BITS == 8) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // pieces 2i, 2i+1 = the two halves of V group i
+      uint32_t Q[4];
+      ldsm_x4_t(Q, vrow + i * 32);
+      const uint32_t b0 = hmul2u(pb0, vlo[i]), b1 = hmul2u(pb1, vhi[i]);
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        uint32_t lo[2], hi[2];
+        Unpack<8>::run_t(Q[2 * e], lo);
+        Unpack<8>::run_t(Q[2 * e + 1], hi);
+        mma16816(w.acc[2 * i + e], lo[0], lo[1], hi[0], hi[1], b0, b1);
+      }
+    }
+  } else if constexpr (BITS == 4) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {  // pieces 2i, 2i+1 = V groups 2i, 2i+1
+      uint32_t Q[4];
+      ldsm_x4_t(Q, vrow + i * 32);
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int G = 2 * i + e;
+        const uint32_t b0 = hmul2u(pb0, vlo[G]), b1 = hmul2u(pb1, vhi[G]);
+        uint32_t lo[4], hi[4];
+        Unpack<4>::run(Q[2 * e], lo);
+        Unpack<4>::run(Q[2 * e + 1], hi);
+        mma16816(w.acc[2 * G], lo[0], lo[1], hi[0], hi[1], b0, b1);
+        mma16816(w.acc[2 * G + 1], lo[2], lo[3], hi[2], hi[3], b0, b1);
+      }
+    }
+  } else {
+    uint32_t Q[4];
+    ldsm_x4_t(Q, vrow);  // pieces 0, 1 = V groups {0,1}, {2,3}; this lane's channels lie in group 2q + (r >= 4)
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const uint32_t sl = r < 4 ? vlo[2 * q] : vlo[2 * q + 1], sh = r < 4 ? vhi[2 * q] : vhi[2 * q + 1];
+      uint32_t lo[8], hi[8];
+      Unpack<2>::run(Q[2 * q], lo);
+      Unpack<2>::run(Q[2 * q + 1], hi);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        mma16816(w.acc[4 * q + u], hmul2u(lo[2 * u], sl), hmul2u(lo[2 * u + 1], sl), hmul2u(hi[2 * u], sh),
+                 hmul2u(hi[2 * u + 1], sh), pb0, pb1);
+    }
+  }
+}
+
+template <int BITS>
+__device__ __forceinline__ void process_tile(const Params& P, const TileView& tv, const StageInfo& si, uint32_t q_lane,
+                                             int h, int lane, WarpState& w, float* remap, int* lock, bool& ok) {
+  const int r = lane >> 2, j = lane & 3;
+  if (w.bits != BITS) {
+    if (w.bits != 0) {  // re-map the accumulators to this tier's channel order (rare: tier changes)
+      if (lane == 0) {
+        uint32_t it = 0;
+        while (atomicCAS(lock, 0, 1) != 0 && ++it < WAIT_LIMIT) {}
+        if (it >= WAIT_LIMIT) ok = false;
+      }
+      __syncwarp();
+      store_any(w, remap, r, j);
+      __syncwarp();
+      load_canonical<BITS>(w, remap, r, j);
+      __syncwarp();
+      if (lane == 0) atomicExch(lock, 0);
+    }
+    w.bits = BITS;
+  }
+  // scores
+  float c[4] = {0.f, 0.f, 0.f, 0.f};
+  if (si.in_res) qk_residual(P.R, si, q_lane, h, lane, c);
+  else qk_codes<BITS>(tv, q_lane, h, lane, c);
+  if (r >= si.n_valid) { c[0] = -INFINITY; c[1] = -INFINITY; }
+  if (r + 8 >= si.n_valid) { c[2] = -INFINITY; c[3] = -INFINITY; }
+  // online softmax over tokens (rows); columns 2j, 2j+1 belong to this lane
+  float t0 = fmaxf(c[0], c[2]), t1 = fmaxf(c[1], c[3]);
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, o));
+    t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, o));
+  }
+  const float n0 = fmaxf(w.m0, t0), n1 = fmaxf(w.m1, t1);
+  const bool grew = (n0 > w.m0) || (n1 > w.m1);
+  if (__any_sync(0xffffffffu, grew)) {
+    const float a0 = ex2(w.m0 - n0), a1 = ex2(w.m1 - n1);
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) { w.acc[mt][0] *= a0; w.acc[mt][1] *= a1; w.acc[mt][2] *= a0; w.acc[mt][3] *= a1; }
+    w.bl[0] *= a0; w.bl[1] *= a1; w.bl[2] *= a0; w.bl[3] *= a1;
+    w.m0 = n0; w.m1 = n1;
+  }
+  const uint32_t p_lo = pack_h2(ex2(c[0] - n0), ex2(c[1] - n1));   // token r
+  const uint32_t p_hi = pack_h2(ex2(c[2] - n0), ex2(c[3] - n1));   // token r + 8
+  const uint32_t pb0 = movm_t(p_lo), pb1 = movm_t(p_hi);
+  // [v_min | ones] rows: bias of V group r (lanes r < NG) and the softmax denominator
+  {
+    uint32_t a0 = 0u, a2 = 0u;
+    if (r < NG) {
+      const uint32_t base = tv.vm + (uint32_t)(((2 * j) * P.H + h) * NG + r) * 2, tok = (uint32_t)P.H * NG * 2;
+      uint32_t x0, x1, x2, x3;
+      asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x0) : "r"(base));
+      asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x1) : "r"(base + tok));
+      asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x2) : "r"(base + 8 * tok));
+      asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x3) : "r"(base + 9 * tok));
+      a0 = x0 | (x1 << 16);
+      a2 = x2 | (x3 << 16);
+    }
+    mma16816(w.bl, a0, H2_ONE, a2, H2_ONE, pb0, pb1);
+  }
+  pv_codes<BITS>(tv, P.H, h, lane, pb0, pb1, w);
+}
+
+// ---- the kernel ------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(const Params P) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const LayoutDev& L = P.L;
+  const DecodeArgs& A = P.A;
+  const int seq = blockIdx.x, split = blockIdx.y;
+  const int64_t seq_len = A.lens[seq];
+  int b_start, b_end;
+  if (!split_range(seq_len, L.BS, A.num_splits, A.bps_min, split, b_start, b_end)) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int H = P.H, TS = P.TS, NS = P.NS;
+  const int64_t tok_begin = (int64_t)b_start * L.BS;
+  const int n_tok = (int)(min(seq_len, (int64_t)b_end * L.BS) - tok_begin);
+  const int n_tiles = (n_tok + TILE - 1) / TILE;
+
+  // shared memory: [barriers | stage info | lock | remap | q | ring (also the final staging)]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* empty = full + MAX_STAGES;
+  StageInfo* info = reinterpret_cast<StageInfo*>(empty + MAX_STAGES);
+  int* lock = reinterpret_cast<int*>(info + MAX_STAGES);
+  float* remap = reinterpret_cast<float*>(smem + 1024);
+  unsigned char* qs = smem + 1024 + REMAP_BYTES;
+  unsigned char* ring = qs + H * 8 * Q_ROW_BYTES;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NS; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, H); }
+    *lock = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // zero the ring once: rows of a partial tile that are never copied must read as finite numbers
+  {
+    const int n16 = (NS * P.stage_bytes) / 16;
+    uint4* z = reinterpret_cast<uint4*>(ring);
+    for (int i = threadIdx.x; i < n16; i += THREADS) z[i] = make_uint4(0, 0, 0, 0);
+  }
+  // queries -> fp16, pre-multiplied by softmax_scale * log2(e); rows >= gqa are zero
+  {
+    const int64_t q_row = A.q_rows ? A.q_rows[seq] : seq;
+    for (int i = threadIdx.x; i < H * 8 * (D / 2); i += THREADS) {
+      const int d2 = i % (D / 2), n = (i / (D / 2)) % 8, hh = i / (4 * D);
+      float x = 0.f, y = 0.f;
+      if (n < A.gqa) {
+        const int64_t e = q_row * A.q_s0 + (int64_t)(hh * A.gqa + n) * A.q_s1 + 2 * d2;
+        x = ld_dt(A.q, A.q_dt, e) * A.scale_log2e;
+        y = ld_dt(A.q, A.q_dt, e + 1) * A.scale_log2e;
+      }
+      *reinterpret_cast<uint32_t*>(qs + (hh * 8 + n) * Q_ROW_BYTES + d2 * 4) = pack_h2(x, y);
+    }
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+
+  bool ok = true;
+  if (warp == CONSUMER_WARPS) {
+    // ===================== producer =====================
+    const int64_t bt_row = A.bt_rows ? A.bt_rows[seq] : seq;
+    const int tiles_per_block = L.BS / TILE;
+    int tile = 0;
+    for (int base = b_start; base < b_end && ok; base += 32) {
+      const int bi = base + lane;
+      int blk = 0, hb = 0, t1 = 0, t2 = 0, t3 = 0, rgrp = -1;
+      long long rslot = -1;
+      if (bi < b_end) {
+        blk = A.bt[bt_row * A.bt_s0 + bi];
+        const uint4 hd = *reinterpret_cast<const uint4*>(P.pages + (int64_t)blk * L.PS);
+        hb = hd.x & 0xff; t1 = (int)hd.y; t2 = (int)hd.z; t3 = (int)hd.w;
+        rslot = P.R.block_res[blk];
+        if (rslot >= 0) rgrp = (int)P.R.res_group[rslot];
+      }
+      const int nb = min(32, b_end - base);
+      for (int k = 0; k < nb && ok; ++k) {
+        const int kblk = __shfl_sync(0xffffffffu, blk, k);
+        int bits = __shfl_sync(0xffffffffu, hb, k);
+        const int c1 = __shfl_sync(0xffffffffu, t1, k), c2 = __shfl_sync(0xffffffffu, t2, k), c3 = __shfl_sync(0xffffffffu, t3, k);
+        const long long ks_slot = __shfl_sync(0xffffffffu, rslot, k);
+        const int kgrp = __shfl_sync(0xffffffffu, rgrp, k);
+        if (bits != 2 && bits != 4 && bits != 8) bits = 2;  // never opened (or unknown): stay inside the page
+        if (bits > P.max_bits) bits = P.max_bits;            // cannot happen under the layout's budget
+        const int blk_tok = (int)min((int64_t)L.BS, seq_len - (int64_t)(base + k) * L.BS);
+        const int row_bytes = (2 * H * D * bits) / 8;
+        const int tpc = (2 * L.BS) / bits;
+        const unsigned char* page = P.pages + (int64_t)kblk * L.PS;
+        for (int tb = 0; tb < tiles_per_block && tb * TILE < blk_tok && ok; ++tb, ++tile) {
+          const int st = tile % NS;
+          if (tile >= NS) ok = mbar_wait(empty + st, ((tile / NS) - 1) & 1);
+          if (!ok) break;
+          const int t0 = tb * TILE;
+          const int n_valid = min(TILE, blk_tok - t0);
+          const int grp = t0 / L.KG;
+          const bool in_res = ks_slot >= 0 && grp == kgrp;
+          unsigned char* sb = ring + st * P.stage_bytes;
+          if (lane == 0) {
+            info[st].bits = bits; info[st].n_valid = n_valid; info[st].in_res = in_res ? 1 : 0;
+            info[st].pos0 = t0 % L.KG; info[st].res_slot = ks_slot;
+            const uint32_t bytes = n_valid * row_bytes + 2 * (TILE * H * NG * 2) + (in_res ? 0 : 2 * H * D * 2);
+            mbar_expect_tx(full + st, bytes);
+          }
+          __syncwarp();
+          if (lane < n_valid) {
+            const int tok = t0 + lane;
+            const int jc = tok / tpc;
+            int64_t pg = kblk, slot = 0;
+            if (jc > 0) { const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3); pg = id / L.KC; slot = id % L.KC; }
+            const unsigned char* src = P.pages + pg * L.PS + L.o_data + slot * L.CB + (int64_t)(tok % tpc) * row_bytes;
+            bulk_copy(sb + lane * (row_bytes + 16), src, row_bytes, full + st);
+          } else if (lane == 16) {
+            bulk_copy(sb + P.o_vs, page + L.o_vs + (int64_t)t0 * H * NG * 2, TILE * H * NG * 2, full + st);
+          } else if (lane == 17) {
+            bulk_copy(sb + P.o_vm, page + L.o_vm + (int64_t)t0 * H * NG * 2, TILE * H * NG * 2, full + st);
+          } else if (lane == 18 && !in_res) {
+            bulk_copy(sb + P.o_ks, page + L.o_ks + (int64_t)grp * H * D * 2, H * D * 2, full + st);
+          } else if (lane == 19 && !in_res) {
+            bulk_copy(sb + P.o_km, page + L.o_km + (int64_t)grp * H * D * 2, H * D * 2, full + st);
+          }
+          __syncwarp();
+        }
+      }
+    }
+  } else {
+    // ===================== consumers =====================
+    const int h = warp % H, ts = warp / H;
+    const int r = lane >> 2, j = lane & 3;
+    WarpState w;
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) { w.acc[mt][0] = w.acc[mt][1] = w.acc[mt][2] = w.acc[mt][3] = 0.f; }
+    w.bl[0] = w.bl[1] = w.bl[2] = w.bl[3] = 0.f;
+    w.m0 = w.m1 = -INFINITY;
+    w.bits = 0;
+    const uint32_t q_lane = smem_u32(qs + (h * 8 + r) * Q_ROW_BYTES);
+    for (int tile = ts; tile < n_tiles && ok; tile += TS) {
+      const int st = tile % NS;
+      ok = mbar_wait(full + st, (tile / NS) & 1);
+      if (!ok) break;
+      const StageInfo si = info[st];
+      TileView tv;
+      const uint32_t sb = smem_u32(ring + st * P.stage_bytes);
+      tv.rows = sb; tv.vs = sb + P.o_vs; tv.vm = sb + P.o_vm; tv.ks = sb + P.o_ks; tv.km = sb + P.o_km;
+      tv.side_bytes = (H * D * si.bits) / 8;
+      tv.head_bytes = (D * si.bits) / 8;
+      tv.row_stride = 2 * tv.side_bytes + 16;
+      if (si.bits == 4) process_tile<4>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
+      else if (si.bits == 8) process_tile<8>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
+      else process_tile<2>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty + st);
+    }
+    // ---- merge the token sets in set order; the ring is reused as staging ----
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32));
+    float* stag = reinterpret_cast<float*>(ring);
+    float* mine = stag + (size_t)(ts * H + h) * (8 * REMAP_ROW + SET_EXTRA);
+    if (w.bits == 0) w.bits = 2;
+    store_any(w, mine, r, j);
+    float* ex = mine + 8 * REMAP_ROW;
+    if (r == 0) { ex[2 * j] = w.m0; ex[2 * j + 1] = w.m1; ex[8 + 2 * j] = w.bl[2]; ex[8 + 2 * j + 1] = w.bl[3]; }
+    if (r < NG) { ex[16 + (2 * j) * NG + r] = w.bl[0]; ex[16 + (2 * j + 1) * NG + r] = w.bl[1]; }
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32));
+    const int tid = threadIdx.x;
+    for (int i = tid; i < H * A.gqa * D; i += CONSUMER_WARPS * 32) {
+      const int d = i % D, g = (i / D) % A.gqa, hh = i / (D * A.gqa);
+      float mt = -INFINITY;
+      for (int s = 0; s < TS; ++s) mt = fmaxf(mt, stag[(size_t)(s * H + hh) * (8 * REMAP_ROW + SET_EXTRA) + 8 * REMAP_ROW + g]);
+      float a = 0.f, lt = 0.f;
+      for (int s = 0; s < TS; ++s) {
+        const float* b = stag + (size_t)(s * H + hh) * (8 * REMAP_ROW + SET_EXTRA);
+        const float* e = b + 8 * REMAP_ROW;
+        const float wgt = exp2f(e[g] - mt);
+        a += (b[g * REMAP_ROW + d] + e[16 + g * NG + d / 32]) * wgt;
+        lt += e[8 + g] * wgt;
+      }
+      const int64_t o = ((int64_t)seq * A.Hq + hh * A.gqa + g) * A.num_splits + split;
+      A.acc[o * D + d] = a;
+      if (d == 0) { A.ml[o * 2] = mt; A.ml[o * 2 + 1] = lt; }
+    }
+  }
+  if (!ok && lane == 0 && P.status) atomicExch(P.status, 1);
+}
+
+}  // namespace mma
+
+// Chooses the tensor-core kernel when the shape fits; otherwise leaves `handled` false.
+static int g_decode_path = 0;  // 0: pick by shape, 1: always the generic kernel
 
 int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
                       int64_t num_seqs, cudaStream_t st, bool* handled) {
-  (void)L; (void)R; (void)pages; (void)A; (void)num_seqs; (void)st;
+  using namespace mma;
   *handled = false;
+  if (g_decode_path == 1) return ECHOKV_OK;
+  const int H = L.H;
+  if (L.D != D || L.VG != 32 || L.KG % TILE || L.BS % TILE || A.gqa > 8) return ECHOKV_OK;
+  if (!(H == 1 || H == 2 || H == 4 || H == 8)) return ECHOKV_OK;
+  if ((R.s_slot | R.s_pos | R.s_head) & 3) return ECHOKV_OK;                 // 8-byte residual loads
+  if ((reinterpret_cast<uintptr_t>(R.base) & 15) != 0) return ECHOKV_OK;
+  Params P;
+  P.L = L; P.R = R; P.pages = pages; P.A = A; P.H = H;
+  P.TS = CONSUMER_WARPS / H;
+  // any tier can appear as soon as the pool has spare chunks (an INT8 block borrows 3 of them),
+  // so stages are sized for INT8 rows unless the pool is empty by construction (mem_bits 2)
+  P.max_bits = L.KC >= 2 ? 8 : 2;
+  const int row_stride = (2 * H * D * P.max_bits) / 8 + 16;
+  P.o_vs = TILE * row_stride;
+  P.o_vm = P.o_vs + TILE * H * NG * 2;
+  P.o_ks = P.o_vm + TILE * H * NG * 2;
+  P.o_km = P.o_ks + H * D * 2;
+  P.stage_bytes = (P.o_km + H * D * 2 + 127) / 128 * 128;
+  P.status = nullptr;
+  const int fixed = 1024 + REMAP_BYTES + H * 8 * Q_ROW_BYTES;
+  const int staging = P.TS * H * (8 * REMAP_ROW + SET_EXTRA) * 4;
+  static int max_smem = -1;
+  if (max_smem < 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  }
+  int ns = (max_smem - fixed) / P.stage_bytes;
+  if (ns > MAX_STAGES) ns = MAX_STAGES;
+  if (ns > 2 * P.TS + 4) ns = 2 * P.TS + 4;
+  if (ns < P.TS + 1 || ns * P.stage_bytes < staging) {
+    ns = (staging + P.stage_bytes - 1) / P.stage_bytes;
+    if (ns < P.TS + 1) ns = P.TS + 1;
+    if (ns > MAX_STAGES || fixed + ns * P.stage_bytes > max_smem) return ECHOKV_OK;
+  }
+  P.NS = ns;
+  const int smem_bytes = fixed + ns * P.stage_bytes;
+  static int configured = 0;
+  if (configured < smem_bytes) {
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e != cudaSuccess) return set_error(ECHOKV_E_CUDA, "decode: cannot raise shared memory: %s", cudaGetErrorString(e));
+    configured = max_smem;
+  }
+  dim3 grid((unsigned)num_seqs, (unsigned)A.num_splits);
+  decode_mma_kernel<<<grid, THREADS, smem_bytes, st>>>(P);
+  int rc = check_launch("decode (tensor-core kernel)");
+  if (rc) return rc;
+  *handled = true;
   return ECHOKV_OK;
 }
 
 }  // namespace echokv
+
+extern "C" int echokv_set_decode_path(int path) {
+  const int old = echokv::g_decode_path;
+  echokv::g_decode_path = path;
+  return old;
+}

@@ -156,6 +156,12 @@ int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const 
                   float softmax_scale, int32_t num_splits, int32_t blocks_per_split,
                   int64_t num_seqs, int32_t num_q_heads, void* stream);
 
+/* Kernel selection of echokv_decode: 0 (default) picks the tensor-core kernel when the shape fits
+ * (head_size 128, v_group 32, 1/2/4/8 KV heads, <= 8 query heads per KV head) and the generic
+ * CUDA-core kernel otherwise; 1 always takes the generic kernel.  Returns the previous setting.
+ * No counterpart in the reference (its Triton autotuner plays this role, kernels/decode.py:265-280). */
+int echokv_set_decode_path(int path);
+
 /* Dequantize whole contexts into dense [total_ctx, H, D] K and V of `out_dtype`
  * -- dequant_dense / _dequant_kernel (kernels/prefill.py:90-115, :329-369).
  * `work` int32 [n_work, 4]: request (block-table row), block index, dense row of the

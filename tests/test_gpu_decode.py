@@ -123,3 +123,42 @@ def test_prefill_matches_oracle_and_fixture(sc):
     assert np.abs(got - want).max() <= tol
     ref = load_golden(sc.name)
     assert np.abs(got[ref["attn_rows"]] - ref["attn_out"]).max() <= tol
+
+
+MMA_SHAPES = [s for s in DEC if s.spec.d == 128 and s.spec.vg == 32 and s.spec.h in (1, 2, 4, 8)]
+
+
+@pytest.mark.parametrize("sc", MMA_SHAPES, ids=lambda s: s.name)
+def test_tensor_core_and_generic_kernels_agree(sc):
+    """Both decode kernels on the same store: each within tolerance of the oracle, and within
+    2e-3 of each other (they differ only in fp16 operand rounding)."""
+    import torch
+    from echokv_b200 import _native as N
+    from echokv_b200.kernels.decode import decode_attention
+
+    store, q, table, lens, _ = _store_and_inputs(sc)
+    want = run_oracle(sc)["attn_out"]
+    old = N.lib.echokv_set_decode_path(1)
+    try:
+        gen = decode_attention(store, q, table, lens, sc.scale).cpu().numpy()
+    finally:
+        N.lib.echokv_set_decode_path(old)
+    mma = decode_attention(store, q, table, lens, sc.scale).cpu().numpy()
+    assert np.isfinite(mma).all()
+    assert np.abs(gen - want).max() <= 5e-3 and np.abs(mma - want).max() <= 5e-3
+    assert np.abs(mma - gen).max() <= 5e-3 and rel_l2(mma, want) <= 2e-3
+
+
+def test_mixed_tiers_inside_one_split_remap_accumulators():
+    """Blocks of all three tiers alternate inside every split of a long sequence (the tensor-core
+    kernel re-maps its accumulators at every tier change) with 1, 3 and 7 splits."""
+    import torch
+    from echokv_b200.kernels.decode import decode_attention
+
+    sc = S.build_attention("alternating", 8, 128, 16, 8, [1000, 517, 31], [8, 4, 2, 4, 2, 8, 2], seed=77, kg=16,
+                           dtype="bf16", gqa=4)
+    store, q, table, lens, _ = _store_and_inputs(sc)
+    want = run_oracle(sc)["attn_out"]
+    for num_splits, bps in ((1, 1), (3, 4), (7, 2), (32, 1)):
+        got = decode_attention(store, q, table, lens, sc.scale, bps, num_splits=num_splits).cpu().numpy()
+        assert np.abs(got - want).max() <= 5e-3 and rel_l2(got, want) <= 2e-3, (num_splits, bps)
