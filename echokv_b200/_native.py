@@ -32,7 +32,8 @@ class LayoutInfo(C.Structure):
 
 
 class Pages(C.Structure):
-    _fields_ = [("base", C.c_void_p), ("page_stride_bytes", C.c_int64), ("num_blocks", C.c_int64)]
+    _fields_ = [("base", C.c_void_p), ("page_stride_bytes", C.c_int64), ("num_blocks", C.c_int64),
+                ("max_tier", C.c_int32), ("reserved", C.c_int32)]
 
 
 class Residual(C.Structure):

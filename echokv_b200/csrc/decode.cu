@@ -5,7 +5,7 @@ using namespace echokv;
 
 namespace echokv {
 int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
-                      int64_t num_seqs, cudaStream_t st, bool* handled);
+                      int64_t num_seqs, int max_tier, int* status, cudaStream_t st, bool* handled);
 
 // out[q_rows[seq], head] = splits merged in split order (kernels/decode.py:226-262).
 __global__ void decode_merge_kernel(DecodeArgs A, int BS, int D) {
@@ -92,7 +92,7 @@ int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const 
   const uint8_t* pg = (const uint8_t*)pages->base;
 
   bool handled = false;
-  rc = launch_decode_mma(L, R, pg, A, num_seqs, st, &handled);
+  rc = launch_decode_mma(L, R, pg, A, num_seqs, pages->max_tier, nullptr, st, &handled);
   if (rc) return rc;
   if (!handled) {
     dim3 grid((unsigned)num_seqs, (unsigned)L.H, (unsigned)num_splits);

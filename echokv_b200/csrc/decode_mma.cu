@@ -28,8 +28,6 @@ namespace mma {
 constexpr int D = 128;          // head size of this kernel
 constexpr int NG = 4;           // V groups per head (v_group 32)
 constexpr int TILE = 16;        // tokens per tile
-constexpr int CONSUMER_WARPS = 16;
-constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
 constexpr int MAX_STAGES = 24;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;  // bounded spin on every mbarrier wait
 
@@ -46,7 +44,7 @@ struct Params {
   ResidualDev R;
   const uint8_t* pages;
   DecodeArgs A;
-  int H, TS, NS, max_bits;
+  int H, NS, max_bits, num_seqs;
   int stage_bytes, o_vs, o_vm, o_ks, o_km;  // stage layout (bytes from the stage base)
   int* status;                             // device status word (0 ok), may be null
 };
@@ -192,7 +190,6 @@ __device__ __forceinline__ int acc_channel(int mt, int r, int half) {
 constexpr int Q_ROW_BYTES = D * 2 + 64;
 constexpr int REMAP_ROW = D + 4;                      // floats per query head in the canonical layout
 constexpr int REMAP_BYTES = 8 * REMAP_ROW * 4;
-constexpr int SET_EXTRA = 8 + 8 + 8 * NG;             // per (set, head): m[8], l[8], bias[8][NG]
 
 struct WarpState {
   float acc[8][4];  // O^T tiles: [m-tile][c0..c3], channel order depends on `bits`
@@ -482,21 +479,77 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
 }
 
 // ---- the kernel ------------------------------------------------------------------------------
-__global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(const Params P) {
+// Persistent: CTA c walks the work items c, c + gridDim.x, ... in split-major order (item =
+// split * num_seqs + seq), so neighbouring CTAs work on different sequences of similar length and
+// the short tail splits come last.  One producer warp + H consumer warps (one per KV head).
+__device__ __forceinline__ bool item_range(const Params& P, int item, int& seq, int& split, int64_t& seq_len,
+                                           int& b_start, int& b_end) {
+  seq = item % P.num_seqs;
+  split = item / P.num_seqs;
+  seq_len = P.A.lens[seq];
+  return split_range(seq_len, P.L.BS, P.A.num_splits, P.A.bps_min, split, b_start, b_end);
+}
+
+// Block metadata the producer prefetches for up to 32 blocks at a time (one block per lane).
+struct BlockMeta {
+  int blk, bits, c1, c2, c3, rgrp;
+  long long rslot;
+};
+__device__ __forceinline__ BlockMeta load_meta(const Params& P, int64_t bt_row, int bi, int b_end) {
+  BlockMeta m;
+  m.blk = 0; m.bits = 0; m.c1 = m.c2 = m.c3 = 0; m.rgrp = -1; m.rslot = -1;
+  if (bi < b_end) {
+    m.blk = P.A.bt[bt_row * P.A.bt_s0 + bi];
+    const uint4 hd = *reinterpret_cast<const uint4*>(P.pages + (int64_t)m.blk * P.L.PS);
+    m.bits = hd.x & 0xff; m.c1 = (int)hd.y; m.c2 = (int)hd.z; m.c3 = (int)hd.w;
+    m.rslot = P.R.block_res[m.blk];
+    if (m.rslot >= 0) m.rgrp = (int)P.R.res_group[m.rslot];
+  }
+  return m;
+}
+
+template <int BITS>
+__device__ __forceinline__ void write_partial(const Params& P, const WarpState& w, int seq, int split, int h, int lane) {
+  const int r = lane >> 2, j = lane & 3;
+  const DecodeArgs& A = P.A;
+  const int g0 = 2 * j, g1 = 2 * j + 1;
+  const int64_t o0 = (((int64_t)seq * A.Hq + h * A.gqa + g0) * A.num_splits + split);
+  const int64_t o1 = o0 + A.num_splits;
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt) {
+    // V min contribution of the channels' group: held by lane (r = G, j)
+    int G;
+    if constexpr (BITS == 8) G = mt >> 1;
+    else if constexpr (BITS == 4) G = mt >> 1;
+    else G = 2 * (mt >> 2) + (r >= 4 ? 1 : 0);
+    const float bias0 = __shfl_sync(0xffffffffu, w.bl[0], G * 4 + j);
+    const float bias1 = __shfl_sync(0xffffffffu, w.bl[1], G * 4 + j);
+    const int c0 = acc_channel<BITS>(mt, r, 0), c1 = acc_channel<BITS>(mt, r, 1);
+    if (g0 < A.gqa) {
+      A.acc[o0 * D + c0] = w.acc[mt][0] + bias0;
+      A.acc[o0 * D + c1] = w.acc[mt][2] + bias0;
+    }
+    if (g1 < A.gqa) {
+      A.acc[o1 * D + c0] = w.acc[mt][1] + bias1;
+      A.acc[o1 * D + c1] = w.acc[mt][3] + bias1;
+    }
+  }
+  if (r == 0) {
+    if (g0 < A.gqa) { A.ml[o0 * 2] = w.m0; A.ml[o0 * 2 + 1] = w.bl[2]; }
+    if (g1 < A.gqa) { A.ml[o1 * 2] = w.m1; A.ml[o1 * 2 + 1] = w.bl[3]; }
+  }
+}
+
+__global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
   extern __shared__ __align__(128) unsigned char smem[];
   const LayoutDev& L = P.L;
   const DecodeArgs& A = P.A;
-  const int seq = blockIdx.x, split = blockIdx.y;
-  const int64_t seq_len = A.lens[seq];
-  int b_start, b_end;
-  if (!split_range(seq_len, L.BS, A.num_splits, A.bps_min, split, b_start, b_end)) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int H = P.H, TS = P.TS, NS = P.NS;
-  const int64_t tok_begin = (int64_t)b_start * L.BS;
-  const int n_tok = (int)(min(seq_len, (int64_t)b_end * L.BS) - tok_begin);
-  const int n_tiles = (n_tok + TILE - 1) / TILE;
+  const int H = P.H, NS = P.NS;
+  const int nthreads = (H + 1) * 32;
+  const int n_items = P.num_seqs * A.num_splits;
 
-  // shared memory: [barriers | stage info | lock | remap | q | ring (also the final staging)]
+  // shared memory: [barriers | stage info | lock][remap][q (fp16, per head)][ring]
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + MAX_STAGES;
   StageInfo* info = reinterpret_cast<StageInfo*>(empty + MAX_STAGES);
@@ -510,82 +563,82 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(const Params P) 
     *lock = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // zero the ring once: rows of a partial tile that are never copied must read as finite numbers
-  {
+  {  // zero the ring once: rows of a partial tile that are never copied must read as finite numbers
     const int n16 = (NS * P.stage_bytes) / 16;
     uint4* z = reinterpret_cast<uint4*>(ring);
-    for (int i = threadIdx.x; i < n16; i += THREADS) z[i] = make_uint4(0, 0, 0, 0);
-  }
-  // queries -> fp16, pre-multiplied by softmax_scale * log2(e); rows >= gqa are zero
-  {
-    const int64_t q_row = A.q_rows ? A.q_rows[seq] : seq;
-    for (int i = threadIdx.x; i < H * 8 * (D / 2); i += THREADS) {
-      const int d2 = i % (D / 2), n = (i / (D / 2)) % 8, hh = i / (4 * D);
-      float x = 0.f, y = 0.f;
-      if (n < A.gqa) {
-        const int64_t e = q_row * A.q_s0 + (int64_t)(hh * A.gqa + n) * A.q_s1 + 2 * d2;
-        x = ld_dt(A.q, A.q_dt, e) * A.scale_log2e;
-        y = ld_dt(A.q, A.q_dt, e + 1) * A.scale_log2e;
-      }
-      *reinterpret_cast<uint32_t*>(qs + (hh * 8 + n) * Q_ROW_BYTES + d2 * 4) = pack_h2(x, y);
-    }
+    for (int i = threadIdx.x; i < n16; i += nthreads) z[i] = make_uint4(0, 0, 0, 0);
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncthreads();
 
-  bool ok = true;
-  if (warp == CONSUMER_WARPS) {
+  bool ok = true, bad_tier = false;
+  int tile = 0;  // tiles issued / consumed by this CTA so far (both sides count identically)
+  if (warp == H) {
     // ===================== producer =====================
-    const int64_t bt_row = A.bt_rows ? A.bt_rows[seq] : seq;
     const int tiles_per_block = L.BS / TILE;
-    int tile = 0;
-    for (int base = b_start; base < b_end && ok; base += 32) {
-      const int bi = base + lane;
-      int blk = 0, hb = 0, t1 = 0, t2 = 0, t3 = 0, rgrp = -1;
-      long long rslot = -1;
-      if (bi < b_end) {
-        blk = A.bt[bt_row * A.bt_s0 + bi];
-        const uint4 hd = *reinterpret_cast<const uint4*>(P.pages + (int64_t)blk * L.PS);
-        hb = hd.x & 0xff; t1 = (int)hd.y; t2 = (int)hd.z; t3 = (int)hd.w;
-        rslot = P.R.block_res[blk];
-        if (rslot >= 0) rgrp = (int)P.R.res_group[rslot];
+    // software pipeline over "units" (an item's next <= 32 blocks): the next unit's metadata is
+    // requested before the current unit's tiles are issued, so its latency hides behind them
+    int item = blockIdx.x, seq = 0, split = 0, b_start = 0, b_end = 0, base = 0;
+    int64_t seq_len = 0, bt_row = 0;
+    bool have = false;
+    auto advance = [&]() {  // move (item, base) to the next unit; false when the CTA is out of work
+      if (have && base + 32 < b_end) { base += 32; return true; }
+      if (have) item += gridDim.x;
+      for (; item < n_items; item += gridDim.x) {
+        if (item_range(P, item, seq, split, seq_len, b_start, b_end)) {
+          base = b_start; bt_row = A.bt_rows ? A.bt_rows[seq] : seq; have = true;
+          return true;
+        }
       }
-      const int nb = min(32, b_end - base);
+      return false;
+    };
+    bool more = advance();
+    BlockMeta nxt = more ? load_meta(P, bt_row, base + lane, b_end) : BlockMeta{};
+    while (more && ok) {
+      const BlockMeta cur = nxt;
+      const int u_base = base, u_end = b_end;
+      const int64_t u_len = seq_len;
+      more = advance();
+      if (more) nxt = load_meta(P, bt_row, base + lane, b_end);
+      const int nb = min(32, u_end - u_base);
       for (int k = 0; k < nb && ok; ++k) {
-        const int kblk = __shfl_sync(0xffffffffu, blk, k);
-        int bits = __shfl_sync(0xffffffffu, hb, k);
-        const int c1 = __shfl_sync(0xffffffffu, t1, k), c2 = __shfl_sync(0xffffffffu, t2, k), c3 = __shfl_sync(0xffffffffu, t3, k);
-        const long long ks_slot = __shfl_sync(0xffffffffu, rslot, k);
-        const int kgrp = __shfl_sync(0xffffffffu, rgrp, k);
-        if (bits != 2 && bits != 4 && bits != 8) bits = 2;  // never opened (or unknown): stay inside the page
-        if (bits > P.max_bits) bits = P.max_bits;            // cannot happen under the layout's budget
-        const int blk_tok = (int)min((int64_t)L.BS, seq_len - (int64_t)(base + k) * L.BS);
+        const int kblk = __shfl_sync(0xffffffffu, cur.blk, k);
+        int bits = __shfl_sync(0xffffffffu, cur.bits, k);
+        const int c1 = __shfl_sync(0xffffffffu, cur.c1, k), c2 = __shfl_sync(0xffffffffu, cur.c2, k),
+                  c3 = __shfl_sync(0xffffffffu, cur.c3, k);
+        const long long ks_slot = __shfl_sync(0xffffffffu, cur.rslot, k);
+        const int kgrp = __shfl_sync(0xffffffffu, cur.rgrp, k);
+        if (bits != 2 && bits != 4 && bits != 8) bits = 2;  // never opened: stay inside the page
+        bool too_wide = bits > P.max_bits;                   // the host's tier bound was wrong
+        if (too_wide) { bits = P.max_bits; bad_tier = true; }  // tiles are issued empty; status reports it
+        const int blk_tok = (int)min((int64_t)L.BS, u_len - (int64_t)(u_base + k) * L.BS);
         const int row_bytes = (2 * H * D * bits) / 8;
         const int tpc = (2 * L.BS) / bits;
         const unsigned char* page = P.pages + (int64_t)kblk * L.PS;
-        for (int tb = 0; tb < tiles_per_block && tb * TILE < blk_tok && ok; ++tb, ++tile) {
+        for (int tb = 0; tb < tiles_per_block && tb * TILE < blk_tok; ++tb, ++tile) {
           const int st = tile % NS;
-          if (tile >= NS) ok = mbar_wait(empty + st, ((tile / NS) - 1) & 1);
-          if (!ok) break;
+          if (tile >= NS && !mbar_wait(empty + st, ((tile / NS) - 1) & 1)) { ok = false; break; }
           const int t0 = tb * TILE;
           const int n_valid = min(TILE, blk_tok - t0);
           const int grp = t0 / L.KG;
           const bool in_res = ks_slot >= 0 && grp == kgrp;
           unsigned char* sb = ring + st * P.stage_bytes;
           if (lane == 0) {
-            info[st].bits = bits; info[st].n_valid = n_valid; info[st].in_res = in_res ? 1 : 0;
+            info[st].bits = bits; info[st].n_valid = too_wide ? 0 : n_valid; info[st].in_res = in_res ? 1 : 0;
             info[st].pos0 = t0 % L.KG; info[st].res_slot = ks_slot;
-            const uint32_t bytes = n_valid * row_bytes + 2 * (TILE * H * NG * 2) + (in_res ? 0 : 2 * H * D * 2);
+            const uint32_t bytes = (too_wide ? 0 : n_valid * row_bytes) + 2 * (TILE * H * NG * 2) + (in_res ? 0 : 2 * H * D * 2);
             mbar_expect_tx(full + st, bytes);
           }
           __syncwarp();
           if (lane < n_valid) {
-            const int tok = t0 + lane;
-            const int jc = tok / tpc;
-            int64_t pg = kblk, slot = 0;
-            if (jc > 0) { const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3); pg = id / L.KC; slot = id % L.KC; }
-            const unsigned char* src = P.pages + pg * L.PS + L.o_data + slot * L.CB + (int64_t)(tok % tpc) * row_bytes;
-            bulk_copy(sb + lane * (row_bytes + 16), src, row_bytes, full + st);
+            if (!too_wide) {
+              const int tok = t0 + lane;
+              const int jc = tok / tpc;
+              int64_t pg = kblk, slot = 0;
+              if (jc > 0) { const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3); pg = id / L.KC; slot = id % L.KC; }
+              const unsigned char* src = P.pages + pg * L.PS + L.o_data + slot * L.CB + (int64_t)(tok % tpc) * row_bytes;
+              bulk_copy(sb + lane * (row_bytes + 16), src, row_bytes, full + st);
+            }
           } else if (lane == 16) {
             bulk_copy(sb + P.o_vs, page + L.o_vs + (int64_t)t0 * H * NG * 2, TILE * H * NG * 2, full + st);
           } else if (lane == 17) {
@@ -600,71 +653,72 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mma_kernel(const Params P) 
       }
     }
   } else {
-    // ===================== consumers =====================
-    const int h = warp % H, ts = warp / H;
-    const int r = lane >> 2, j = lane & 3;
-    WarpState w;
-#pragma unroll
-    for (int mt = 0; mt < 8; ++mt) { w.acc[mt][0] = w.acc[mt][1] = w.acc[mt][2] = w.acc[mt][3] = 0.f; }
-    w.bl[0] = w.bl[1] = w.bl[2] = w.bl[3] = 0.f;
-    w.m0 = w.m1 = -INFINITY;
-    w.bits = 0;
-    const uint32_t q_lane = smem_u32(qs + (h * 8 + r) * Q_ROW_BYTES);
-    for (int tile = ts; tile < n_tiles && ok; tile += TS) {
-      const int st = tile % NS;
-      ok = mbar_wait(full + st, (tile / NS) & 1);
-      if (!ok) break;
-      const StageInfo si = info[st];
-      TileView tv;
-      const uint32_t sb = smem_u32(ring + st * P.stage_bytes);
-      tv.rows = sb; tv.vs = sb + P.o_vs; tv.vm = sb + P.o_vm; tv.ks = sb + P.o_ks; tv.km = sb + P.o_km;
-      tv.side_bytes = (H * D * si.bits) / 8;
-      tv.head_bytes = (D * si.bits) / 8;
-      tv.row_stride = 2 * tv.side_bytes + 16;
-      if (si.bits == 4) process_tile<4>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
-      else if (si.bits == 8) process_tile<8>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
-      else process_tile<2>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty + st);
-    }
-    // ---- merge the token sets in set order; the ring is reused as staging ----
-    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32));
-    float* stag = reinterpret_cast<float*>(ring);
-    float* mine = stag + (size_t)(ts * H + h) * (8 * REMAP_ROW + SET_EXTRA);
-    if (w.bits == 0) w.bits = 2;
-    store_any(w, mine, r, j);
-    float* ex = mine + 8 * REMAP_ROW;
-    if (r == 0) { ex[2 * j] = w.m0; ex[2 * j + 1] = w.m1; ex[8 + 2 * j] = w.bl[2]; ex[8 + 2 * j + 1] = w.bl[3]; }
-    if (r < NG) { ex[16 + (2 * j) * NG + r] = w.bl[0]; ex[16 + (2 * j + 1) * NG + r] = w.bl[1]; }
-    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32));
-    const int tid = threadIdx.x;
-    for (int i = tid; i < H * A.gqa * D; i += CONSUMER_WARPS * 32) {
-      const int d = i % D, g = (i / D) % A.gqa, hh = i / (D * A.gqa);
-      float mt = -INFINITY;
-      for (int s = 0; s < TS; ++s) mt = fmaxf(mt, stag[(size_t)(s * H + hh) * (8 * REMAP_ROW + SET_EXTRA) + 8 * REMAP_ROW + g]);
-      float a = 0.f, lt = 0.f;
-      for (int s = 0; s < TS; ++s) {
-        const float* b = stag + (size_t)(s * H + hh) * (8 * REMAP_ROW + SET_EXTRA);
-        const float* e = b + 8 * REMAP_ROW;
-        const float wgt = exp2f(e[g] - mt);
-        a += (b[g * REMAP_ROW + d] + e[16 + g * NG + d / 32]) * wgt;
-        lt += e[8 + g] * wgt;
+    // ===================== consumers: warp h owns KV head h =====================
+    const int h = warp;
+    const int r = lane >> 2;
+    unsigned char* my_q = qs + h * 8 * Q_ROW_BYTES;
+    const uint32_t q_lane = smem_u32(my_q + r * Q_ROW_BYTES);
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      int seq, split, b_start, b_end;
+      int64_t seq_len;
+      if (!item_range(P, item, seq, split, seq_len, b_start, b_end)) continue;
+      const int n_tok = (int)(min(seq_len, (int64_t)b_end * L.BS) - (int64_t)b_start * L.BS);
+      const int n_tiles = (n_tok + TILE - 1) / TILE;
+      // this head's queries -> fp16, pre-multiplied by softmax_scale * log2(e); rows >= gqa are zero
+      {
+        const int64_t q_row = A.q_rows ? A.q_rows[seq] : seq;
+        __syncwarp();
+        for (int i = lane; i < 8 * (D / 2); i += 32) {
+          const int d2 = i % (D / 2), n = i / (D / 2);
+          float x = 0.f, y = 0.f;
+          if (n < A.gqa) {
+            const int64_t e = q_row * A.q_s0 + (int64_t)(h * A.gqa + n) * A.q_s1 + 2 * d2;
+            x = ld_dt(A.q, A.q_dt, e) * A.scale_log2e;
+            y = ld_dt(A.q, A.q_dt, e + 1) * A.scale_log2e;
+          }
+          *reinterpret_cast<uint32_t*>(my_q + n * Q_ROW_BYTES + d2 * 4) = pack_h2(x, y);
+        }
+        __syncwarp();
       }
-      const int64_t o = ((int64_t)seq * A.Hq + hh * A.gqa + g) * A.num_splits + split;
-      A.acc[o * D + d] = a;
-      if (d == 0) { A.ml[o * 2] = mt; A.ml[o * 2 + 1] = lt; }
+      WarpState w;
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) { w.acc[mt][0] = w.acc[mt][1] = w.acc[mt][2] = w.acc[mt][3] = 0.f; }
+      w.bl[0] = w.bl[1] = w.bl[2] = w.bl[3] = 0.f;
+      w.m0 = w.m1 = -INFINITY;
+      w.bits = 0;
+      for (int t = 0; t < n_tiles; ++t, ++tile) {
+        const int st = tile % NS;
+        if (!mbar_wait(full + st, (tile / NS) & 1)) { ok = false; break; }
+        const StageInfo si = info[st];
+        TileView tv;
+        const uint32_t sb = smem_u32(ring + st * P.stage_bytes);
+        tv.rows = sb; tv.vs = sb + P.o_vs; tv.vm = sb + P.o_vm; tv.ks = sb + P.o_ks; tv.km = sb + P.o_km;
+        tv.side_bytes = (H * D * si.bits) / 8;
+        tv.head_bytes = (D * si.bits) / 8;
+        tv.row_stride = 2 * tv.side_bytes + 16;
+        if (si.n_valid > 0) {
+          if (si.bits == 4) process_tile<4>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
+          else if (si.bits == 8) process_tile<8>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
+          else process_tile<2>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + st);
+      }
+      if (w.bits == 4) write_partial<4>(P, w, seq, split, h, lane);
+      else if (w.bits == 8) write_partial<8>(P, w, seq, split, h, lane);
+      else write_partial<2>(P, w, seq, split, h, lane);
     }
   }
-  if (!ok && lane == 0 && P.status) atomicExch(P.status, 1);
+  if ((!ok || bad_tier) && lane == 0 && P.status) atomicExch(P.status, bad_tier ? 2 : 1);
 }
 
 }  // namespace mma
 
-// Chooses the tensor-core kernel when the shape fits; otherwise leaves `handled` false.
 static int g_decode_path = 0;  // 0: pick by shape, 1: always the generic kernel
 
+// Chooses the tensor-core kernel when the shape fits; otherwise leaves `handled` false.
 int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
-                      int64_t num_seqs, cudaStream_t st, bool* handled) {
+                      int64_t num_seqs, int max_tier, int* status, cudaStream_t st, bool* handled) {
   using namespace mma;
   *handled = false;
   if (g_decode_path == 1) return ECHOKV_OK;
@@ -673,45 +727,50 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   if (!(H == 1 || H == 2 || H == 4 || H == 8)) return ECHOKV_OK;
   if ((R.s_slot | R.s_pos | R.s_head) & 3) return ECHOKV_OK;                 // 8-byte residual loads
   if ((reinterpret_cast<uintptr_t>(R.base) & 15) != 0) return ECHOKV_OK;
+  if (num_seqs * (int64_t)A.num_splits > (1 << 30)) return ECHOKV_OK;
   Params P;
-  P.L = L; P.R = R; P.pages = pages; P.A = A; P.H = H;
-  P.TS = CONSUMER_WARPS / H;
-  // any tier can appear as soon as the pool has spare chunks (an INT8 block borrows 3 of them),
-  // so stages are sized for INT8 rows unless the pool is empty by construction (mem_bits 2)
+  P.L = L; P.R = R; P.pages = pages; P.A = A; P.H = H; P.num_seqs = (int)num_seqs;
+  // Any tier can appear as soon as the pool has spare chunks (an INT8 block borrows 3 of them), so
+  // stages are sized for INT8 rows unless the caller bounds the tiers present in this pool.
   P.max_bits = L.KC >= 2 ? 8 : 2;
+  if (max_tier == 2 || max_tier == 4 || max_tier == 8) P.max_bits = max_tier < P.max_bits ? max_tier : P.max_bits;
   const int row_stride = (2 * H * D * P.max_bits) / 8 + 16;
   P.o_vs = TILE * row_stride;
   P.o_vm = P.o_vs + TILE * H * NG * 2;
   P.o_ks = P.o_vm + TILE * H * NG * 2;
   P.o_km = P.o_ks + H * D * 2;
   P.stage_bytes = (P.o_km + H * D * 2 + 127) / 128 * 128;
-  P.status = nullptr;
+  P.status = status;
   const int fixed = 1024 + REMAP_BYTES + H * 8 * Q_ROW_BYTES;
-  const int staging = P.TS * H * (8 * REMAP_ROW + SET_EXTRA) * 4;
-  static int max_smem = -1;
+  static int max_smem = -1, num_sms = 0;
   if (max_smem < 0) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e != cudaSuccess) { max_smem = -1; return set_error(ECHOKV_E_CUDA, "decode: cannot raise shared memory: %s", cudaGetErrorString(e)); }
   }
-  int ns = (max_smem - fixed) / P.stage_bytes;
-  if (ns > MAX_STAGES) ns = MAX_STAGES;
-  if (ns > 2 * P.TS + 4) ns = 2 * P.TS + 4;
-  if (ns < P.TS + 1 || ns * P.stage_bytes < staging) {
-    ns = (staging + P.stage_bytes - 1) / P.stage_bytes;
-    if (ns < P.TS + 1) ns = P.TS + 1;
-    if (ns > MAX_STAGES || fixed + ns * P.stage_bytes > max_smem) return ECHOKV_OK;
+  // CTAs per SM: bounded by warps (16 consumer warps per SM is the target) and shared memory
+  // (each SM has ~228 KB, 1 KB of it reserved per CTA)
+  int per_sm = 16 / H;
+  if (per_sm < 2) per_sm = 2;
+  if (per_sm > 8) per_sm = 8;
+  int ns = 0;
+  for (; per_sm >= 1; --per_sm) {
+    const int budget = (max_smem + 1024) / per_sm - 1024;
+    ns = (budget - fixed) / P.stage_bytes;
+    if (ns > MAX_STAGES) ns = MAX_STAGES;
+    if (ns > 6) ns = 6;
+    if (ns >= 2) break;
   }
+  if (per_sm < 1 || ns < 2) return ECHOKV_OK;
   P.NS = ns;
   const int smem_bytes = fixed + ns * P.stage_bytes;
-  static int configured = 0;
-  if (configured < smem_bytes) {
-    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-    if (e != cudaSuccess) return set_error(ECHOKV_E_CUDA, "decode: cannot raise shared memory: %s", cudaGetErrorString(e));
-    configured = max_smem;
-  }
-  dim3 grid((unsigned)num_seqs, (unsigned)A.num_splits);
-  decode_mma_kernel<<<grid, THREADS, smem_bytes, st>>>(P);
+  int64_t grid = (int64_t)num_sms * per_sm;
+  const int64_t n_items = num_seqs * (int64_t)A.num_splits;
+  if (grid > n_items) grid = n_items;
+  decode_mma_kernel<<<(unsigned)grid, (H + 1) * 32, smem_bytes, st>>>(P);
   int rc = check_launch("decode (tensor-core kernel)");
   if (rc) return rc;
   *handled = true;

@@ -161,6 +161,8 @@ class GroupRunner:
         for i, pages in enumerate(caches):
             res = residuals[i] if residuals else torch.zeros(residual_slots + 1, g, h, d, dtype=model_dtype, device=dev)
             self.stores.append(TieredKVCache(layout, pages, residual=res, shared=self.shared))
+            if controllers[i].params.fixed_bits is not None:  # a pinned layer can never hold a higher tier
+                self.stores[-1].max_tier = controllers[i].params.fixed_bits
             self.krefs.append(krefs[i] if krefs else torch.zeros(kref_window, h, d, dtype=torch.float32, device=dev))
             self.stashes.append(stashes[i] if stashes else
                                 torch.zeros(canary_max_q, num_q_heads, d, dtype=model_dtype, device=dev))

@@ -214,7 +214,7 @@ class TieredKVCache:
 
         # ctypes descriptors, built once (the C ABI takes them by pointer)
         self._c_layout = L.native()
-        self._c_pages = N.Pages(pages.data_ptr(), pages.stride(0), n)
+        self._c_pages = N.Pages(pages.data_ptr(), pages.stride(0), n, 0, 0)
         self._c_res = N.Residual(residual.data_ptr(), N.dtype_code(residual.dtype), 0, residual.stride(0),
                                  residual.stride(1), residual.stride(2), self.block_res.data_ptr(),
                                  self.res_group.data_ptr())
@@ -223,6 +223,19 @@ class TieredKVCache:
         self._mark_h = np.zeros(n, dtype=np.int64)
         self._tok_tier = np.zeros(9, dtype=np.int64)
         self.reset_counters()
+
+    @property
+    def max_tier(self) -> int:
+        """Upper bound (2/4/8) the caller guarantees for the tier of every block of this layer, or 0.
+        The decode kernel sizes its shared-memory stages by it; a block above the bound is read as
+        empty, so only set it when the layer's tier cannot rise (e.g. a pinned tier)."""
+        return self._c_pages.max_tier
+
+    @max_tier.setter
+    def max_tier(self, bits: int) -> None:
+        if bits not in (0, 2, 4, 8):
+            raise ValueError("max_tier must be 0 (unknown), 2, 4 or 8")
+        self._c_pages.max_tier = bits
 
     # reference-compatible host mirrors
     @property

@@ -69,6 +69,9 @@ typedef struct echokv_pages {
   void* base;
   int64_t page_stride_bytes;
   int64_t num_blocks;
+  int32_t max_tier; /* upper bound of the tier of any block in this pool (2/4/8), 0 = unknown;
+                       lets the decode kernel size its shared-memory stages for narrower rows */
+  int32_t reserved;
 } echokv_pages;
 
 /* Residual buffer [slots + 1, k_group, H, D] in the model dtype
