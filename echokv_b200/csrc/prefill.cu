@@ -13,11 +13,4 @@ int echokv_prefill(const echokv_layout* layout, const echokv_pages* pages, const
   return set_error(ECHOKV_E_UNSUPPORTED, "prefill: not built yet");
 }
 
-int echokv_canary_kl(const void* query, int32_t q_dtype, int64_t q_sl, int64_t q_sq, int64_t q_sh, const float* kref,
-                     int64_t k_sl, int64_t k_sw, int64_t k_sh, int32_t ring_pos, int32_t ring_fill, int32_t window,
-                     int32_t num_layers, int32_t nq, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_size,
-                     int32_t k_group, float softmax_scale, float* out, void* stream) {
-  return set_error(ECHOKV_E_UNSUPPORTED, "canary_kl: not built yet");
-}
-
 }  // extern "C"
