@@ -177,6 +177,27 @@ template <> struct Unpack<2> {
   }
 };
 
+// Offset-carrying variants for INT8 / INT4: the fp16 values are OFF + code (OFF = 1024 for codes
+// that sit in mantissa bits 0..7, 64 for nibbles in bits 4..7) and the offsets are cancelled
+// exactly by a twin MMA whose A operand is the constant -OFF (products are exact in the fp32
+// accumulator), which is cheaper than one fp16 subtract per pair.
+constexpr uint32_t H2_N1024 = 0xe400e400u, H2_N64 = 0xd400d400u;
+__device__ __forceinline__ void raw8(uint32_t w, uint32_t (&o)[2]) {
+  o[0] = prmt(w, 0x64646464u, 0x4140u);
+  o[1] = prmt(w, 0x64646464u, 0x4342u);
+}
+__device__ __forceinline__ void raw8_t(uint32_t w, uint32_t (&o)[2]) {
+  o[0] = prmt(w, 0x64646464u, 0x4240u);
+  o[1] = prmt(w, 0x64646464u, 0x4341u);
+}
+__device__ __forceinline__ void raw4(uint32_t w, uint32_t (&o)[4]) {  // o[0], o[2]: 1024 + c; o[1], o[3]: 64 + c
+  o[0] = and_or<0x000f000fu, H2_1024>(w);
+  o[1] = and_or<0x00f000f0u, H2_64>(w);
+  const uint32_t v = w >> 8;
+  o[2] = and_or<0x000f000fu, H2_1024>(v);
+  o[3] = and_or<0x00f000f0u, H2_64>(v);
+}
+
 // Channel held by accumulator row (mt, r, half) for blocks of tier BITS.
 template <int BITS>
 __device__ __forceinline__ int acc_channel(int mt, int r, int half) {
@@ -228,21 +249,41 @@ __device__ __forceinline__ void store_any(const WarpState& w, float* buf, int r,
 
 // Everything a consumer warp needs to address one staged tile.
 struct TileView {
-  uint32_t rows;      // shared address of token row 0 ([K codes | V codes], stride row_stride)
-  uint32_t vs, vm;    // V scale / min of the tile: fp16 [16][H][NG]
-  uint32_t ks, km;    // K scale / min of the tile's group: fp16 [H][D]
-  int row_stride, side_bytes, head_bytes;
+  uint32_t krow, vrow;  // this lane's ldmatrix row address for the K side / V side of the staged rows
+  uint32_t vs, vm;      // this lane's V scale (tokens 2j.., all groups) / V min (group r) address
+  uint32_t ks, km;      // this head's K scale / min of the tile's group: fp16 [D]
+  uint32_t tok;         // bytes between consecutive tokens in the V stats
 };
+
+// Per-lane byte offsets that do not change from tile to tile (computed once per warp).
+struct LaneConst {
+  uint32_t k2, k4, k8, v2, v4, v8;  // per tier: offset of this lane's ldmatrix row on the K / V side
+  uint32_t vs_off, vm_off, ksm_off, tok;
+};
+__device__ __forceinline__ LaneConst lane_const(int H, int h, int lane) {
+  LaneConst c;
+  const int r = lane >> 2, j = lane & 3, mi = lane >> 3;
+  // row stride = [K codes | V codes] of all heads + 16 bytes of padding = 32 * H * bits + 16
+  const uint32_t row = (lane & 7) + 8 * (mi & 1), piece = (mi >> 1) * 16u;
+  c.k2 = row * (64u * H + 16u) + h * 32u + piece;   c.v2 = c.k2 + 32u * H;
+  c.k4 = row * (128u * H + 16u) + h * 64u + piece;  c.v4 = c.k4 + 64u * H;
+  c.k8 = row * (256u * H + 16u) + h * 128u + piece; c.v8 = c.k8 + 128u * H;
+  c.tok = (uint32_t)H * NG * 2;
+  c.vs_off = (uint32_t)((2 * j) * H + h) * NG * 2;
+  c.vm_off = c.vs_off + (uint32_t)r * 2;
+  c.ksm_off = (uint32_t)h * D * 2;
+  return c;
+}
 
 // ---- Q.K^T for one tile: scores c[4] = S^T[token r / r+8][query head 2j / 2j+1] (log2 domain) -----
 template <int BITS>
-__device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t q_lane, int h, int lane, float (&c)[4]) {
+__device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t q_lane, int lane, float (&c)[4]) {
   const int j = lane & 3;
-  const uint32_t ks = tv.ks + h * D * 2, km = tv.km + h * D * 2;
+  const uint32_t ks = tv.ks, km = tv.km;
   // ldmatrix row address of this lane: matrix (lane / 8): token (lane % 8) + 8 * (matrix & 1), piece + (matrix >> 1)
-  const int mi = lane >> 3;
-  const uint32_t krow = tv.rows + ((lane & 7) + 8 * (mi & 1)) * tv.row_stride + h * tv.head_bytes + (mi >> 1) * 16;
+  const uint32_t krow = tv.krow;
   if constexpr (BITS == 8) {
+    float c2[4] = {0.f, 0.f, 0.f, 0.f};  // second accumulator: halves the dependent MMA chain
 #pragma unroll
     for (int i = 0; i < 4; ++i) {  // pieces 2i, 2i+1 (16 channels each)
       uint32_t R[4];
@@ -255,14 +296,19 @@ __device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t q_lane, in
         asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(qw.x), "=r"(qw.y) : "r"(q_lane + off));
         asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(sw.x), "=r"(sw.y) : "r"(ks + off));
         asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(mw.x), "=r"(mw.y) : "r"(km + off));
-        mma16816(c, mw.x, mw.x, mw.y, mw.y, qw.x, qw.y);
+        const uint32_t z0 = hmul2u(qw.x, sw.x), z1 = hmul2u(qw.y, sw.y);
+        mma16816(c2, mw.x, mw.x, mw.y, mw.y, qw.x, qw.y);
+        mma16816(c2, H2_N1024, H2_N1024, H2_N1024, H2_N1024, z0, z1);
         uint32_t a[2], b[2];
-        Unpack<8>::run(R[2 * e], a);
-        Unpack<8>::run(R[2 * e + 1], b);
-        mma16816(c, a[0], b[0], a[1], b[1], hmul2u(qw.x, sw.x), hmul2u(qw.y, sw.y));
+        raw8(R[2 * e], a);
+        raw8(R[2 * e + 1], b);
+        mma16816(c, a[0], b[0], a[1], b[1], z0, z1);
       }
     }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) c[k] += c2[k];
   } else if constexpr (BITS == 4) {
+    float c2[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 2; ++i) {  // pieces 2i, 2i+1 (32 channels each)
       uint32_t R[4];
@@ -275,17 +321,23 @@ __device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t q_lane, in
         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(W[0]), "=r"(W[1]), "=r"(W[2]), "=r"(W[3]) : "r"(q_lane + off));
         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(S[0]), "=r"(S[1]), "=r"(S[2]), "=r"(S[3]) : "r"(ks + off));
         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(M[0]), "=r"(M[1]), "=r"(M[2]), "=r"(M[3]) : "r"(km + off));
-        mma16816(c, M[0], M[0], M[1], M[1], W[0], W[1]);
-        mma16816(c, M[2], M[2], M[3], M[3], W[2], W[3]);
+        mma16816(c2, M[0], M[0], M[1], M[1], W[0], W[1]);
+        mma16816(c2, M[2], M[2], M[3], M[3], W[2], W[3]);
 #pragma unroll
         for (int k = 0; k < 4; ++k) Z[k] = hmul2u(W[k], S[k]);
+        const uint32_t l0 = prmt(Z[0], Z[2], 0x5410u), h0 = prmt(Z[0], Z[2], 0x7632u);
+        const uint32_t l1 = prmt(Z[1], Z[3], 0x5410u), h1 = prmt(Z[1], Z[3], 0x7632u);
         uint32_t a[4], b[4];
-        Unpack<4>::run(R[2 * e], a);
-        Unpack<4>::run(R[2 * e + 1], b);
-        mma16816(c, a[0], b[0], a[1], b[1], prmt(Z[0], Z[2], 0x5410u), prmt(Z[0], Z[2], 0x7632u));
-        mma16816(c, a[2], b[2], a[3], b[3], prmt(Z[1], Z[3], 0x5410u), prmt(Z[1], Z[3], 0x7632u));
+        raw4(R[2 * e], a);
+        raw4(R[2 * e + 1], b);
+        mma16816(c, a[0], b[0], a[1], b[1], l0, h0);
+        mma16816(c2, H2_N1024, H2_N1024, H2_N64, H2_N64, l0, h0);
+        mma16816(c, a[2], b[2], a[3], b[3], l1, h1);
+        mma16816(c2, H2_N1024, H2_N1024, H2_N64, H2_N64, l1, h1);
       }
     }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) c[k] += c2[k];
   } else {
     uint32_t R[4];
     ldsm_x4(R, krow);  // pieces 0, 1 (64 channels each)
@@ -348,15 +400,13 @@ __device__ __forceinline__ void qk_residual(const ResidualDev& R, const StageInf
 // ---- P.V for one tile --------------------------------------------------------------------------
 // pb0 / pb1: B fragments of P (tokens 2j,2j+1 / 2j+8,2j+9 of query head n = lane / 4), fp16.
 template <int BITS>
-__device__ __forceinline__ void pv_codes(const TileView& tv, int H, int h, int lane, uint32_t pb0, uint32_t pb1,
-                                         WarpState& w) {
-  const int r = lane >> 2, j = lane & 3;
+__device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t pb0, uint32_t pb1, WarpState& w) {
+  const int r = lane >> 2;
   // V scale of this lane's four tokens, all NG groups: vs2lo[G] = {vs[2j][G], vs[2j+1][G]}, vs2hi[G] likewise +8
   uint32_t vlo[NG], vhi[NG];
   {
     uint2 t0, t1, t2, t3;
-    const uint32_t base = tv.vs + (uint32_t)((2 * j) * H + h) * NG * 2;
-    const uint32_t tok = (uint32_t)H * NG * 2;
+    const uint32_t base = tv.vs, tok = tv.tok;
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t0.x), "=r"(t0.y) : "r"(base));
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t1.x), "=r"(t1.y) : "r"(base + tok));
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t2.x), "=r"(t2.y) : "r"(base + 8 * tok));
@@ -366,8 +416,7 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int H, int h, int l
     vhi[0] = prmt(t2.x, t3.x, 0x5410u); vhi[1] = prmt(t2.x, t3.x, 0x7632u);
     vhi[2] = prmt(t2.y, t3.y, 0x5410u); vhi[3] = prmt(t2.y, t3.y, 0x7632u);
   }
-  const int mi = lane >> 3;
-  const uint32_t vrow = tv.rows + ((lane & 7) + 8 * (mi & 1)) * tv.row_stride + tv.side_bytes + h * tv.head_bytes + (mi >> 1) * 16;
+  const uint32_t vrow = tv.vrow;
   if constexpr (BITS == 8) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {  // pieces 2i, 2i+1 = the two halves of V group i
@@ -377,9 +426,10 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int H, int h, int l
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         uint32_t lo[2], hi[2];
-        Unpack<8>::run_t(Q[2 * e], lo);
-        Unpack<8>::run_t(Q[2 * e + 1], hi);
+        raw8_t(Q[2 * e], lo);
+        raw8_t(Q[2 * e + 1], hi);
         mma16816(w.acc[2 * i + e], lo[0], lo[1], hi[0], hi[1], b0, b1);
+        mma16816(w.acc[2 * i + e], H2_N1024, H2_N1024, H2_N1024, H2_N1024, b0, b1);
       }
     }
   } else if constexpr (BITS == 4) {
@@ -392,10 +442,12 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int H, int h, int l
         const int G = 2 * i + e;
         const uint32_t b0 = hmul2u(pb0, vlo[G]), b1 = hmul2u(pb1, vhi[G]);
         uint32_t lo[4], hi[4];
-        Unpack<4>::run(Q[2 * e], lo);
-        Unpack<4>::run(Q[2 * e + 1], hi);
+        raw4(Q[2 * e], lo);
+        raw4(Q[2 * e + 1], hi);
         mma16816(w.acc[2 * G], lo[0], lo[1], hi[0], hi[1], b0, b1);
         mma16816(w.acc[2 * G + 1], lo[2], lo[3], hi[2], hi[3], b0, b1);
+        mma16816(w.acc[2 * G], H2_N1024, H2_N64, H2_N1024, H2_N64, b0, b1);
+        mma16816(w.acc[2 * G + 1], H2_N1024, H2_N64, H2_N1024, H2_N64, b0, b1);
       }
     }
   } else {
@@ -438,7 +490,7 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
   // scores
   float c[4] = {0.f, 0.f, 0.f, 0.f};
   if (si.in_res) qk_residual(P.R, si, q_lane, h, lane, c);
-  else qk_codes<BITS>(tv, q_lane, h, lane, c);
+  else qk_codes<BITS>(tv, q_lane, lane, c);
   if (r >= si.n_valid) { c[0] = -INFINITY; c[1] = -INFINITY; }
   if (r + 8 >= si.n_valid) { c[2] = -INFINITY; c[3] = -INFINITY; }
   // online softmax over tokens (rows); columns 2j, 2j+1 belong to this lane
@@ -464,7 +516,7 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
   {
     uint32_t a0 = 0u, a2 = 0u;
     if (r < NG) {
-      const uint32_t base = tv.vm + (uint32_t)(((2 * j) * P.H + h) * NG + r) * 2, tok = (uint32_t)P.H * NG * 2;
+      const uint32_t base = tv.vm, tok = tv.tok;
       uint32_t x0, x1, x2, x3;
       asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x0) : "r"(base));
       asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x1) : "r"(base + tok));
@@ -475,7 +527,7 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
     }
     mma16816(w.bl, a0, H2_ONE, a2, H2_ONE, pb0, pb1);
   }
-  pv_codes<BITS>(tv, P.H, h, lane, pb0, pb1, w);
+  pv_codes<BITS>(tv, lane, pb0, pb1, w);
 }
 
 // ---- the kernel ------------------------------------------------------------------------------
@@ -658,6 +710,7 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
     const int r = lane >> 2;
     unsigned char* my_q = qs + h * 8 * Q_ROW_BYTES;
     const uint32_t q_lane = smem_u32(my_q + r * Q_ROW_BYTES);
+    const LaneConst lc = lane_const(H, h, lane);
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       int seq, split, b_start, b_end;
       int64_t seq_len;
@@ -692,10 +745,10 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
         const StageInfo si = info[st];
         TileView tv;
         const uint32_t sb = smem_u32(ring + st * P.stage_bytes);
-        tv.rows = sb; tv.vs = sb + P.o_vs; tv.vm = sb + P.o_vm; tv.ks = sb + P.o_ks; tv.km = sb + P.o_km;
-        tv.side_bytes = (H * D * si.bits) / 8;
-        tv.head_bytes = (D * si.bits) / 8;
-        tv.row_stride = 2 * tv.side_bytes + 16;
+        tv.krow = sb + (si.bits == 8 ? lc.k8 : (si.bits == 4 ? lc.k4 : lc.k2));
+        tv.vrow = sb + (si.bits == 8 ? lc.v8 : (si.bits == 4 ? lc.v4 : lc.v2));
+        tv.vs = sb + P.o_vs + lc.vs_off; tv.vm = sb + P.o_vm + lc.vm_off;
+        tv.ks = sb + P.o_ks + lc.ksm_off; tv.km = sb + P.o_km + lc.ksm_off; tv.tok = lc.tok;
         if (si.n_valid > 0) {
           if (si.bits == 4) process_tile<4>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
           else if (si.bits == 8) process_tile<8>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
