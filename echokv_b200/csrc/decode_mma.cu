@@ -79,6 +79,9 @@ __device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t b
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -611,7 +614,7 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
   unsigned char* ring = qs + H * 8 * Q_ROW_BYTES;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < NS; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, H); }
+    for (int s = 0; s < NS; ++s) { mbar_init(full + s, 33); mbar_init(empty + s, H); }
     *lock = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -678,28 +681,51 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
           if (lane == 0) {
             info[st].bits = bits; info[st].n_valid = too_wide ? 0 : n_valid; info[st].in_res = in_res ? 1 : 0;
             info[st].pos0 = t0 % L.KG; info[st].res_slot = ks_slot;
-            const uint32_t bytes = (too_wide ? 0 : n_valid * row_bytes) + 2 * (TILE * H * NG * 2) + (in_res ? 0 : 2 * H * D * 2);
-            mbar_expect_tx(full + st, bytes);
           }
-          __syncwarp();
-          if (lane < n_valid) {
-            if (!too_wide) {
-              const int tok = t0 + lane;
-              const int jc = tok / tpc;
+          // token rows: 16-byte asynchronous copies, each row to its padded slot.  A tile's tokens lie
+          // in at most 4 source runs (one per chunk the tile touches).
+          if (!too_wide) {
+            const int ppr = row_bytes >> 4;  // 16-byte pieces per row (a power of two)
+            const int first_chunk = t0 / tpc;
+            const unsigned char* run[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int jc = first_chunk + q;
               int64_t pg = kblk, slot = 0;
               if (jc > 0) { const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3); pg = id / L.KC; slot = id % L.KC; }
-              const unsigned char* src = P.pages + pg * L.PS + L.o_data + slot * L.CB + (int64_t)(tok % tpc) * row_bytes;
-              bulk_copy(sb + lane * (row_bytes + 16), src, row_bytes, full + st);
+              run[q] = P.pages + pg * L.PS + L.o_data + slot * L.CB;
             }
-          } else if (lane == 16) {
-            bulk_copy(sb + P.o_vs, page + L.o_vs + (int64_t)t0 * H * NG * 2, TILE * H * NG * 2, full + st);
-          } else if (lane == 17) {
-            bulk_copy(sb + P.o_vm, page + L.o_vm + (int64_t)t0 * H * NG * 2, TILE * H * NG * 2, full + st);
-          } else if (lane == 18 && !in_res) {
-            bulk_copy(sb + P.o_ks, page + L.o_ks + (int64_t)grp * H * D * 2, H * D * 2, full + st);
-          } else if (lane == 19 && !in_res) {
-            bulk_copy(sb + P.o_km, page + L.o_km + (int64_t)grp * H * D * 2, H * D * 2, full + st);
+            const uint32_t dst0 = smem_u32(sb);
+            for (int t = 0; t < n_valid; ++t) {
+              const int tok = t0 + t;
+              const int q = tok / tpc - first_chunk;
+              const unsigned char* src = (q == 0 ? run[0] : (q == 1 ? run[1] : (q == 2 ? run[2] : run[3]))) +
+                                         (int64_t)(tok % tpc) * row_bytes;
+              const uint32_t dst = dst0 + t * (row_bytes + 16);
+              for (int o = lane; o < ppr; o += 32) cp_async16(dst + o * 16, src + o * 16);
+            }
           }
+          {  // V stats of the tile, K stats of its group
+            const int nv = (TILE * H * NG * 2) >> 4, nk = (H * D * 2) >> 4;
+            const unsigned char* vsrc = page + L.o_vs + (int64_t)t0 * H * NG * 2;
+            const unsigned char* msrc = page + L.o_vm + (int64_t)t0 * H * NG * 2;
+            for (int i = lane; i < nv; i += 32) {
+              cp_async16(smem_u32(sb + P.o_vs) + i * 16, vsrc + i * 16);
+              cp_async16(smem_u32(sb + P.o_vm) + i * 16, msrc + i * 16);
+            }
+            if (!in_res) {
+              const unsigned char* ssrc = page + L.o_ks + (int64_t)grp * H * D * 2;
+              const unsigned char* nsrc = page + L.o_km + (int64_t)grp * H * D * 2;
+              for (int i = lane; i < nk; i += 32) {
+                cp_async16(smem_u32(sb + P.o_ks) + i * 16, ssrc + i * 16);
+                cp_async16(smem_u32(sb + P.o_km) + i * 16, nsrc + i * 16);
+              }
+            }
+          }
+          // the stage is full once every lane's copies have landed (32 asynchronous arrivals) and
+          // lane 0 has published the tile's description (1 ordinary arrival)
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(full + st)) : "memory");
+          if (lane == 0) mbar_arrive(full + st);
           __syncwarp();
         }
       }
