@@ -39,6 +39,15 @@ struct StageInfo {
   long long res_slot;
 };
 
+// One published tile: what to copy and how to read it.
+struct TileDesc {
+  int bits, n_valid, in_res, pos0;   // n_valid: 1..16 tokens, 0 = skip (tier above the bound), -1 = end of work
+  long long res_slot;
+  const unsigned char *vs_src, *vm_src, *ks_src, *km_src;
+  const unsigned char* row_src[TILE];
+};
+constexpr int ND = 16;  // descriptor ring slots
+
 struct Params {
   LayoutDev L;
   ResidualDev R;
@@ -536,7 +545,16 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
 // ---- the kernel ------------------------------------------------------------------------------
 // Persistent: CTA c walks the work items c, c + gridDim.x, ... in split-major order (item =
 // split * num_seqs + seq), so neighbouring CTAs work on different sequences of similar length and
-// the short tail splits come last.  One producer warp + H consumer warps (one per KV head).
+// the short tail splits come last.  H consumer warps (one per KV head) + one descriptor warp.
+//
+// The descriptor warp runs ahead of the consumers: it resolves block table -> page header ->
+// chunk ids -> residual map for up to 32 blocks at a time (the dependent global loads of the next
+// batch are in flight while the current one is consumed) and publishes one TileDesc per 16-token
+// tile in a small ring.  The consumers stream the data themselves: all their threads issue
+// 16-byte cp.async copies for tile t + NS - 1 into the stage ring (token rows padded by 16 bytes
+// so ldmatrix over 8 rows is conflict free) and then compute tile t, with one named barrier per
+// tile.  Spreading the copies over every warp keeps enough loads in flight; a single issuing
+// warp (or one bulk-copy request per token row) could not.
 __device__ __forceinline__ bool item_range(const Params& P, int item, int& seq, int& split, int64_t& seq_len,
                                            int& b_start, int& b_end) {
   seq = item % P.num_seqs;
@@ -545,7 +563,7 @@ __device__ __forceinline__ bool item_range(const Params& P, int item, int& seq, 
   return split_range(seq_len, P.L.BS, P.A.num_splits, P.A.bps_min, split, b_start, b_end);
 }
 
-// Block metadata the producer prefetches for up to 32 blocks at a time (one block per lane).
+// Block metadata the descriptor warp prefetches for up to 32 blocks at a time (one block per lane).
 struct BlockMeta {
   int blk, bits, c1, c2, c3, rgrp;
   long long rslot;
@@ -595,48 +613,69 @@ __device__ __forceinline__ void write_partial(const Params& P, const WarpState& 
   }
 }
 
+// Named barrier 1 over the consumer threads that also ORs a per-thread flag: every thread learns
+// whether any of them gave up on a wait, so they all leave the pipeline at the same point.
+__device__ __forceinline__ bool bar_or(int nthreads, bool flag) {
+  uint32_t any;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, 1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(any) : "r"((uint32_t)flag), "r"(nthreads) : "memory");
+  return any != 0;
+}
+
+__device__ __forceinline__ void cp_wait(int pending) {  // wait until at most `pending` groups are in flight
+  switch (pending) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+  }
+}
+
 __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
   extern __shared__ __align__(128) unsigned char smem[];
   const LayoutDev& L = P.L;
   const DecodeArgs& A = P.A;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int H = P.H, NS = P.NS;
-  const int nthreads = (H + 1) * 32;
+  const int n_cons = H * 32;
   const int n_items = P.num_seqs * A.num_splits;
 
-  // shared memory: [barriers | stage info | lock][remap][q (fp16, per head)][ring]
+  // shared memory: [barriers | lock][descriptors][remap][q (fp16, per head)][stage ring]
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  uint64_t* empty = full + MAX_STAGES;
-  StageInfo* info = reinterpret_cast<StageInfo*>(empty + MAX_STAGES);
-  int* lock = reinterpret_cast<int*>(info + MAX_STAGES);
-  float* remap = reinterpret_cast<float*>(smem + 1024);
-  unsigned char* qs = smem + 1024 + REMAP_BYTES;
+  uint64_t* empty = full + ND;
+  int* lock = reinterpret_cast<int*>(empty + ND);
+  TileDesc* desc = reinterpret_cast<TileDesc*>(smem + 512);
+  float* remap = reinterpret_cast<float*>(smem + 512 + ND * sizeof(TileDesc));
+  unsigned char* qs = reinterpret_cast<unsigned char*>(remap) + REMAP_BYTES;
   unsigned char* ring = qs + H * 8 * Q_ROW_BYTES;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < NS; ++s) { mbar_init(full + s, 33); mbar_init(empty + s, H); }
+    for (int s = 0; s < ND; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, H); }
     *lock = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   {  // zero the ring once: rows of a partial tile that are never copied must read as finite numbers
     const int n16 = (NS * P.stage_bytes) / 16;
     uint4* z = reinterpret_cast<uint4*>(ring);
-    for (int i = threadIdx.x; i < n16; i += nthreads) z[i] = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < n16; i += (H + 1) * 32) z[i] = make_uint4(0, 0, 0, 0);
   }
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncthreads();
 
   bool ok = true, bad_tier = false;
-  int tile = 0;  // tiles issued / consumed by this CTA so far (both sides count identically)
   if (warp == H) {
-    // ===================== producer =====================
+    // ===================== descriptor warp =====================
     const int tiles_per_block = L.BS / TILE;
-    // software pipeline over "units" (an item's next <= 32 blocks): the next unit's metadata is
-    // requested before the current unit's tiles are issued, so its latency hides behind them
+    int tile = 0;
     int item = blockIdx.x, seq = 0, split = 0, b_start = 0, b_end = 0, base = 0;
     int64_t seq_len = 0, bt_row = 0;
     bool have = false;
-    auto advance = [&]() {  // move (item, base) to the next unit; false when the CTA is out of work
+    auto advance = [&]() {  // move (item, base) to the next unit of <= 32 blocks; false when out of work
       if (have && base + 32 < b_end) { base += 32; return true; }
       if (have) item += gridDim.x;
       for (; item < n_items; item += gridDim.x) {
@@ -646,6 +685,10 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
         }
       }
       return false;
+    };
+    auto claim = [&](int t) {  // wait until the consumers have released descriptor slot t % ND
+      if (t >= ND && !mbar_wait(empty + (t % ND), ((t / ND) - 1) & 1)) ok = false;
+      return ok;
     };
     bool more = advance();
     BlockMeta nxt = more ? load_meta(P, bt_row, base + lane, b_end) : BlockMeta{};
@@ -664,80 +707,88 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
         const long long ks_slot = __shfl_sync(0xffffffffu, cur.rslot, k);
         const int kgrp = __shfl_sync(0xffffffffu, cur.rgrp, k);
         if (bits != 2 && bits != 4 && bits != 8) bits = 2;  // never opened: stay inside the page
-        bool too_wide = bits > P.max_bits;                   // the host's tier bound was wrong
-        if (too_wide) { bits = P.max_bits; bad_tier = true; }  // tiles are issued empty; status reports it
+        const bool too_wide = bits > P.max_bits;             // the caller's tier bound was wrong
+        if (too_wide) { bits = P.max_bits; bad_tier = true; }  // such tiles are published empty
         const int blk_tok = (int)min((int64_t)L.BS, u_len - (int64_t)(u_base + k) * L.BS);
         const int row_bytes = (2 * H * D * bits) / 8;
         const int tpc = (2 * L.BS) / bits;
         const unsigned char* page = P.pages + (int64_t)kblk * L.PS;
         for (int tb = 0; tb < tiles_per_block && tb * TILE < blk_tok; ++tb, ++tile) {
-          const int st = tile % NS;
-          if (tile >= NS && !mbar_wait(empty + st, ((tile / NS) - 1) & 1)) { ok = false; break; }
+          if (!claim(tile)) break;
+          TileDesc& d = desc[tile % ND];
           const int t0 = tb * TILE;
-          const int n_valid = min(TILE, blk_tok - t0);
           const int grp = t0 / L.KG;
           const bool in_res = ks_slot >= 0 && grp == kgrp;
-          unsigned char* sb = ring + st * P.stage_bytes;
-          if (lane == 0) {
-            info[st].bits = bits; info[st].n_valid = too_wide ? 0 : n_valid; info[st].in_res = in_res ? 1 : 0;
-            info[st].pos0 = t0 % L.KG; info[st].res_slot = ks_slot;
+          if (lane < TILE) {  // where token t0 + lane lives
+            const int tok = t0 + lane;
+            const int jc = tok / tpc;
+            int64_t pg = kblk, slot = 0;
+            if (jc > 0) { const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3); pg = id / L.KC; slot = id % L.KC; }
+            d.row_src[lane] = P.pages + pg * L.PS + L.o_data + slot * L.CB + (int64_t)(tok % tpc) * row_bytes;
+          } else if (lane == 16) {
+            d.bits = bits; d.n_valid = too_wide ? 0 : min(TILE, blk_tok - t0); d.in_res = in_res ? 1 : 0;
+            d.pos0 = t0 % L.KG; d.res_slot = ks_slot;
+          } else if (lane == 17) {
+            d.vs_src = page + L.o_vs + (int64_t)t0 * H * NG * 2;
+            d.vm_src = page + L.o_vm + (int64_t)t0 * H * NG * 2;
+            d.ks_src = page + L.o_ks + (int64_t)grp * H * D * 2;
+            d.km_src = page + L.o_km + (int64_t)grp * H * D * 2;
           }
-          // token rows: 16-byte asynchronous copies, each row to its padded slot.  A tile's tokens lie
-          // in at most 4 source runs (one per chunk the tile touches).
-          if (!too_wide) {
-            const int ppr = row_bytes >> 4;  // 16-byte pieces per row (a power of two)
-            const int first_chunk = t0 / tpc;
-            const unsigned char* run[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int jc = first_chunk + q;
-              int64_t pg = kblk, slot = 0;
-              if (jc > 0) { const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3); pg = id / L.KC; slot = id % L.KC; }
-              run[q] = P.pages + pg * L.PS + L.o_data + slot * L.CB;
-            }
-            const uint32_t dst0 = smem_u32(sb);
-            for (int t = 0; t < n_valid; ++t) {
-              const int tok = t0 + t;
-              const int q = tok / tpc - first_chunk;
-              const unsigned char* src = (q == 0 ? run[0] : (q == 1 ? run[1] : (q == 2 ? run[2] : run[3]))) +
-                                         (int64_t)(tok % tpc) * row_bytes;
-              const uint32_t dst = dst0 + t * (row_bytes + 16);
-              for (int o = lane; o < ppr; o += 32) cp_async16(dst + o * 16, src + o * 16);
-            }
-          }
-          {  // V stats of the tile, K stats of its group
-            const int nv = (TILE * H * NG * 2) >> 4, nk = (H * D * 2) >> 4;
-            const unsigned char* vsrc = page + L.o_vs + (int64_t)t0 * H * NG * 2;
-            const unsigned char* msrc = page + L.o_vm + (int64_t)t0 * H * NG * 2;
-            for (int i = lane; i < nv; i += 32) {
-              cp_async16(smem_u32(sb + P.o_vs) + i * 16, vsrc + i * 16);
-              cp_async16(smem_u32(sb + P.o_vm) + i * 16, msrc + i * 16);
-            }
-            if (!in_res) {
-              const unsigned char* ssrc = page + L.o_ks + (int64_t)grp * H * D * 2;
-              const unsigned char* nsrc = page + L.o_km + (int64_t)grp * H * D * 2;
-              for (int i = lane; i < nk; i += 32) {
-                cp_async16(smem_u32(sb + P.o_ks) + i * 16, ssrc + i * 16);
-                cp_async16(smem_u32(sb + P.o_km) + i * 16, nsrc + i * 16);
-              }
-            }
-          }
-          // the stage is full once every lane's copies have landed (32 asynchronous arrivals) and
-          // lane 0 has published the tile's description (1 ordinary arrival)
-          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(full + st)) : "memory");
-          if (lane == 0) mbar_arrive(full + st);
           __syncwarp();
+          if (lane == 0) mbar_arrive(full + (tile % ND));
         }
       }
+    }
+    if (ok && claim(tile)) {  // terminal descriptor: no more tiles for this CTA
+      if (lane == 0) { desc[tile % ND].n_valid = -1; mbar_arrive(full + (tile % ND)); }
     }
   } else {
     // ===================== consumers: warp h owns KV head h =====================
     const int h = warp;
     const int r = lane >> 2;
+    const int tid = threadIdx.x;  // 0 .. n_cons - 1
     unsigned char* my_q = qs + h * 8 * Q_ROW_BYTES;
     const uint32_t q_lane = smem_u32(my_q + r * Q_ROW_BYTES);
     const LaneConst lc = lane_const(H, h, lane);
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    const uint32_t ring_u = smem_u32(ring);
+    bool ended = false;
+    int issued = 0;  // tiles whose copies this thread has issued (a copy group is committed per tile)
+    // Issue this thread's share of the copies of tile `x` into stage x % NS (or an empty group past the end).
+    auto issue = [&](int x) {
+      if (!ended && ok) {
+        const int ds = x % ND;
+        if (!mbar_wait(full + ds, (x / ND) & 1)) ok = false;
+        const TileDesc& d = desc[ds];
+        if (ok && d.n_valid < 0) ended = true;
+        if (ok && !ended) {
+          const uint32_t sb = ring_u + (x % NS) * P.stage_bytes;
+          const int row_bytes = 32 * H * d.bits;
+          const int sh = 31 - __clz(row_bytes >> 4);  // log2(16-byte pieces per row)
+          const int n_row = d.n_valid << sh;
+          for (int i = tid; i < n_row; i += n_cons) {
+            const int t = i >> sh, o = i & ((1 << sh) - 1);
+            cp_async16(sb + t * (row_bytes + 16) + o * 16, d.row_src[t] + o * 16);
+          }
+          const int nv = (TILE * H * NG * 2) >> 4, nk = (H * D * 2) >> 4;
+          for (int i = tid; i < nv; i += n_cons) {
+            cp_async16(sb + P.o_vs + i * 16, d.vs_src + i * 16);
+            cp_async16(sb + P.o_vm + i * 16, d.vm_src + i * 16);
+          }
+          if (!d.in_res) {
+            for (int i = tid; i < nk; i += n_cons) {
+              cp_async16(sb + P.o_ks + i * 16, d.ks_src + i * 16);
+              cp_async16(sb + P.o_km + i * 16, d.km_src + i * 16);
+            }
+          }
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      ++issued;
+    };
+    for (int x = 0; x < NS - 1; ++x) issue(x);  // prologue: NS - 1 tiles in flight
+    int tile = 0;
+    bool stop = false;  // uniform over the consumer threads (decided at the per-tile barrier)
+    for (int item = blockIdx.x; item < n_items && !stop; item += gridDim.x) {
       int seq, split, b_start, b_end;
       int64_t seq_len;
       if (!item_range(P, item, seq, split, seq_len, b_start, b_end)) continue;
@@ -766,11 +817,15 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
       w.m0 = w.m1 = -INFINITY;
       w.bits = 0;
       for (int t = 0; t < n_tiles; ++t, ++tile) {
-        const int st = tile % NS;
-        if (!mbar_wait(full + st, (tile / NS) & 1)) { ok = false; break; }
-        const StageInfo si = info[st];
+        cp_wait(NS - 2);                                   // this thread's copies of `tile` have landed
+        stop = bar_or(n_cons, !ok);                        // ... and everyone's; all warps are done with tile - 1
+        if (stop) break;
+        issue(tile + NS - 1);                              // refill the stage tile - 1 used
+        const TileDesc& d = desc[tile % ND];
+        StageInfo si;
+        si.bits = d.bits; si.n_valid = d.n_valid; si.in_res = d.in_res; si.pos0 = d.pos0; si.res_slot = d.res_slot;
         TileView tv;
-        const uint32_t sb = smem_u32(ring + st * P.stage_bytes);
+        const uint32_t sb = ring_u + (tile % NS) * P.stage_bytes;
         tv.krow = sb + (si.bits == 8 ? lc.k8 : (si.bits == 4 ? lc.k4 : lc.k2));
         tv.vrow = sb + (si.bits == 8 ? lc.v8 : (si.bits == 4 ? lc.v4 : lc.v2));
         tv.vs = sb + P.o_vs + lc.vs_off; tv.vm = sb + P.o_vm + lc.vm_off;
@@ -781,12 +836,14 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
           else process_tile<2>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty + st);
+        if (lane == 0) mbar_arrive(empty + (tile % ND));
       }
+      if (stop) break;
       if (w.bits == 4) write_partial<4>(P, w, seq, split, h, lane);
       else if (w.bits == 8) write_partial<8>(P, w, seq, split, h, lane);
       else write_partial<2>(P, w, seq, split, h, lane);
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
   if ((!ok || bad_tier) && lane == 0 && P.status) atomicExch(P.status, bad_tier ? 2 : 1);
 }
@@ -820,7 +877,7 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   P.o_km = P.o_ks + H * D * 2;
   P.stage_bytes = (P.o_km + H * D * 2 + 127) / 128 * 128;
   P.status = status;
-  const int fixed = 1024 + REMAP_BYTES + H * 8 * Q_ROW_BYTES;
+  const int fixed = 512 + ND * (int)sizeof(TileDesc) + REMAP_BYTES + H * 8 * Q_ROW_BYTES;
   static int max_smem = -1, num_sms = 0;
   if (max_smem < 0) {
     int dev = 0;
@@ -839,7 +896,6 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   for (; per_sm >= 1; --per_sm) {
     const int budget = (max_smem + 1024) / per_sm - 1024;
     ns = (budget - fixed) / P.stage_bytes;
-    if (ns > MAX_STAGES) ns = MAX_STAGES;
     if (ns > 6) ns = 6;
     if (ns >= 2) break;
   }
