@@ -220,7 +220,9 @@ __device__ __forceinline__ int acc_channel(int mt, int r, int half) {
 
 // Shared-memory geometry of the query block: [H][8 query rows][D] fp16, rows padded by 64 bytes so
 // that the 128-bit fragment loads of two neighbouring rows fall into different bank halves.
-constexpr int Q_ROW_BYTES = D * 2 + 64;
+constexpr int QT_ROW = D * 2 + 64;   // tier copy: rows padded so 128-bit fragment loads of two rows hit different bank halves
+constexpr int QN_ROW = D * 2 + 16;   // natural copy: rows padded for ldmatrix over the 8 query rows
+constexpr int Q_HEAD_BYTES = 8 * (QT_ROW + QN_ROW);
 constexpr int REMAP_ROW = D + 4;                      // floats per query head in the canonical layout
 constexpr int REMAP_BYTES = 8 * REMAP_ROW * 4;
 
@@ -229,17 +231,27 @@ struct WarpState {
   float bl[4];      // [0],[1]: sum_t p * v_min for V group r (lanes r < NG); [2],[3]: sum_t p
   float m0, m1;     // running max (log2 domain) of query heads 2j and 2j+1
   int bits;         // tier whose channel order `acc` is in (0: none yet)
+  int qbits;        // tier the warp's scaled query copy was built for (0: none yet)
 };
+
+// The PV accumulators of INT8 / INT4 blocks hold code units: rows fed by in-place subnormal codes
+// are 2^-24 of the true value (2^-20 for the rows fed by upper nibbles: `half` 1 at INT4).
+template <int BITS>
+__device__ __forceinline__ float acc_unit(int half) {
+  if constexpr (BITS == 8) return 16777216.f;
+  else if constexpr (BITS == 4) return half ? 1048576.f : 16777216.f;
+  else return 1.f;
+}
 
 template <int BITS>
 __device__ __forceinline__ void store_canonical(const WarpState& w, float* buf, int r, int j) {
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) {
     const int c0 = acc_channel<BITS>(mt, r, 0), c1 = acc_channel<BITS>(mt, r, 1);
-    buf[(2 * j) * REMAP_ROW + c0] = w.acc[mt][0];
-    buf[(2 * j + 1) * REMAP_ROW + c0] = w.acc[mt][1];
-    buf[(2 * j) * REMAP_ROW + c1] = w.acc[mt][2];
-    buf[(2 * j + 1) * REMAP_ROW + c1] = w.acc[mt][3];
+    buf[(2 * j) * REMAP_ROW + c0] = w.acc[mt][0] * acc_unit<BITS>(0);
+    buf[(2 * j + 1) * REMAP_ROW + c0] = w.acc[mt][1] * acc_unit<BITS>(0);
+    buf[(2 * j) * REMAP_ROW + c1] = w.acc[mt][2] * acc_unit<BITS>(1);
+    buf[(2 * j + 1) * REMAP_ROW + c1] = w.acc[mt][3] * acc_unit<BITS>(1);
   }
 }
 template <int BITS>
@@ -247,10 +259,10 @@ __device__ __forceinline__ void load_canonical(WarpState& w, const float* buf, i
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) {
     const int c0 = acc_channel<BITS>(mt, r, 0), c1 = acc_channel<BITS>(mt, r, 1);
-    w.acc[mt][0] = buf[(2 * j) * REMAP_ROW + c0];
-    w.acc[mt][1] = buf[(2 * j + 1) * REMAP_ROW + c0];
-    w.acc[mt][2] = buf[(2 * j) * REMAP_ROW + c1];
-    w.acc[mt][3] = buf[(2 * j + 1) * REMAP_ROW + c1];
+    w.acc[mt][0] = buf[(2 * j) * REMAP_ROW + c0] * (1.f / acc_unit<BITS>(0));
+    w.acc[mt][1] = buf[(2 * j + 1) * REMAP_ROW + c0] * (1.f / acc_unit<BITS>(0));
+    w.acc[mt][2] = buf[(2 * j) * REMAP_ROW + c1] * (1.f / acc_unit<BITS>(1));
+    w.acc[mt][3] = buf[(2 * j + 1) * REMAP_ROW + c1] * (1.f / acc_unit<BITS>(1));
   }
 }
 __device__ __forceinline__ void store_any(const WarpState& w, float* buf, int r, int j) {
@@ -288,14 +300,57 @@ __device__ __forceinline__ LaneConst lane_const(int H, int h, int lane) {
 }
 
 // ---- Q.K^T for one tile: scores c[4] = S^T[token r / r+8][query head 2j / 2j+1] (log2 domain) -----
+//
+// INT8 / INT4 codes enter the tensor cores as fp16 SUBNORMALS: a code byte or nibble masked in
+// place inside a zero 16-bit lane is the number code * 2^-24 (nibbles at bits 4..7: code * 2^-20),
+// exactly, with no conversion instruction at all.  The 2^-4 of the upper nibbles is pre-applied to
+// the odd channels of the tier's query copy, and the 2^24 is applied once to the fp32 scores.
+// INT2 keeps the magic-number path (its four crumb positions would need four query scalings and
+// its V path multiplies codes by scales in fp16, which subnormals cannot take).
+constexpr float CODE_UNSCALE = 16777216.f;  // 2^24
+
+__device__ __forceinline__ void sub4(uint32_t w, uint32_t (&o)[4]) {  // INT4 word -> 4 subnormal pairs
+  o[0] = w & 0x000f000fu;
+  o[1] = w & 0x00f000f0u;
+  const uint32_t v = w >> 8;
+  o[2] = v & 0x000f000fu;
+  o[3] = v & 0x00f000f0u;
+}
+__device__ __forceinline__ void sub8(uint32_t w, uint32_t (&o)[2]) {  // INT8 word -> pairs (0,1) (2,3)
+  o[0] = prmt(w, 0u, 0x4140u);
+  o[1] = prmt(w, 0u, 0x4342u);
+}
+__device__ __forceinline__ void sub8_t(uint32_t w, uint32_t (&o)[2]) {  // [a.c0 a.c1 | b.c0 b.c1] -> (a.c0,b.c0) (a.c1,b.c1)
+  o[0] = prmt(w, 0u, 0x4240u);
+  o[1] = prmt(w, 0u, 0x4341u);
+}
+
+// Constant term of the scores, sum_d q[g, d] * k_min[d]: 8 MMA k-steps whose A fragments are the
+// group's k_min row broadcast to all 16 token rows (ldmatrix with every row address equal) and
+// whose B fragments are the natural-order query (ldmatrix over the 8 query rows).
+__device__ __forceinline__ void km_term(uint32_t km, uint32_t qn_ld, int lane, float (&c2)[4]) {
+  const uint32_t km_ld = km + (lane < 16 ? 0u : 16u);
+#pragma unroll
+  for (int k2 = 0; k2 < 4; ++k2) {
+    uint32_t B[4];
+    ldsm_x4(B, qn_ld + k2 * 64);
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+      uint32_t A[4];
+      ldsm_x4(A, km_ld + (2 * k2 + kk) * 32);
+      mma16816(c2, A[0], A[1], A[2], A[3], B[2 * kk], B[2 * kk + 1]);
+    }
+  }
+}
+
 template <int BITS>
-__device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t q_lane, int lane, float (&c)[4]) {
+__device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t qt_lane, uint32_t qn_ld, int lane, float (&c)[4]) {
   const int j = lane & 3;
-  const uint32_t ks = tv.ks, km = tv.km;
-  // ldmatrix row address of this lane: matrix (lane / 8): token (lane % 8) + 8 * (matrix & 1), piece + (matrix >> 1)
+  const uint32_t ks = tv.ks;
   const uint32_t krow = tv.krow;
+  float c2[4] = {0.f, 0.f, 0.f, 0.f};
+  km_term(tv.km, qn_ld, lane, c2);
   if constexpr (BITS == 8) {
-    float c2[4] = {0.f, 0.f, 0.f, 0.f};  // second accumulator: halves the dependent MMA chain
 #pragma unroll
     for (int i = 0; i < 4; ++i) {  // pieces 2i, 2i+1 (16 channels each)
       uint32_t R[4];
@@ -304,23 +359,18 @@ __device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t q_lane, in
       for (int e = 0; e < 2; ++e) {
         const int p = 2 * i + e;
         const uint32_t off = (16 * p + 4 * j) * 2;
-        uint2 qw, sw, mw;
-        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(qw.x), "=r"(qw.y) : "r"(q_lane + off));
+        uint2 qw, sw;
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(qw.x), "=r"(qw.y) : "r"(qt_lane + off));
         asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(sw.x), "=r"(sw.y) : "r"(ks + off));
-        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(mw.x), "=r"(mw.y) : "r"(km + off));
-        const uint32_t z0 = hmul2u(qw.x, sw.x), z1 = hmul2u(qw.y, sw.y);
-        mma16816(c2, mw.x, mw.x, mw.y, mw.y, qw.x, qw.y);
-        mma16816(c2, H2_N1024, H2_N1024, H2_N1024, H2_N1024, z0, z1);
         uint32_t a[2], b[2];
-        raw8(R[2 * e], a);
-        raw8(R[2 * e + 1], b);
-        mma16816(c, a[0], b[0], a[1], b[1], z0, z1);
+        sub8(R[2 * e], a);
+        sub8(R[2 * e + 1], b);
+        mma16816(c, a[0], b[0], a[1], b[1], hmul2u(qw.x, sw.x), hmul2u(qw.y, sw.y));
       }
     }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) c[k] += c2[k];
+    for (int k = 0; k < 4; ++k) c[k] = fmaf(c[k], CODE_UNSCALE, c2[k]);
   } else if constexpr (BITS == 4) {
-    float c2[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 2; ++i) {  // pieces 2i, 2i+1 (32 channels each)
       uint32_t R[4];
@@ -329,42 +379,32 @@ __device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t q_lane, in
       for (int e = 0; e < 2; ++e) {
         const int p = 2 * i + e;
         const uint32_t off = (32 * p + 8 * j) * 2;
-        uint32_t W[4], S[4], M[4], Z[4];
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(W[0]), "=r"(W[1]), "=r"(W[2]), "=r"(W[3]) : "r"(q_lane + off));
+        uint32_t W[4], S[4], Z[4];
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(W[0]), "=r"(W[1]), "=r"(W[2]), "=r"(W[3]) : "r"(qt_lane + off));
         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(S[0]), "=r"(S[1]), "=r"(S[2]), "=r"(S[3]) : "r"(ks + off));
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(M[0]), "=r"(M[1]), "=r"(M[2]), "=r"(M[3]) : "r"(km + off));
-        mma16816(c2, M[0], M[0], M[1], M[1], W[0], W[1]);
-        mma16816(c2, M[2], M[2], M[3], M[3], W[2], W[3]);
 #pragma unroll
         for (int k = 0; k < 4; ++k) Z[k] = hmul2u(W[k], S[k]);
-        const uint32_t l0 = prmt(Z[0], Z[2], 0x5410u), h0 = prmt(Z[0], Z[2], 0x7632u);
-        const uint32_t l1 = prmt(Z[1], Z[3], 0x5410u), h1 = prmt(Z[1], Z[3], 0x7632u);
         uint32_t a[4], b[4];
-        raw4(R[2 * e], a);
-        raw4(R[2 * e + 1], b);
-        mma16816(c, a[0], b[0], a[1], b[1], l0, h0);
-        mma16816(c2, H2_N1024, H2_N1024, H2_N64, H2_N64, l0, h0);
-        mma16816(c, a[2], b[2], a[3], b[3], l1, h1);
-        mma16816(c2, H2_N1024, H2_N1024, H2_N64, H2_N64, l1, h1);
+        sub4(R[2 * e], a);
+        sub4(R[2 * e + 1], b);
+        mma16816(c, a[0], b[0], a[1], b[1], prmt(Z[0], Z[2], 0x5410u), prmt(Z[0], Z[2], 0x7632u));
+        mma16816(c, a[2], b[2], a[3], b[3], prmt(Z[1], Z[3], 0x5410u), prmt(Z[1], Z[3], 0x7632u));
       }
     }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) c[k] += c2[k];
+    for (int k = 0; k < 4; ++k) c[k] = fmaf(c[k], CODE_UNSCALE, c2[k]);
   } else {
     uint32_t R[4];
     ldsm_x4(R, krow);  // pieces 0, 1 (64 channels each)
 #pragma unroll
     for (int p = 0; p < 2; ++p) {
       const uint32_t off = (64 * p + 16 * j) * 2;
-      uint32_t W[8], S[8], M[8], Z[8];
+      uint32_t W[8], S[8], Z[8];
 #pragma unroll
       for (int v = 0; v < 2; ++v) {
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(W[4 * v]), "=r"(W[4 * v + 1]), "=r"(W[4 * v + 2]), "=r"(W[4 * v + 3]) : "r"(q_lane + off + 16 * v));
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(W[4 * v]), "=r"(W[4 * v + 1]), "=r"(W[4 * v + 2]), "=r"(W[4 * v + 3]) : "r"(qt_lane + off + 16 * v));
         asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(S[4 * v]), "=r"(S[4 * v + 1]), "=r"(S[4 * v + 2]), "=r"(S[4 * v + 3]) : "r"(ks + off + 16 * v));
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(M[4 * v]), "=r"(M[4 * v + 1]), "=r"(M[4 * v + 2]), "=r"(M[4 * v + 3]) : "r"(km + off + 16 * v));
       }
-#pragma unroll
-      for (int k = 0; k < 4; ++k) mma16816(c, M[2 * k], M[2 * k], M[2 * k + 1], M[2 * k + 1], W[2 * k], W[2 * k + 1]);
 #pragma unroll
       for (int k = 0; k < 8; ++k) Z[k] = hmul2u(W[k], S[k]);
       uint32_t a[8], b[8];
@@ -374,6 +414,8 @@ __device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t q_lane, in
       for (int k = 0; k < 4; ++k)
         mma16816(c, a[2 * k], b[2 * k], a[2 * k + 1], b[2 * k + 1], prmt(Z[k], Z[k + 4], 0x5410u), prmt(Z[k], Z[k + 4], 0x7632u));
     }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) c[k] += c2[k];
   }
 }
 
@@ -392,7 +434,7 @@ __device__ __forceinline__ uint32_t res_pair(const ResidualDev& R, int64_t e) {
   }
   return pack_h2(x, y);
 }
-__device__ __forceinline__ void qk_residual(const ResidualDev& R, const StageInfo& si, uint32_t q_lane, int h, int lane,
+__device__ __forceinline__ void qk_residual(const ResidualDev& R, const StageInfo& si, uint32_t qn_lane, int h, int lane,
                                             float (&c)[4]) {
   const int r = lane >> 2, j = lane & 3;
   const bool v0 = r < si.n_valid, v1 = r + 8 < si.n_valid;
@@ -402,7 +444,7 @@ __device__ __forceinline__ void qk_residual(const ResidualDev& R, const StageInf
   for (int p = 0; p < 8; ++p) {
     const int ch = 16 * p + 4 * j;
     uint2 qw;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(qw.x), "=r"(qw.y) : "r"(q_lane + ch * 2));
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(qw.x), "=r"(qw.y) : "r"(qn_lane + ch * 2));
     const uint32_t a0 = v0 ? res_pair(R, e0 + ch) : 0u, a2 = v0 ? res_pair(R, e0 + ch + 2) : 0u;
     const uint32_t a1 = v1 ? res_pair(R, e1 + ch) : 0u, a3 = v1 ? res_pair(R, e1 + ch + 2) : 0u;
     mma16816(c, a0, a1, a2, a3, qw.x, qw.y);
@@ -438,10 +480,9 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t 
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         uint32_t lo[2], hi[2];
-        raw8_t(Q[2 * e], lo);
-        raw8_t(Q[2 * e + 1], hi);
+        sub8_t(Q[2 * e], lo);
+        sub8_t(Q[2 * e + 1], hi);
         mma16816(w.acc[2 * i + e], lo[0], lo[1], hi[0], hi[1], b0, b1);
-        mma16816(w.acc[2 * i + e], H2_N1024, H2_N1024, H2_N1024, H2_N1024, b0, b1);
       }
     }
   } else if constexpr (BITS == 4) {
@@ -454,12 +495,10 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t 
         const int G = 2 * i + e;
         const uint32_t b0 = hmul2u(pb0, vlo[G]), b1 = hmul2u(pb1, vhi[G]);
         uint32_t lo[4], hi[4];
-        raw4(Q[2 * e], lo);
-        raw4(Q[2 * e + 1], hi);
+        sub4(Q[2 * e], lo);
+        sub4(Q[2 * e + 1], hi);
         mma16816(w.acc[2 * G], lo[0], lo[1], hi[0], hi[1], b0, b1);
         mma16816(w.acc[2 * G + 1], lo[2], lo[3], hi[2], hi[3], b0, b1);
-        mma16816(w.acc[2 * G], H2_N1024, H2_N64, H2_N1024, H2_N64, b0, b1);
-        mma16816(w.acc[2 * G + 1], H2_N1024, H2_N64, H2_N1024, H2_N64, b0, b1);
       }
     }
   } else {
@@ -479,10 +518,28 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t 
   }
 }
 
+// A warp's two query copies in shared memory (see QT_ROW / QN_ROW).
+struct QView {
+  unsigned char *qn, *qt;      // natural copy [8][QN_ROW], tier-scaled copy [8][QT_ROW]
+  uint32_t qt_lane, qn_lane;   // shared address of this lane's query row (row lane / 4) in each copy
+  uint32_t qn_ld;              // this lane's ldmatrix row address in the natural copy
+};
+
 template <int BITS>
-__device__ __forceinline__ void process_tile(const Params& P, const TileView& tv, const StageInfo& si, uint32_t q_lane,
+__device__ __forceinline__ void process_tile(const Params& P, const TileView& tv, const StageInfo& si, const QView& qv,
                                              int h, int lane, WarpState& w, float* remap, int* lock, bool& ok) {
   const int r = lane >> 2, j = lane & 3;
+  if (w.qbits != BITS) {  // (re)build the tier's query copy: INT4 needs its odd channels scaled by 2^-4
+    __syncwarp();
+    for (int i = lane; i < 8 * (D / 2); i += 32) {
+      const int n = i / (D / 2), wd = i % (D / 2);
+      uint32_t v = *reinterpret_cast<const uint32_t*>(qv.qn + n * QN_ROW + wd * 4);
+      if constexpr (BITS == 4) v = hmul2u(v, 0x2c003c00u);  // (1, 2^-4)
+      *reinterpret_cast<uint32_t*>(qv.qt + n * QT_ROW + wd * 4) = v;
+    }
+    __syncwarp();
+    w.qbits = BITS;
+  }
   if (w.bits != BITS) {
     if (w.bits != 0) {  // re-map the accumulators to this tier's channel order (rare: tier changes)
       if (lane == 0) {
@@ -501,8 +558,8 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
   }
   // scores
   float c[4] = {0.f, 0.f, 0.f, 0.f};
-  if (si.in_res) qk_residual(P.R, si, q_lane, h, lane, c);
-  else qk_codes<BITS>(tv, q_lane, lane, c);
+  if (si.in_res) qk_residual(P.R, si, qv.qn_lane, h, lane, c);
+  else qk_codes<BITS>(tv, qv.qt_lane, qv.qn_ld, lane, c);
   if (r >= si.n_valid) { c[0] = -INFINITY; c[1] = -INFINITY; }
   if (r + 8 >= si.n_valid) { c[2] = -INFINITY; c[3] = -INFINITY; }
   // online softmax over tokens (rows); columns 2j, 2j+1 belong to this lane
@@ -599,12 +656,12 @@ __device__ __forceinline__ void write_partial(const Params& P, const WarpState& 
     const float bias1 = __shfl_sync(0xffffffffu, w.bl[1], G * 4 + j);
     const int c0 = acc_channel<BITS>(mt, r, 0), c1 = acc_channel<BITS>(mt, r, 1);
     if (g0 < A.gqa) {
-      A.acc[o0 * D + c0] = w.acc[mt][0] + bias0;
-      A.acc[o0 * D + c1] = w.acc[mt][2] + bias0;
+      A.acc[o0 * D + c0] = fmaf(w.acc[mt][0], acc_unit<BITS>(0), bias0);
+      A.acc[o0 * D + c1] = fmaf(w.acc[mt][2], acc_unit<BITS>(1), bias0);
     }
     if (g1 < A.gqa) {
-      A.acc[o1 * D + c0] = w.acc[mt][1] + bias1;
-      A.acc[o1 * D + c1] = w.acc[mt][3] + bias1;
+      A.acc[o1 * D + c0] = fmaf(w.acc[mt][1], acc_unit<BITS>(0), bias1);
+      A.acc[o1 * D + c1] = fmaf(w.acc[mt][3], acc_unit<BITS>(1), bias1);
     }
   }
   if (r == 0) {
@@ -653,7 +710,7 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
   TileDesc* desc = reinterpret_cast<TileDesc*>(smem + 512);
   float* remap = reinterpret_cast<float*>(smem + 512 + ND * sizeof(TileDesc));
   unsigned char* qs = reinterpret_cast<unsigned char*>(remap) + REMAP_BYTES;
-  unsigned char* ring = qs + H * 8 * Q_ROW_BYTES;
+  unsigned char* ring = qs + H * Q_HEAD_BYTES;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < ND; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, H); }
@@ -747,8 +804,12 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
     const int h = warp;
     const int r = lane >> 2;
     const int tid = threadIdx.x;  // 0 .. n_cons - 1
-    unsigned char* my_q = qs + h * 8 * Q_ROW_BYTES;
-    const uint32_t q_lane = smem_u32(my_q + r * Q_ROW_BYTES);
+    QView qv;
+    qv.qn = qs + h * Q_HEAD_BYTES;
+    qv.qt = qv.qn + 8 * QN_ROW;
+    qv.qt_lane = smem_u32(qv.qt + r * QT_ROW);
+    qv.qn_lane = smem_u32(qv.qn + r * QN_ROW);
+    qv.qn_ld = smem_u32(qv.qn + (lane & 7) * QN_ROW + (lane >> 3) * 16);
     const LaneConst lc = lane_const(H, h, lane);
     const uint32_t ring_u = smem_u32(ring);
     bool ended = false;
@@ -806,7 +867,7 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
             x = ld_dt(A.q, A.q_dt, e) * A.scale_log2e;
             y = ld_dt(A.q, A.q_dt, e + 1) * A.scale_log2e;
           }
-          *reinterpret_cast<uint32_t*>(my_q + n * Q_ROW_BYTES + d2 * 4) = pack_h2(x, y);
+          *reinterpret_cast<uint32_t*>(qv.qn + n * QN_ROW + d2 * 4) = pack_h2(x, y);
         }
         __syncwarp();
       }
@@ -816,6 +877,7 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
       w.bl[0] = w.bl[1] = w.bl[2] = w.bl[3] = 0.f;
       w.m0 = w.m1 = -INFINITY;
       w.bits = 0;
+      w.qbits = 0;
       for (int t = 0; t < n_tiles; ++t, ++tile) {
         cp_wait(NS - 2);                                   // this thread's copies of `tile` have landed
         stop = bar_or(n_cons, !ok);                        // ... and everyone's; all warps are done with tile - 1
@@ -831,9 +893,9 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
         tv.vs = sb + P.o_vs + lc.vs_off; tv.vm = sb + P.o_vm + lc.vm_off;
         tv.ks = sb + P.o_ks + lc.ksm_off; tv.km = sb + P.o_km + lc.ksm_off; tv.tok = lc.tok;
         if (si.n_valid > 0) {
-          if (si.bits == 4) process_tile<4>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
-          else if (si.bits == 8) process_tile<8>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
-          else process_tile<2>(P, tv, si, q_lane, h, lane, w, remap, lock, ok);
+          if (si.bits == 4) process_tile<4>(P, tv, si, qv, h, lane, w, remap, lock, ok);
+          else if (si.bits == 8) process_tile<8>(P, tv, si, qv, h, lane, w, remap, lock, ok);
+          else process_tile<2>(P, tv, si, qv, h, lane, w, remap, lock, ok);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty + (tile % ND));
@@ -877,7 +939,7 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   P.o_km = P.o_ks + H * D * 2;
   P.stage_bytes = (P.o_km + H * D * 2 + 127) / 128 * 128;
   P.status = status;
-  const int fixed = 512 + ND * (int)sizeof(TileDesc) + REMAP_BYTES + H * 8 * Q_ROW_BYTES;
+  const int fixed = 512 + ND * (int)sizeof(TileDesc) + REMAP_BYTES + H * Q_HEAD_BYTES;
   static int max_smem = -1, num_sms = 0;
   if (max_smem < 0) {
     int dev = 0;
