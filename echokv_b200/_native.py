@@ -87,6 +87,9 @@ for _name, _args in _SIGS.items():
 lib.echokv_set_decode_path.argtypes = [C.c_int]
 lib.echokv_set_decode_path.restype = C.c_int
 
+if os.environ.get("ECHOKV_B200_DECODE_PATH"):  # experiments: see echokv_set_decode_path
+    lib.echokv_set_decode_path(int(os.environ["ECHOKV_B200_DECODE_PATH"], 0))
+
 EXPORTS = sorted(list(_SIGS) + ["echokv_set_decode_path", "echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
                                 "echokv_demote_scratch_bytes"])
 

@@ -56,6 +56,7 @@ struct Params {
   int H, NS, max_bits, num_seqs;
   int stage_bytes, o_vs, o_vm, o_ks, o_km;  // stage layout (bytes from the stage base)
   int* status;                             // device status word (0 ok), may be null
+  int debug;                               // experiments only: 1 skip the math, 2 skip the copies
 };
 
 // ---- PTX helpers ---------------------------------------------------------------------------
@@ -694,16 +695,17 @@ __device__ __forceinline__ void cp_wait(int pending) {  // wait until at most `p
   }
 }
 
-__global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
+template <int H>
+__global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H == 2 ? 5 : 8))) decode_mma_kernel(const Params P) {
   extern __shared__ __align__(128) unsigned char smem[];
   const LayoutDev& L = P.L;
   const DecodeArgs& A = P.A;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int H = P.H, NS = P.NS;
-  const int n_cons = H * 32;
+  const int NS = P.NS;
+  constexpr int N_CONS = H * 32;
   const int n_items = P.num_seqs * A.num_splits;
 
-  // shared memory: [barriers | lock][descriptors][remap][q (fp16, per head)][stage ring]
+  // shared memory: [barriers | lock][descriptors][remap][q copies per head][stage ring]
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + ND;
   int* lock = reinterpret_cast<int*>(empty + ND);
@@ -767,7 +769,7 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
         const bool too_wide = bits > P.max_bits;             // the caller's tier bound was wrong
         if (too_wide) { bits = P.max_bits; bad_tier = true; }  // such tiles are published empty
         const int blk_tok = (int)min((int64_t)L.BS, u_len - (int64_t)(u_base + k) * L.BS);
-        const int row_bytes = (2 * H * D * bits) / 8;
+        const int row_bytes = 32 * H * bits;
         const int tpc = (2 * L.BS) / bits;
         const unsigned char* page = P.pages + (int64_t)kblk * L.PS;
         for (int tb = 0; tb < tiles_per_block && tb * TILE < blk_tok; ++tb, ++tile) {
@@ -783,7 +785,9 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
             if (jc > 0) { const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3); pg = id / L.KC; slot = id % L.KC; }
             d.row_src[lane] = P.pages + pg * L.PS + L.o_data + slot * L.CB + (int64_t)(tok % tpc) * row_bytes;
           } else if (lane == 16) {
-            d.bits = bits; d.n_valid = too_wide ? 0 : min(TILE, blk_tok - t0); d.in_res = in_res ? 1 : 0;
+            // in_res bit 1: the tile's four stats arrays form one contiguous run (tile = whole 16-token block)
+            const bool contig = L.BS == TILE && L.KG == TILE;
+            d.bits = bits; d.n_valid = too_wide ? 0 : min(TILE, blk_tok - t0); d.in_res = (in_res ? 1 : 0) | (contig ? 2 : 0);
             d.pos0 = t0 % L.KG; d.res_slot = ks_slot;
           } else if (lane == 17) {
             d.vs_src = page + L.o_vs + (int64_t)t0 * H * NG * 2;
@@ -803,7 +807,7 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
     // ===================== consumers: warp h owns KV head h =====================
     const int h = warp;
     const int r = lane >> 2;
-    const int tid = threadIdx.x;  // 0 .. n_cons - 1
+    const int tid = threadIdx.x;  // 0 .. N_CONS - 1
     QView qv;
     qv.qn = qs + h * Q_HEAD_BYTES;
     qv.qt = qv.qn + 8 * QN_ROW;
@@ -812,42 +816,56 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
     qv.qn_ld = smem_u32(qv.qn + (lane & 7) * QN_ROW + (lane >> 3) * 16);
     const LaneConst lc = lane_const(H, h, lane);
     const uint32_t ring_u = smem_u32(ring);
+    const uint32_t stage_bytes = P.stage_bytes;
+    const uint32_t stats_off = P.o_vs;  // [vs | vm | ks | km] are contiguous in a stage
+    constexpr int STAT16 = (2 * TILE * H * NG * 2 + 2 * H * D * 2) / 16;  // 16-byte pieces of a tile's stats
+    constexpr int TOK_PER_WARP = TILE / H > 0 ? TILE / H : 1;
     bool ended = false;
-    int issued = 0;  // tiles whose copies this thread has issued (a copy group is committed per tile)
-    // Issue this thread's share of the copies of tile `x` into stage x % NS (or an empty group past the end).
-    auto issue = [&](int x) {
+    // issue side of the stage pipeline: slot counters advance without divisions
+    int is_st = 0, is_ds = 0, is_par = 0;   // stage / descriptor slot / descriptor parity of the next tile to issue
+    uint32_t is_sb = ring_u;
+    // Issue this thread's share of the copies of the next tile (or an empty group past the end).
+    auto issue = [&]() {
       if (!ended && ok) {
-        const int ds = x % ND;
-        if (!mbar_wait(full + ds, (x / ND) & 1)) ok = false;
-        const TileDesc& d = desc[ds];
-        if (ok && d.n_valid < 0) ended = true;
-        if (ok && !ended) {
-          const uint32_t sb = ring_u + (x % NS) * P.stage_bytes;
-          const int row_bytes = 32 * H * d.bits;
-          const int sh = 31 - __clz(row_bytes >> 4);  // log2(16-byte pieces per row)
-          const int n_row = d.n_valid << sh;
-          for (int i = tid; i < n_row; i += n_cons) {
-            const int t = i >> sh, o = i & ((1 << sh) - 1);
-            cp_async16(sb + t * (row_bytes + 16) + o * 16, d.row_src[t] + o * 16);
+        if (!mbar_wait(full + is_ds, is_par)) ok = false;
+        const TileDesc& d = desc[is_ds];
+        const int4 hd = *reinterpret_cast<const int4*>(&d);  // bits, n_valid, in_res, pos0
+        if (ok && hd.y < 0) ended = true;
+        if (ok && !ended && P.debug != 2) {
+          const uint32_t row_bytes = 32u * H * hd.x;
+          // token rows: warp h copies tokens h, h + H, ... (each row to its padded slot)
+#pragma unroll
+          for (int k = 0; k < TOK_PER_WARP; ++k) {
+            const int t = h + k * H;
+            if (t < hd.y) {
+              const unsigned char* src = d.row_src[t] + lane * 16;
+              const uint32_t dst = is_sb + t * (row_bytes + 16) + lane * 16;
+              for (uint32_t o = lane * 16; o < row_bytes; o += 512) cp_async16(dst + (o - lane * 16), src + (o - lane * 16));
+            }
           }
-          const int nv = (TILE * H * NG * 2) >> 4, nk = (H * D * 2) >> 4;
-          for (int i = tid; i < nv; i += n_cons) {
-            cp_async16(sb + P.o_vs + i * 16, d.vs_src + i * 16);
-            cp_async16(sb + P.o_vm + i * 16, d.vm_src + i * 16);
-          }
-          if (!d.in_res) {
-            for (int i = tid; i < nk; i += n_cons) {
-              cp_async16(sb + P.o_ks + i * 16, d.ks_src + i * 16);
-              cp_async16(sb + P.o_km + i * 16, d.km_src + i * 16);
+          // stats: when the tile is a whole block of 16 tokens the four arrays are one contiguous run
+          if (hd.z & 2) {
+            for (int i = tid; i < STAT16; i += N_CONS) cp_async16(is_sb + stats_off + i * 16, d.vs_src + i * 16);
+          } else {
+            constexpr int NV = (TILE * H * NG * 2) / 16, NK = (H * D * 2) / 16;
+            for (int i = tid; i < NV; i += N_CONS) {
+              cp_async16(is_sb + P.o_vs + i * 16, d.vs_src + i * 16);
+              cp_async16(is_sb + P.o_vm + i * 16, d.vm_src + i * 16);
+            }
+            for (int i = tid; i < NK; i += N_CONS) {
+              cp_async16(is_sb + P.o_ks + i * 16, d.ks_src + i * 16);
+              cp_async16(is_sb + P.o_km + i * 16, d.km_src + i * 16);
             }
           }
         }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
-      ++issued;
+      if (++is_st == NS) { is_st = 0; is_sb = ring_u; } else { is_sb += stage_bytes; }
+      if (++is_ds == ND) { is_ds = 0; is_par ^= 1; }
     };
-    for (int x = 0; x < NS - 1; ++x) issue(x);  // prologue: NS - 1 tiles in flight
-    int tile = 0;
+    for (int x = 0; x < NS - 1; ++x) issue();  // prologue: NS - 1 tiles in flight
+    int c_st = 0, c_ds = 0;                      // stage / descriptor slot of the tile being consumed
+    uint32_t c_sb = ring_u;
     bool stop = false;  // uniform over the consumer threads (decided at the per-tile barrier)
     for (int item = blockIdx.x; item < n_items && !stop; item += gridDim.x) {
       int seq, split, b_start, b_end;
@@ -878,27 +896,29 @@ __global__ void __launch_bounds__(9 * 32, 2) decode_mma_kernel(const Params P) {
       w.m0 = w.m1 = -INFINITY;
       w.bits = 0;
       w.qbits = 0;
-      for (int t = 0; t < n_tiles; ++t, ++tile) {
-        cp_wait(NS - 2);                                   // this thread's copies of `tile` have landed
-        stop = bar_or(n_cons, !ok);                        // ... and everyone's; all warps are done with tile - 1
+      for (int t = 0; t < n_tiles; ++t) {
+        cp_wait(NS - 2);                 // this thread's copies of the tile have landed
+        stop = bar_or(N_CONS, !ok);      // ... and everyone's; all warps are done with the previous tile
         if (stop) break;
-        issue(tile + NS - 1);                              // refill the stage tile - 1 used
-        const TileDesc& d = desc[tile % ND];
+        issue();                         // refill the stage the previous tile used
+        const TileDesc& d = desc[c_ds];
+        const int4 hd = *reinterpret_cast<const int4*>(&d);
         StageInfo si;
-        si.bits = d.bits; si.n_valid = d.n_valid; si.in_res = d.in_res; si.pos0 = d.pos0; si.res_slot = d.res_slot;
+        si.bits = hd.x; si.n_valid = hd.y; si.in_res = hd.z & 1; si.pos0 = hd.w; si.res_slot = d.res_slot;
         TileView tv;
-        const uint32_t sb = ring_u + (tile % NS) * P.stage_bytes;
-        tv.krow = sb + (si.bits == 8 ? lc.k8 : (si.bits == 4 ? lc.k4 : lc.k2));
-        tv.vrow = sb + (si.bits == 8 ? lc.v8 : (si.bits == 4 ? lc.v4 : lc.v2));
-        tv.vs = sb + P.o_vs + lc.vs_off; tv.vm = sb + P.o_vm + lc.vm_off;
-        tv.ks = sb + P.o_ks + lc.ksm_off; tv.km = sb + P.o_km + lc.ksm_off; tv.tok = lc.tok;
-        if (si.n_valid > 0) {
+        tv.krow = c_sb + (si.bits == 8 ? lc.k8 : (si.bits == 4 ? lc.k4 : lc.k2));
+        tv.vrow = c_sb + (si.bits == 8 ? lc.v8 : (si.bits == 4 ? lc.v4 : lc.v2));
+        tv.vs = c_sb + P.o_vs + lc.vs_off; tv.vm = c_sb + P.o_vm + lc.vm_off;
+        tv.ks = c_sb + P.o_ks + lc.ksm_off; tv.km = c_sb + P.o_km + lc.ksm_off; tv.tok = lc.tok;
+        if (si.n_valid > 0 && P.debug != 1) {
           if (si.bits == 4) process_tile<4>(P, tv, si, qv, h, lane, w, remap, lock, ok);
           else if (si.bits == 8) process_tile<8>(P, tv, si, qv, h, lane, w, remap, lock, ok);
           else process_tile<2>(P, tv, si, qv, h, lane, w, remap, lock, ok);
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty + (tile % ND));
+        if (lane == 0) mbar_arrive(empty + c_ds);
+        if (++c_st == NS) { c_st = 0; c_sb = ring_u; } else { c_sb += stage_bytes; }
+        if (++c_ds == ND) c_ds = 0;
       }
       if (stop) break;
       if (w.bits == 4) write_partial<4>(P, w, seq, split, h, lane);
@@ -919,7 +939,7 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
                       int64_t num_seqs, int max_tier, int* status, cudaStream_t st, bool* handled) {
   using namespace mma;
   *handled = false;
-  if (g_decode_path == 1) return ECHOKV_OK;
+  if ((g_decode_path & 15) == 1) return ECHOKV_OK;
   const int H = L.H;
   if (L.D != D || L.VG != 32 || L.KG % TILE || L.BS % TILE || A.gqa > 8) return ECHOKV_OK;
   if (!(H == 1 || H == 2 || H == 4 || H == 8)) return ECHOKV_OK;
@@ -939,6 +959,7 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   P.o_km = P.o_ks + H * D * 2;
   P.stage_bytes = (P.o_km + H * D * 2 + 127) / 128 * 128;
   P.status = status;
+  P.debug = (g_decode_path >> 4) & 15;
   const int fixed = 512 + ND * (int)sizeof(TileDesc) + REMAP_BYTES + H * Q_HEAD_BYTES;
   static int max_smem = -1, num_sms = 0;
   if (max_smem < 0) {
@@ -946,7 +967,10 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     if (e != cudaSuccess) { max_smem = -1; return set_error(ECHOKV_E_CUDA, "decode: cannot raise shared memory: %s", cudaGetErrorString(e)); }
   }
   // CTAs per SM: bounded by warps (16 consumer warps per SM is the target) and shared memory
@@ -962,12 +986,21 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
     if (ns >= 2) break;
   }
   if (per_sm < 1 || ns < 2) return ECHOKV_OK;
+  if ((g_decode_path >> 8) & 15) {  // experiments only: forced CTAs per SM / stage count
+    const int f_sm = (g_decode_path >> 8) & 15, f_ns = (g_decode_path >> 12) & 15;
+    if (fixed + f_ns * P.stage_bytes <= (max_smem + 1024) / f_sm - 1024) { per_sm = f_sm; ns = f_ns; }
+  }
   P.NS = ns;
   const int smem_bytes = fixed + ns * P.stage_bytes;
   int64_t grid = (int64_t)num_sms * per_sm;
   const int64_t n_items = num_seqs * (int64_t)A.num_splits;
   if (grid > n_items) grid = n_items;
-  decode_mma_kernel<<<(unsigned)grid, (H + 1) * 32, smem_bytes, st>>>(P);
+  switch (H) {
+    case 1: decode_mma_kernel<1><<<(unsigned)grid, 2 * 32, smem_bytes, st>>>(P); break;
+    case 2: decode_mma_kernel<2><<<(unsigned)grid, 3 * 32, smem_bytes, st>>>(P); break;
+    case 4: decode_mma_kernel<4><<<(unsigned)grid, 5 * 32, smem_bytes, st>>>(P); break;
+    default: decode_mma_kernel<8><<<(unsigned)grid, 9 * 32, smem_bytes, st>>>(P); break;
+  }
   int rc = check_launch("decode (tensor-core kernel)");
   if (rc) return rc;
   *handled = true;
