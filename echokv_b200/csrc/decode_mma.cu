@@ -40,13 +40,14 @@ struct StageInfo {
 };
 
 // One published tile: what to copy and how to read it.
-struct TileDesc {
+struct alignas(16) TileDesc {  // 16-byte aligned: the four leading ints are read with one 128-bit load
   int bits, n_valid, in_res, pos0;   // n_valid: 1..16 tokens, 0 = skip (tier above the bound), -1 = end of work
   long long res_slot;
   const unsigned char *vs_src, *vm_src, *ks_src, *km_src;
   const unsigned char* row_src[TILE];
 };
 constexpr int ND = 16;  // descriptor ring slots
+static_assert(sizeof(TileDesc) % 16 == 0, "descriptor slots must stay 16-byte aligned");
 
 struct Params {
   LayoutDev L;
