@@ -46,7 +46,9 @@ struct alignas(16) TileDesc {  // 16-byte aligned: the four leading ints are rea
   const unsigned char *vs_src, *vm_src, *ks_src, *km_src;
   const unsigned char* row_src[TILE];
 };
-constexpr int ND = 16;  // descriptor ring slots
+constexpr int ND = 32;  // descriptor ring slots (one per lane of the descriptor warp)
+constexpr int HDR_BYTES = 1024;  // 2 * ND mbarriers + the remap lock
+static_assert(2 * ND * 8 + 4 <= HDR_BYTES, "barriers and lock must fit the header");
 static_assert(sizeof(TileDesc) % 16 == 0, "descriptor slots must stay 16-byte aligned");
 
 struct Params {
@@ -710,8 +712,8 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + ND;
   int* lock = reinterpret_cast<int*>(empty + ND);
-  TileDesc* desc = reinterpret_cast<TileDesc*>(smem + 512);
-  float* remap = reinterpret_cast<float*>(smem + 512 + ND * sizeof(TileDesc));
+  TileDesc* desc = reinterpret_cast<TileDesc*>(smem + HDR_BYTES);
+  float* remap = reinterpret_cast<float*>(smem + HDR_BYTES + ND * sizeof(TileDesc));
   unsigned char* qs = reinterpret_cast<unsigned char*>(remap) + REMAP_BYTES;
   unsigned char* ring = qs + H * Q_HEAD_BYTES;
 
@@ -730,13 +732,17 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
   bool ok = true, bad_tier = false;
   if (warp == H) {
     // ===================== descriptor warp =====================
-    const int tiles_per_block = L.BS / TILE;
-    int tile = 0;
+    // Lane-parallel: a unit is the next <= 32 tiles of an item; lane l resolves tile l of the unit
+    // (its block's metadata comes by shuffle from the lane that loaded it) and publishes it in its
+    // own ring slot, so a whole unit costs about as many instructions as one tile would serially.
+    const int tpb = L.BS / TILE;                     // tiles per block
+    const int U = tpb >= 32 ? 1 : 32 / tpb;          // blocks per unit
+    int tile = 0;                                    // tiles published by this CTA so far
     int item = blockIdx.x, seq = 0, split = 0, b_start = 0, b_end = 0, base = 0;
     int64_t seq_len = 0, bt_row = 0;
     bool have = false;
-    auto advance = [&]() {  // move (item, base) to the next unit of <= 32 blocks; false when out of work
-      if (have && base + 32 < b_end) { base += 32; return true; }
+    auto advance = [&]() {  // move (item, base) to the next unit; false when the CTA is out of work
+      if (have && base + U < b_end) { base += U; return true; }
       if (have) item += gridDim.x;
       for (; item < n_items; item += gridDim.x) {
         if (item_range(P, item, seq, split, seq_len, b_start, b_end)) {
@@ -746,63 +752,71 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
       }
       return false;
     };
-    auto claim = [&](int t) {  // wait until the consumers have released descriptor slot t % ND
-      if (t >= ND && !mbar_wait(empty + (t % ND), ((t / ND) - 1) & 1)) ok = false;
-      return ok;
-    };
     bool more = advance();
-    BlockMeta nxt = more ? load_meta(P, bt_row, base + lane, b_end) : BlockMeta{};
+    BlockMeta nxt = more ? load_meta(P, bt_row, lane < U ? base + lane : b_end, b_end) : BlockMeta{};
     while (more && ok) {
       const BlockMeta cur = nxt;
       const int u_base = base, u_end = b_end;
       const int64_t u_len = seq_len;
       more = advance();
-      if (more) nxt = load_meta(P, bt_row, base + lane, b_end);
-      const int nb = min(32, u_end - u_base);
-      for (int k = 0; k < nb && ok; ++k) {
-        const int kblk = __shfl_sync(0xffffffffu, cur.blk, k);
-        int bits = __shfl_sync(0xffffffffu, cur.bits, k);
-        const int c1 = __shfl_sync(0xffffffffu, cur.c1, k), c2 = __shfl_sync(0xffffffffu, cur.c2, k),
-                  c3 = __shfl_sync(0xffffffffu, cur.c3, k);
-        const long long ks_slot = __shfl_sync(0xffffffffu, cur.rslot, k);
-        const int kgrp = __shfl_sync(0xffffffffu, cur.rgrp, k);
-        if (bits != 2 && bits != 4 && bits != 8) bits = 2;  // never opened: stay inside the page
-        const bool too_wide = bits > P.max_bits;             // the caller's tier bound was wrong
-        if (too_wide) { bits = P.max_bits; bad_tier = true; }  // such tiles are published empty
-        const int blk_tok = (int)min((int64_t)L.BS, u_len - (int64_t)(u_base + k) * L.BS);
-        const int row_bytes = 32 * H * bits;
-        const int tpc = (2 * L.BS) / bits;
-        const unsigned char* page = P.pages + (int64_t)kblk * L.PS;
-        for (int tb = 0; tb < tiles_per_block && tb * TILE < blk_tok; ++tb, ++tile) {
-          if (!claim(tile)) break;
-          TileDesc& d = desc[tile % ND];
+      if (more) nxt = load_meta(P, bt_row, lane < U ? base + lane : b_end, b_end);
+      const int nb = min(U, u_end - u_base);
+      // tokens of the unit: all blocks are full except possibly the item's last one
+      const int unit_tok = (int)min((int64_t)nb * L.BS, u_len - (int64_t)u_base * L.BS);
+      const int unit_tiles = (unit_tok + TILE - 1) / TILE;
+      const int kb = lane / tpb, tb = lane - kb * tpb;   // this lane's block within the unit, tile within the block
+      const int kblk = __shfl_sync(0xffffffffu, cur.blk, kb);
+      int bits = __shfl_sync(0xffffffffu, cur.bits, kb);
+      const int c1 = __shfl_sync(0xffffffffu, cur.c1, kb), c2 = __shfl_sync(0xffffffffu, cur.c2, kb),
+                c3 = __shfl_sync(0xffffffffu, cur.c3, kb);
+      const long long ks_slot = __shfl_sync(0xffffffffu, cur.rslot, kb);
+      const int kgrp = __shfl_sync(0xffffffffu, cur.rgrp, kb);
+      if (lane < unit_tiles) {
+        const int my_tile = tile + lane;
+        const int slot = my_tile % ND;
+        if (my_tile >= ND && !mbar_wait(empty + slot, ((my_tile / ND) - 1) & 1)) ok = false;
+        if (ok) {
+          if (bits != 2 && bits != 4 && bits != 8) bits = 2;  // never opened: stay inside the page
+          const bool too_wide = bits > P.max_bits;             // the caller's tier bound was wrong
+          if (too_wide) { bits = P.max_bits; bad_tier = true; }  // such tiles are published empty
+          const int row_bytes = 32 * H * bits;
+          const int tpc = (2 * L.BS) / bits;
           const int t0 = tb * TILE;
+          const int blk_tok = min(L.BS, unit_tok - kb * L.BS);
           const int grp = t0 / L.KG;
           const bool in_res = ks_slot >= 0 && grp == kgrp;
-          if (lane < TILE) {  // where token t0 + lane lives
-            const int tok = t0 + lane;
-            const int jc = tok / tpc;
-            int64_t pg = kblk, slot = 0;
-            if (jc > 0) { const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3); pg = id / L.KC; slot = id % L.KC; }
-            d.row_src[lane] = P.pages + pg * L.PS + L.o_data + slot * L.CB + (int64_t)(tok % tpc) * row_bytes;
-          } else if (lane == 16) {
-            // in_res bit 1: the tile's four stats arrays form one contiguous run (tile = whole 16-token block)
-            const bool contig = L.BS == TILE && L.KG == TILE;
-            d.bits = bits; d.n_valid = too_wide ? 0 : min(TILE, blk_tok - t0); d.in_res = (in_res ? 1 : 0) | (contig ? 2 : 0);
-            d.pos0 = t0 % L.KG; d.res_slot = ks_slot;
-          } else if (lane == 17) {
-            d.vs_src = page + L.o_vs + (int64_t)t0 * H * NG * 2;
-            d.vm_src = page + L.o_vm + (int64_t)t0 * H * NG * 2;
-            d.ks_src = page + L.o_ks + (int64_t)grp * H * D * 2;
-            d.km_src = page + L.o_km + (int64_t)grp * H * D * 2;
+          const unsigned char* page = P.pages + (int64_t)kblk * L.PS;
+          TileDesc& d = desc[slot];
+          int jc = t0 / tpc, in_chunk = t0 - jc * tpc;      // chunk of the tile's first token, position inside it
+          const unsigned char* chunk = nullptr;
+          for (int t = 0; t < TILE; ++t) {
+            if (t == 0 || in_chunk == tpc) {
+              if (t) { ++jc; in_chunk = 0; }
+              int64_t pg = kblk, cs = 0;
+              if (jc > 0) { const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3); pg = id / L.KC; cs = id - pg * L.KC; }
+              chunk = P.pages + pg * L.PS + L.o_data + cs * L.CB;
+            }
+            d.row_src[t] = chunk + (int64_t)in_chunk * row_bytes;
+            ++in_chunk;
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(full + (tile % ND));
+          const bool contig = L.BS == TILE && L.KG == TILE;  // the tile's four stats arrays form one run
+          d.bits = bits; d.n_valid = too_wide ? 0 : min(TILE, blk_tok - t0);
+          d.in_res = (in_res ? 1 : 0) | (contig ? 2 : 0);
+          d.pos0 = t0 % L.KG; d.res_slot = ks_slot;
+          d.vs_src = page + L.o_vs + (int64_t)t0 * H * NG * 2;
+          d.vm_src = page + L.o_vm + (int64_t)t0 * H * NG * 2;
+          d.ks_src = page + L.o_ks + (int64_t)grp * H * D * 2;
+          d.km_src = page + L.o_km + (int64_t)grp * H * D * 2;
+          mbar_arrive(full + slot);
         }
       }
+      tile += unit_tiles;
+      ok = !__any_sync(0xffffffffu, !ok);
     }
-    if (ok && claim(tile)) {  // terminal descriptor: no more tiles for this CTA
-      if (lane == 0) { desc[tile % ND].n_valid = -1; mbar_arrive(full + (tile % ND)); }
+    if (ok && lane == 0) {  // terminal descriptor: no more tiles for this CTA
+      const int slot = tile % ND;
+      if (tile < ND || mbar_wait(empty + slot, ((tile / ND) - 1) & 1)) { desc[slot].n_valid = -1; mbar_arrive(full + slot); }
+      else ok = false;
     }
   } else {
     // ===================== consumers: warp h owns KV head h =====================
@@ -942,7 +956,7 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   *handled = false;
   if ((g_decode_path & 15) == 1) return ECHOKV_OK;
   const int H = L.H;
-  if (L.D != D || L.VG != 32 || L.KG % TILE || L.BS % TILE || A.gqa > 8) return ECHOKV_OK;
+  if (L.D != D || L.VG != 32 || L.KG % TILE || L.BS % TILE || L.BS > 32 * TILE || A.gqa > 8) return ECHOKV_OK;
   if (!(H == 1 || H == 2 || H == 4 || H == 8)) return ECHOKV_OK;
   if ((R.s_slot | R.s_pos | R.s_head) & 3) return ECHOKV_OK;                 // 8-byte residual loads
   if ((reinterpret_cast<uintptr_t>(R.base) & 15) != 0) return ECHOKV_OK;
@@ -961,7 +975,7 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   P.stage_bytes = (P.o_km + H * D * 2 + 127) / 128 * 128;
   P.status = status;
   P.debug = (g_decode_path >> 4) & 15;
-  const int fixed = 512 + ND * (int)sizeof(TileDesc) + REMAP_BYTES + H * Q_HEAD_BYTES;
+  const int fixed = HDR_BYTES + ND * (int)sizeof(TileDesc) + REMAP_BYTES + H * Q_HEAD_BYTES;
   static int max_smem = -1, num_sms = 0;
   if (max_smem < 0) {
     int dev = 0;
