@@ -59,6 +59,7 @@ struct Params {
   int H, NS, max_bits, num_seqs;
   int stage_bytes, o_vs, o_vm, o_ks, o_km;  // stage layout (bytes from the stage base)
   int* status;                             // device status word (0 ok), may be null
+  int q_vec16;                             // 16-bit queries whose rows can be read with 16-byte loads
   int debug;                               // experiments only: 1 skip the math, 2 skip the copies
 };
 
@@ -888,19 +889,47 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
       if (!item_range(P, item, seq, split, seq_len, b_start, b_end)) continue;
       const int n_tok = (int)(min(seq_len, (int64_t)b_end * L.BS) - (int64_t)b_start * L.BS);
       const int n_tiles = (n_tok + TILE - 1) / TILE;
-      // this head's queries -> fp16, pre-multiplied by softmax_scale * log2(e); rows >= gqa are zero
+      // this head's queries -> fp16, pre-multiplied by softmax_scale * log2(e); rows >= gqa are zero.
+      // All global loads are issued before the first use so the item pays one memory latency.
       {
         const int64_t q_row = A.q_rows ? A.q_rows[seq] : seq;
         __syncwarp();
-        for (int i = lane; i < 8 * (D / 2); i += 32) {
-          const int d2 = i % (D / 2), n = i / (D / 2);
-          float x = 0.f, y = 0.f;
-          if (n < A.gqa) {
-            const int64_t e = q_row * A.q_s0 + (int64_t)(h * A.gqa + n) * A.q_s1 + 2 * d2;
-            x = ld_dt(A.q, A.q_dt, e) * A.scale_log2e;
-            y = ld_dt(A.q, A.q_dt, e + 1) * A.scale_log2e;
+        if (P.q_vec16) {  // 16-bit queries, 16-byte aligned rows: lane l loads 8 channels of rows l / 16, + 2, + 4, + 6
+          const int c8 = (lane & 15) * 8;
+          uint4 raw[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int n = (lane >> 4) + 2 * k;
+            raw[k] = make_uint4(0, 0, 0, 0);
+            if (n < A.gqa)
+              raw[k] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(A.q) + q_row * A.q_s0 +
+                                                       (int64_t)(h * A.gqa + n) * A.q_s1 + c8);
           }
-          *reinterpret_cast<uint32_t*>(qv.qn + n * QN_ROW + d2 * 4) = pack_h2(x, y);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int n = (lane >> 4) + 2 * k;
+            const uint32_t* wds = reinterpret_cast<const uint32_t*>(&raw[k]);
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float x, y;
+              if (A.q_dt == ECHOKV_DT_BF16) { x = __uint_as_float(wds[e] << 16); y = __uint_as_float(wds[e] & 0xffff0000u); }
+              else { const __half2 hh = *reinterpret_cast<const __half2*>(&wds[e]); x = __low2float(hh); y = __high2float(hh); }
+              o[e] = pack_h2(x * A.scale_log2e, y * A.scale_log2e);
+            }
+            *reinterpret_cast<uint4*>(qv.qn + n * QN_ROW + c8 * 2) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        } else {
+          for (int i = lane; i < 8 * (D / 2); i += 32) {
+            const int d2 = i % (D / 2), n = i / (D / 2);
+            float x = 0.f, y = 0.f;
+            if (n < A.gqa) {
+              const int64_t e = q_row * A.q_s0 + (int64_t)(h * A.gqa + n) * A.q_s1 + 2 * d2;
+              x = ld_dt(A.q, A.q_dt, e) * A.scale_log2e;
+              y = ld_dt(A.q, A.q_dt, e + 1) * A.scale_log2e;
+            }
+            *reinterpret_cast<uint32_t*>(qv.qn + n * QN_ROW + d2 * 4) = pack_h2(x, y);
+          }
         }
         __syncwarp();
       }
@@ -974,6 +1003,7 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   P.o_km = P.o_ks + H * D * 2;
   P.stage_bytes = (P.o_km + H * D * 2 + 127) / 128 * 128;
   P.status = status;
+  P.q_vec16 = (A.q_dt != ECHOKV_DT_F32) && (reinterpret_cast<uintptr_t>(A.q) % 16 == 0) && A.q_s0 % 8 == 0 && A.q_s1 % 8 == 0;
   P.debug = (g_decode_path >> 4) & 15;
   const int fixed = HDR_BYTES + ND * (int)sizeof(TileDesc) + REMAP_BYTES + H * Q_HEAD_BYTES;
   static int max_smem = -1, num_sms = 0;
