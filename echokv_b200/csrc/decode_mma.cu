@@ -227,7 +227,8 @@ __device__ __forceinline__ int acc_channel(int mt, int r, int half) {
 // that the 128-bit fragment loads of two neighbouring rows fall into different bank halves.
 constexpr int QT_ROW = D * 2 + 64;   // tier copy: rows padded so 128-bit fragment loads of two rows hit different bank halves
 constexpr int QN_ROW = D * 2 + 16;   // natural copy: rows padded for ldmatrix over the 8 query rows
-constexpr int Q_HEAD_BYTES = 8 * (QT_ROW + QN_ROW);
+constexpr int Q_ROWS_MAX = 9;          // up to 8 query heads per KV head + one shared zero row
+__host__ __device__ constexpr int q_head_bytes(int rows) { return rows * (QT_ROW + QN_ROW); }
 constexpr int REMAP_ROW = D + 4;                      // floats per query head in the canonical layout
 constexpr int REMAP_BYTES = 8 * REMAP_ROW * 4;
 
@@ -525,7 +526,8 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t 
 
 // A warp's two query copies in shared memory (see QT_ROW / QN_ROW).
 struct QView {
-  unsigned char *qn, *qt;      // natural copy [8][QN_ROW], tier-scaled copy [8][QT_ROW]
+  unsigned char *qn, *qt;      // natural copy [rows][QN_ROW], tier-scaled copy [rows][QT_ROW]
+  int rows;                    // gqa real rows + one zero row that every unused query column reads
   uint32_t qt_lane, qn_lane;   // shared address of this lane's query row (row lane / 4) in each copy
   uint32_t qn_ld;              // this lane's ldmatrix row address in the natural copy
 };
@@ -536,7 +538,7 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
   const int r = lane >> 2, j = lane & 3;
   if (w.qbits != BITS) {  // (re)build the tier's query copy: INT4 needs its odd channels scaled by 2^-4
     __syncwarp();
-    for (int i = lane; i < 8 * (D / 2); i += 32) {
+    for (int i = lane; i < qv.rows * (D / 2); i += 32) {
       const int n = i / (D / 2), wd = i % (D / 2);
       uint32_t v = *reinterpret_cast<const uint32_t*>(qv.qn + n * QN_ROW + wd * 4);
       if constexpr (BITS == 4) v = hmul2u(v, 0x2c003c00u);  // (1, 2^-4)
@@ -716,7 +718,8 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
   TileDesc* desc = reinterpret_cast<TileDesc*>(smem + HDR_BYTES);
   float* remap = reinterpret_cast<float*>(smem + HDR_BYTES + ND * sizeof(TileDesc));
   unsigned char* qs = reinterpret_cast<unsigned char*>(remap) + REMAP_BYTES;
-  unsigned char* ring = qs + H * Q_HEAD_BYTES;
+  const int q_rows = A.gqa + 1;
+  unsigned char* ring = qs + H * q_head_bytes(q_rows);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < ND; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, H); }
@@ -732,6 +735,7 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
 
   bool ok = true, bad_tier = false;
   if (warp == H) {
+    if (P.debug == 3) return;  // experiment: consumers make up their own addresses
     // ===================== descriptor warp =====================
     // Lane-parallel: a unit is the next <= 32 tiles of an item; lane l resolves tile l of the unit
     // (its block's metadata comes by shuffle from the lane that loaded it) and publishes it in its
@@ -825,11 +829,16 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
     const int r = lane >> 2;
     const int tid = threadIdx.x;  // 0 .. N_CONS - 1
     QView qv;
-    qv.qn = qs + h * Q_HEAD_BYTES;
-    qv.qt = qv.qn + 8 * QN_ROW;
-    qv.qt_lane = smem_u32(qv.qt + r * QT_ROW);
-    qv.qn_lane = smem_u32(qv.qn + r * QN_ROW);
-    qv.qn_ld = smem_u32(qv.qn + (lane & 7) * QN_ROW + (lane >> 3) * 16);
+    qv.rows = q_rows;
+    qv.qn = qs + h * q_head_bytes(q_rows);
+    qv.qt = qv.qn + q_rows * QN_ROW;
+    {  // query columns >= gqa of the MMAs read the shared zero row
+      const int my_row = r < A.gqa ? r : A.gqa, ld_row = (lane & 7) < A.gqa ? (lane & 7) : A.gqa;
+      qv.qt_lane = smem_u32(qv.qt + my_row * QT_ROW);
+      qv.qn_lane = smem_u32(qv.qn + my_row * QN_ROW);
+      qv.qn_ld = smem_u32(qv.qn + ld_row * QN_ROW + (lane >> 3) * 16);
+      for (int i = lane; i < D / 2; i += 32) *reinterpret_cast<uint32_t*>(qv.qn + A.gqa * QN_ROW + i * 4) = 0u;
+    }
     const LaneConst lc = lane_const(H, h, lane);
     const uint32_t ring_u = smem_u32(ring);
     const uint32_t stage_bytes = P.stage_bytes;
@@ -841,7 +850,32 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
     int is_st = 0, is_ds = 0, is_par = 0;   // stage / descriptor slot / descriptor parity of the next tile to issue
     uint32_t is_sb = ring_u;
     // Issue this thread's share of the copies of the next tile (or an empty group past the end).
+    int dbg_issued = 0, dbg_total = 0;
+    if (P.debug == 3) {
+      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        int seq, split, b_start, b_end; int64_t seq_len;
+        if (item_range(P, item, seq, split, seq_len, b_start, b_end))
+          dbg_total += (int)((min(seq_len, (int64_t)b_end * L.BS) - (int64_t)b_start * L.BS + TILE - 1) / TILE);
+      }
+    }
     auto issue = [&]() {
+      if (P.debug == 3) {  // experiment: synthetic INT4 tile addresses, no descriptor handshake
+        if (dbg_issued < dbg_total) {
+          const int64_t blk = ((int64_t)(blockIdx.x * 977 + dbg_issued * 131) % L.NB);
+          const unsigned char* pg = P.pages + blk * L.PS;
+          const unsigned char* pg2 = P.pages + ((blk * 7 + 3) % L.NB) * L.PS;
+          const uint32_t row_bytes = 32u * H * 4;
+#pragma unroll
+          for (int k = 0; k < TOK_PER_WARP; ++k) {
+            const int t = h + k * H;
+            const unsigned char* src = (t < 8 ? pg + L.o_data + t * row_bytes : pg2 + L.o_data + 8192 + (t - 8) * row_bytes) + lane * 16;
+            const uint32_t dst = is_sb + t * (row_bytes + 16) + lane * 16;
+            for (uint32_t o = lane * 16; o < row_bytes; o += 512) cp_async16(dst + (o - lane * 16), src + (o - lane * 16));
+          }
+          for (int i = tid; i < STAT16; i += N_CONS) cp_async16(is_sb + stats_off + i * 16, pg + L.o_vs + i * 16);
+        }
+        ++dbg_issued;
+      } else
       if (!ended && ok) {
         if (!mbar_wait(full + is_ds, is_par)) ok = false;
         const TileDesc& d = desc[is_ds];
@@ -917,17 +951,13 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
               else { const __half2 hh = *reinterpret_cast<const __half2*>(&wds[e]); x = __low2float(hh); y = __high2float(hh); }
               o[e] = pack_h2(x * A.scale_log2e, y * A.scale_log2e);
             }
-            *reinterpret_cast<uint4*>(qv.qn + n * QN_ROW + c8 * 2) = make_uint4(o[0], o[1], o[2], o[3]);
+            if (n < A.gqa) *reinterpret_cast<uint4*>(qv.qn + n * QN_ROW + c8 * 2) = make_uint4(o[0], o[1], o[2], o[3]);
           }
         } else {
-          for (int i = lane; i < 8 * (D / 2); i += 32) {
+          for (int i = lane; i < A.gqa * (D / 2); i += 32) {
             const int d2 = i % (D / 2), n = i / (D / 2);
-            float x = 0.f, y = 0.f;
-            if (n < A.gqa) {
-              const int64_t e = q_row * A.q_s0 + (int64_t)(h * A.gqa + n) * A.q_s1 + 2 * d2;
-              x = ld_dt(A.q, A.q_dt, e) * A.scale_log2e;
-              y = ld_dt(A.q, A.q_dt, e + 1) * A.scale_log2e;
-            }
+            const int64_t e = q_row * A.q_s0 + (int64_t)(h * A.gqa + n) * A.q_s1 + 2 * d2;
+            const float x = ld_dt(A.q, A.q_dt, e) * A.scale_log2e, y = ld_dt(A.q, A.q_dt, e + 1) * A.scale_log2e;
             *reinterpret_cast<uint32_t*>(qv.qn + n * QN_ROW + d2 * 4) = pack_h2(x, y);
           }
         }
@@ -954,13 +984,13 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
         tv.vrow = c_sb + (si.bits == 8 ? lc.v8 : (si.bits == 4 ? lc.v4 : lc.v2));
         tv.vs = c_sb + P.o_vs + lc.vs_off; tv.vm = c_sb + P.o_vm + lc.vm_off;
         tv.ks = c_sb + P.o_ks + lc.ksm_off; tv.km = c_sb + P.o_km + lc.ksm_off; tv.tok = lc.tok;
-        if (si.n_valid > 0 && P.debug != 1) {
+        if (si.n_valid > 0 && P.debug != 1 && P.debug != 3) {
           if (si.bits == 4) process_tile<4>(P, tv, si, qv, h, lane, w, remap, lock, ok);
           else if (si.bits == 8) process_tile<8>(P, tv, si, qv, h, lane, w, remap, lock, ok);
           else process_tile<2>(P, tv, si, qv, h, lane, w, remap, lock, ok);
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty + c_ds);
+        if (lane == 0 && P.debug != 3) mbar_arrive(empty + c_ds);
         if (++c_st == NS) { c_st = 0; c_sb = ring_u; } else { c_sb += stage_bytes; }
         if (++c_ds == ND) c_ds = 0;
       }
@@ -1005,7 +1035,8 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   P.status = status;
   P.q_vec16 = (A.q_dt != ECHOKV_DT_F32) && (reinterpret_cast<uintptr_t>(A.q) % 16 == 0) && A.q_s0 % 8 == 0 && A.q_s1 % 8 == 0;
   P.debug = (g_decode_path >> 4) & 15;
-  const int fixed = HDR_BYTES + ND * (int)sizeof(TileDesc) + REMAP_BYTES + H * Q_HEAD_BYTES;
+  if (P.debug == 3 && P.max_bits < 4) P.debug = 0;  // the synthetic-address experiment copies INT4-sized rows
+  const int fixed = HDR_BYTES + ND * (int)sizeof(TileDesc) + REMAP_BYTES + H * q_head_bytes(A.gqa + 1);
   static int max_smem = -1, num_sms = 0;
   if (max_smem < 0) {
     int dev = 0;
