@@ -20,6 +20,8 @@
 // out packed codes); when consecutive blocks differ in tier the warp re-maps its accumulators
 // through shared memory.  Token sets are merged in set order and splits in split order, so a
 // sequence's result depends on its own length only.
+#include <utility>
+
 #include "decode_generic.cuh"
 
 namespace echokv {
@@ -96,13 +98,37 @@ __device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t b
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+// Compile-time loop: the index is an integral constant, so it can feed template arguments.
+template <class F, int... I>
+__device__ __forceinline__ void static_for_impl(F&& f, std::integer_sequence<int, I...>) {
+  (f(std::integral_constant<int, I>{}), ...);
 }
+template <int N, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+  static_for_impl(f, std::make_integer_sequence<int, N>{});
+}
+
+// Shared-memory loads take a base register plus a compile-time byte offset so the offset folds
+// into the instruction instead of costing an integer add each.
+template <int OFF>
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4+%5];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(OFF));
+}
+template <int OFF>
 __device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(OFF));
+}
+template <int OFF>
+__device__ __forceinline__ void lds128(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(OFF));
+}
+template <int OFF>
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
+  return v;
 }
 __device__ __forceinline__ uint32_t movm_t(uint32_t a) {
   uint32_t d;
@@ -300,7 +326,7 @@ __device__ __forceinline__ LaneConst lane_const(int H, int h, int lane) {
   c.k8 = row * (256u * H + 16u) + h * 128u + piece; c.v8 = c.k8 + 128u * H;
   c.tok = (uint32_t)H * NG * 2;
   c.vs_off = (uint32_t)((2 * j) * H + h) * NG * 2;
-  c.vm_off = c.vs_off + (uint32_t)r * 2;
+  c.vm_off = c.vs_off + (uint32_t)(r < NG ? r : 0) * 2;
   c.ksm_off = (uint32_t)h * D * 2;
   return c;
 }
@@ -314,6 +340,7 @@ __device__ __forceinline__ LaneConst lane_const(int H, int h, int lane) {
 // INT2 keeps the magic-number path (its four crumb positions would need four query scalings and
 // its V path multiplies codes by scales in fp16, which subnormals cannot take).
 constexpr float CODE_UNSCALE = 16777216.f;  // 2^24
+constexpr float RESCALE_SLACK = 6.f;
 
 __device__ __forceinline__ void sub4(uint32_t w, uint32_t (&o)[4]) {  // INT4 word -> 4 subnormal pairs
   o[0] = w & 0x000f000fu;
@@ -336,58 +363,53 @@ __device__ __forceinline__ void sub8_t(uint32_t w, uint32_t (&o)[2]) {  // [a.c0
 // whose B fragments are the natural-order query (ldmatrix over the 8 query rows).
 __device__ __forceinline__ void km_term(uint32_t km, uint32_t qn_ld, int lane, float (&c2)[4]) {
   const uint32_t km_ld = km + (lane < 16 ? 0u : 16u);
-#pragma unroll
-  for (int k2 = 0; k2 < 4; ++k2) {
+  static_for<4>([&](auto k2c) {
+    constexpr int k2 = decltype(k2c)::value;
     uint32_t B[4];
-    ldsm_x4(B, qn_ld + k2 * 64);
-#pragma unroll
-    for (int kk = 0; kk < 2; ++kk) {
+    ldsm_x4<k2 * 64>(B, qn_ld);
+    static_for<2>([&](auto kkc) {
+      constexpr int kk = decltype(kkc)::value;
       uint32_t A[4];
-      ldsm_x4(A, km_ld + (2 * k2 + kk) * 32);
+      ldsm_x4<(2 * k2 + kk) * 32>(A, km_ld);
       mma16816(c2, A[0], A[1], A[2], A[3], B[2 * kk], B[2 * kk + 1]);
-    }
-  }
+    });
+  });
 }
 
 template <int BITS>
 __device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t qt_lane, uint32_t qn_ld, int lane, float (&c)[4]) {
   const int j = lane & 3;
-  const uint32_t ks = tv.ks;
   const uint32_t krow = tv.krow;
   float c2[4] = {0.f, 0.f, 0.f, 0.f};
   km_term(tv.km, qn_ld, lane, c2);
   if constexpr (BITS == 8) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {  // pieces 2i, 2i+1 (16 channels each)
+    const uint32_t qb = qt_lane + j * 8, sb = tv.ks + j * 8;  // this lane's 4 channels of every 16-channel piece
+    static_for<4>([&](auto ic) {  // pieces 2i, 2i+1 (16 channels each)
+      constexpr int i = decltype(ic)::value;
       uint32_t R[4];
-      ldsm_x4(R, krow + i * 32);
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int p = 2 * i + e;
-        const uint32_t off = (16 * p + 4 * j) * 2;
-        uint2 qw, sw;
-        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(qw.x), "=r"(qw.y) : "r"(qt_lane + off));
-        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(sw.x), "=r"(sw.y) : "r"(ks + off));
+      ldsm_x4<i * 32>(R, krow);
+      static_for<2>([&](auto ec) {
+        constexpr int e = decltype(ec)::value, p = 2 * i + e;
+        const uint2 qw = lds64<32 * p>(qb), sw = lds64<32 * p>(sb);
         uint32_t a[2], b[2];
         sub8(R[2 * e], a);
         sub8(R[2 * e + 1], b);
         mma16816(c, a[0], b[0], a[1], b[1], hmul2u(qw.x, sw.x), hmul2u(qw.y, sw.y));
-      }
-    }
+      });
+    });
 #pragma unroll
     for (int k = 0; k < 4; ++k) c[k] = fmaf(c[k], CODE_UNSCALE, c2[k]);
   } else if constexpr (BITS == 4) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {  // pieces 2i, 2i+1 (32 channels each)
+    const uint32_t qb = qt_lane + j * 16, sb = tv.ks + j * 16;  // this lane's 8 channels of every 32-channel piece
+    static_for<2>([&](auto ic) {  // pieces 2i, 2i+1 (32 channels each)
+      constexpr int i = decltype(ic)::value;
       uint32_t R[4];
-      ldsm_x4(R, krow + i * 32);
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int p = 2 * i + e;
-        const uint32_t off = (32 * p + 8 * j) * 2;
+      ldsm_x4<i * 32>(R, krow);
+      static_for<2>([&](auto ec) {
+        constexpr int e = decltype(ec)::value, p = 2 * i + e;
         uint32_t W[4], S[4], Z[4];
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(W[0]), "=r"(W[1]), "=r"(W[2]), "=r"(W[3]) : "r"(qt_lane + off));
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(S[0]), "=r"(S[1]), "=r"(S[2]), "=r"(S[3]) : "r"(ks + off));
+        lds128<64 * p>(W, qb);
+        lds128<64 * p>(S, sb);
 #pragma unroll
         for (int k = 0; k < 4; ++k) Z[k] = hmul2u(W[k], S[k]);
         uint32_t a[4], b[4];
@@ -395,21 +417,23 @@ __device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t qt_lane, u
         sub4(R[2 * e + 1], b);
         mma16816(c, a[0], b[0], a[1], b[1], prmt(Z[0], Z[2], 0x5410u), prmt(Z[0], Z[2], 0x7632u));
         mma16816(c, a[2], b[2], a[3], b[3], prmt(Z[1], Z[3], 0x5410u), prmt(Z[1], Z[3], 0x7632u));
-      }
-    }
+      });
+    });
 #pragma unroll
     for (int k = 0; k < 4; ++k) c[k] = fmaf(c[k], CODE_UNSCALE, c2[k]);
   } else {
+    const uint32_t qb = qt_lane + j * 32, sb = tv.ks + j * 32;  // this lane's 16 channels of every 64-channel piece
     uint32_t R[4];
-    ldsm_x4(R, krow);  // pieces 0, 1 (64 channels each)
-#pragma unroll
-    for (int p = 0; p < 2; ++p) {
-      const uint32_t off = (64 * p + 16 * j) * 2;
+    ldsm_x4<0>(R, krow);  // pieces 0, 1 (64 channels each)
+    static_for<2>([&](auto pc) {
+      constexpr int p = decltype(pc)::value;
       uint32_t W[8], S[8], Z[8];
-#pragma unroll
-      for (int v = 0; v < 2; ++v) {
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(W[4 * v]), "=r"(W[4 * v + 1]), "=r"(W[4 * v + 2]), "=r"(W[4 * v + 3]) : "r"(qt_lane + off + 16 * v));
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(S[4 * v]), "=r"(S[4 * v + 1]), "=r"(S[4 * v + 2]), "=r"(S[4 * v + 3]) : "r"(ks + off + 16 * v));
+      {
+        uint32_t t4[4];
+        lds128<128 * p>(t4, qb);      W[0] = t4[0]; W[1] = t4[1]; W[2] = t4[2]; W[3] = t4[3];
+        lds128<128 * p + 16>(t4, qb); W[4] = t4[0]; W[5] = t4[1]; W[6] = t4[2]; W[7] = t4[3];
+        lds128<128 * p>(t4, sb);      S[0] = t4[0]; S[1] = t4[1]; S[2] = t4[2]; S[3] = t4[3];
+        lds128<128 * p + 16>(t4, sb); S[4] = t4[0]; S[5] = t4[1]; S[6] = t4[2]; S[7] = t4[3];
       }
 #pragma unroll
       for (int k = 0; k < 8; ++k) Z[k] = hmul2u(W[k], S[k]);
@@ -419,7 +443,7 @@ __device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t qt_lane, u
 #pragma unroll
       for (int k = 0; k < 4; ++k)
         mma16816(c, a[2 * k], b[2 * k], a[2 * k + 1], b[2 * k + 1], prmt(Z[k], Z[k + 4], 0x5410u), prmt(Z[k], Z[k + 4], 0x7632u));
-    }
+    });
 #pragma unroll
     for (int k = 0; k < 4; ++k) c[k] += c2[k];
   }
@@ -446,11 +470,12 @@ __device__ __forceinline__ void qk_residual(const ResidualDev& R, const StageInf
   const bool v0 = r < si.n_valid, v1 = r + 8 < si.n_valid;
   const int64_t e0 = si.res_slot * R.s_slot + (int64_t)(si.pos0 + r) * R.s_pos + h * R.s_head;
   const int64_t e1 = e0 + 8 * R.s_pos;
+  const uint32_t qb = qn_lane + j * 8;
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
     const int ch = 16 * p + 4 * j;
     uint2 qw;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(qw.x), "=r"(qw.y) : "r"(qn_lane + ch * 2));
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(qw.x), "=r"(qw.y) : "r"(qb + p * 32));
     const uint32_t a0 = v0 ? res_pair(R, e0 + ch) : 0u, a2 = v0 ? res_pair(R, e0 + ch + 2) : 0u;
     const uint32_t a1 = v1 ? res_pair(R, e1 + ch) : 0u, a3 = v1 ? res_pair(R, e1 + ch + 2) : 0u;
     mma16816(c, a0, a1, a2, a3, qw.x, qw.y);
@@ -462,7 +487,7 @@ __device__ __forceinline__ void qk_residual(const ResidualDev& R, const StageInf
 template <int BITS>
 __device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t pb0, uint32_t pb1, WarpState& w) {
   const int r = lane >> 2;
-  // V scale of this lane's four tokens, all NG groups: vs2lo[G] = {vs[2j][G], vs[2j+1][G]}, vs2hi[G] likewise +8
+  // V scale of this lane's four tokens, all NG groups: vlo[G] = {vs[2j][G], vs[2j+1][G]}, vhi[G] likewise +8
   uint32_t vlo[NG], vhi[NG];
   {
     uint2 t0, t1, t2, t3;
@@ -478,10 +503,10 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t 
   }
   const uint32_t vrow = tv.vrow;
   if constexpr (BITS == 8) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {  // pieces 2i, 2i+1 = the two halves of V group i
+    static_for<4>([&](auto ic) {  // pieces 2i, 2i+1 = the two halves of V group i
+      constexpr int i = decltype(ic)::value;
       uint32_t Q[4];
-      ldsm_x4_t(Q, vrow + i * 32);
+      ldsm_x4_t<i * 32>(Q, vrow);
       const uint32_t b0 = hmul2u(pb0, vlo[i]), b1 = hmul2u(pb1, vhi[i]);
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
@@ -490,12 +515,12 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t 
         sub8_t(Q[2 * e + 1], hi);
         mma16816(w.acc[2 * i + e], lo[0], lo[1], hi[0], hi[1], b0, b1);
       }
-    }
+    });
   } else if constexpr (BITS == 4) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {  // pieces 2i, 2i+1 = V groups 2i, 2i+1
+    static_for<2>([&](auto ic) {  // pieces 2i, 2i+1 = V groups 2i, 2i+1
+      constexpr int i = decltype(ic)::value;
       uint32_t Q[4];
-      ldsm_x4_t(Q, vrow + i * 32);
+      ldsm_x4_t<i * 32>(Q, vrow);
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int G = 2 * i + e;
@@ -506,10 +531,10 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t 
         mma16816(w.acc[2 * G], lo[0], lo[1], hi[0], hi[1], b0, b1);
         mma16816(w.acc[2 * G + 1], lo[2], lo[3], hi[2], hi[3], b0, b1);
       }
-    }
+    });
   } else {
     uint32_t Q[4];
-    ldsm_x4_t(Q, vrow);  // pieces 0, 1 = V groups {0,1}, {2,3}; this lane's channels lie in group 2q + (r >= 4)
+    ldsm_x4_t<0>(Q, vrow);  // pieces 0, 1 = V groups {0,1}, {2,3}; this lane's channels lie in group 2q + (r >= 4)
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
       const uint32_t sl = r < 4 ? vlo[2 * q] : vlo[2 * q + 1], sh = r < 4 ? vhi[2 * q] : vhi[2 * q + 1];
@@ -576,9 +601,13 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
     t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, o));
     t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, o));
   }
-  const float n0 = fmaxf(w.m0, t0), n1 = fmaxf(w.m1, t1);
-  const bool grew = (n0 > w.m0) || (n1 > w.m1);
+  // The reference point of the exponentials only moves when a tile's maximum exceeds it by more
+  // than RESCALE_SLACK (in log2 units): until then p <= 2^RESCALE_SLACK, well inside fp16, and the
+  // accumulators need no rescaling.  The result is the same softmax (the reference point cancels).
+  const bool grew = (t0 > w.m0 + RESCALE_SLACK) || (t1 > w.m1 + RESCALE_SLACK);
+  float n0 = w.m0, n1 = w.m1;
   if (__any_sync(0xffffffffu, grew)) {
+    n0 = fmaxf(w.m0, t0); n1 = fmaxf(w.m1, t1);
     const float a0 = ex2(w.m0 - n0), a1 = ex2(w.m1 - n1);
 #pragma unroll
     for (int mt = 0; mt < 8; ++mt) { w.acc[mt][0] *= a0; w.acc[mt][1] *= a1; w.acc[mt][2] *= a0; w.acc[mt][3] *= a1; }
@@ -590,18 +619,14 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
   const uint32_t pb0 = movm_t(p_lo), pb1 = movm_t(p_hi);
   // [v_min | ones] rows: bias of V group r (lanes r < NG) and the softmax denominator
   {
-    uint32_t a0 = 0u, a2 = 0u;
-    if (r < NG) {
-      const uint32_t base = tv.vm, tok = tv.tok;
-      uint32_t x0, x1, x2, x3;
-      asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x0) : "r"(base));
-      asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x1) : "r"(base + tok));
-      asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x2) : "r"(base + 8 * tok));
-      asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x3) : "r"(base + 9 * tok));
-      a0 = x0 | (x1 << 16);
-      a2 = x2 | (x3 << 16);
-    }
-    mma16816(w.bl, a0, H2_ONE, a2, H2_ONE, pb0, pb1);
+    const uint32_t base = tv.vm, tok = tv.tok;  // lanes r >= NG read group 0 and mask it to zero
+    uint32_t x0, x1, x2, x3;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x0) : "r"(base));
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x1) : "r"(base + tok));
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x2) : "r"(base + 8 * tok));
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x3) : "r"(base + 9 * tok));
+    const uint32_t keep = r < NG ? 0xffffffffu : 0u;
+    mma16816(w.bl, prmt(x0, x1, 0x5410u) & keep, H2_ONE, prmt(x2, x3, 0x5410u) & keep, H2_ONE, pb0, pb1);
   }
   pv_codes<BITS>(tv, lane, pb0, pb1, w);
 }
