@@ -36,6 +36,9 @@ sys.path.insert(0, str(ROOT))
 
 HQ, H, D, BS, KG, VG, MEM_BITS = 32, 8, 128, 16, 16, 32, 8
 METRIC = "decode tokens/s/GPU at INT4 KV; paged-decode attention HBM GB/s vs peak"
+# dram__bytes_read.sum + dram__bytes_write.sum of one INT4 decode launch at batch 64 x ctx 4096 from the
+# ncu capture summarised under profiles/ (reads 378 MB of pages, writes 16 MB of split partials)
+DRAM_TRAFFIC_INT4 = 394_000_000
 
 
 def parse():
@@ -332,21 +335,29 @@ def run_b200(a) -> None:
     clocks = sampler.stop() if rank == 0 else {}
     ms_e2e = timed(max(2, a.steps // 2), True) / max(2, a.steps // 2)
 
-    # ---- roofline of the dominant kernel: decode attention, one launch per layer, timed with
-    # CUDA events on the launching stream; consecutive launches read different layers' pools
-    # (hundreds of MB each, larger than L2)
+    # ---- roofline of the dominant kernel: paged decode attention (split kernel + merge), timed with
+    # CUDA events on the launching stream over back-to-back launches: all layers of one tier, three
+    # passes, no host synchronisation in between (consecutive launches read different layers' pools,
+    # ~640 MB each, so nothing is served from L2)
     lens_now = np.full(S, state["len"])
     meta = host_plan()
     per_tier: dict[int, list[float]] = {2: [], 4: [], 8: []}
-    for rep in range(3):
-        for l in range(Lr):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
+    for b in (2, 4, 8):
+        layers_b = [l for l in range(Lr) if tiers[l] == b]
+        if not layers_b:
+            continue
+        for l in layers_b:  # warm
             runner.decode(l, q_dev[l], table, out_dev[l], meta)
-            e1.record()
-            torch.cuda.synchronize()
-            if rep:
-                per_tier[tiers[l]].append(e0.elapsed_time(e1))
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
+        e0.record()
+        for _ in range(reps):
+            for l in layers_b:
+                runner.decode(l, q_dev[l], table, out_dev[l], meta)
+        e1.record()
+        torch.cuda.synchronize()
+        per_tier[b].append(e0.elapsed_time(e1) / (reps * len(layers_b)))
     peaks = {}
     try:
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
@@ -378,7 +389,8 @@ def run_b200(a) -> None:
                        "cuda_graph": graph is not None, "l2": "each layer's pool is larger than L2; layers alternate",
                        "host_cores": cores},
             "roofline": {"bound": "hbm", "achieved": main["gbs"], "peak": peak, "unit": "GB/s", "frac": main["frac"],
-                         "traffic": None, "kernel": "paged decode attention, INT4 layers", "peak_source": peak_src,
+                         "traffic": DRAM_TRAFFIC_INT4 if (S, ctx, world) == (64, 4096, 1) else None,
+                         "kernel": "paged decode attention (split kernel + merge), INT4 layers", "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": main["bytes"], "per_tier": tier_stats},
             "cpu_baseline": base,
             "e2e": {"value": S / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
