@@ -53,6 +53,7 @@ def parse():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph")
     ap.add_argument("--cpu-seqs", type=int, default=4, help="sequences in the CPU-baseline sample")
+    ap.add_argument("--canary-interval", type=int, default=8, help="measure the canary KL every N steps (0 = never)")
     return ap.parse_args()
 
 
@@ -275,12 +276,13 @@ def run_b200(a) -> None:
         n = state["len"]
         slots = table_np[:, n // BS].astype(np.int64) * BS + n % BS
         state["len"] = n + 1
-        return runner.plan_step(slots, decode=(rows, rows, np.full(S, n + 1)))
+        return runner.plan_step(slots, decode=(rows, rows, np.full(S, n + 1)), canary=rows[:8].astype(np.int64))
 
     def device_step(meta, capturing=False):
         for l in range(Lr):
             runner.write(l, k_dev[l], v_dev[l], meta, capturing=capturing)
             runner.decode(l, q_dev[l], table, out_dev[l], meta)
+            runner.stash_queries(l, q_dev[l], meta)  # the canary's query rows (captured unconditionally)
 
     launches_per_step = 4 * Lr  # finalize, write_tokens, decode, merge per layer (+ host-plan scatters)
     graph = None
@@ -295,7 +297,23 @@ def run_b200(a) -> None:
         graph.replay()
         torch.cuda.synchronize()
 
+    canary = {"n": 0, "pending": None, "fires": 0}
+    tp_group = None  # the default process group is the tensor-parallel group here
+
+    def canary_tick():
+        """Every --canary-interval steps: KL of every layer at 2/4/8 bits from the K_ref rings and the
+        stashed queries (one kernel), mean over TP ranks (one small NCCL all-reduce), and the previous
+        measurement goes to the controllers (so nothing waits on the GPU)."""
+        canary["n"] += 1
+        if not a.canary_interval or canary["n"] % a.canary_interval:
+            return
+        if canary["pending"] is not None:
+            runner.observe(canary["pending"], float(state["len"]))
+        canary["pending"] = runner.measure_canary(8, tp_group)
+        canary["fires"] += 1
+
     def step(e2e: bool):
+        canary_tick()  # before this step's plan moves the K_ref ring
         if e2e:
             q_dev.copy_(q_host, non_blocking=True)
             k_dev.copy_(k_host, non_blocking=True)
@@ -394,7 +412,9 @@ def run_b200(a) -> None:
                          "algorithmic_bytes_per_launch": main["bytes"], "per_tier": tier_stats},
             "cpu_baseline": base,
             "e2e": {"value": S / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches_per_step * a.steps,
+            "gpu_launches": launches_per_step * a.steps + canary["fires"],
+            "canary": {"interval": a.canary_interval, "fires": canary["fires"],
+                       "last": None if canary["pending"] is None else [round(x, 6) for x in canary["pending"][0].tolist()]},
             "clocks": clocks,
             "write": {"gbs": write_bytes / write_ms / 1e6, "ms_total": write_ms, "what": "bulk quantize-on-write of the context"},
         }))

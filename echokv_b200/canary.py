@@ -103,3 +103,19 @@ def canary_kl(query: torch.Tensor, kref: torch.Tensor, bits: tuple[int, ...], k_
     full = canary_kl_ring(q4, k4, 0, k4.shape[1], k_group, softmax_scale)
     cols = [SUPPORTED_BITS.index(b) for b in bits]
     return full[:, cols].reshape(*lead, len(bits))
+
+
+def tp_mean(x: torch.Tensor, group=None) -> torch.Tensor:
+    """Average ``x`` over the tensor-parallel ranks (each rank's canary sees only its own KV heads),
+    so every rank takes the same tier decision -- the reference's ``backend._tp_mean``
+    (echokv_vllm/backend.py:665-675).  One small all-reduce (NCCL on GPUs); a no-op without a
+    process group or with a single rank."""
+    import torch.distributed as dist
+
+    if not dist.is_available() or not dist.is_initialized():
+        return x
+    world = dist.get_world_size(group)
+    if world == 1:
+        return x
+    dist.all_reduce(x, op=dist.ReduceOp.SUM, group=group)
+    return x.div_(world)

@@ -20,7 +20,9 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
+from echokv_b200.canary import canary_kl_ring, tp_mean
 from echokv_b200.controller import LayerController
+from echokv_b200.quant import SUPPORTED_BITS
 from echokv_b200.kernels.decode import BLOCKS_PER_SPLIT, decode_attention
 from echokv_b200.tiered_cache import TieredKVCache, TieredLayout
 from echokv_b200.write_plan import SharedState, WriteMeta
@@ -158,14 +160,17 @@ class GroupRunner:
         self.stores: list[TieredKVCache] = []
         self.krefs: list[torch.Tensor] = []
         self.stashes: list[torch.Tensor] = []
+        # one allocation for all layers' K_ref rings / stashes: the canary kernel reads them in place
+        self._kref_all = None if krefs else torch.zeros(len(caches), kref_window, h, d, dtype=torch.float32, device=dev)
+        self._stash_all = None if stashes else torch.zeros(len(caches), canary_max_q, num_q_heads, d,
+                                                           dtype=model_dtype, device=dev)
         for i, pages in enumerate(caches):
             res = residuals[i] if residuals else torch.zeros(residual_slots + 1, g, h, d, dtype=model_dtype, device=dev)
             self.stores.append(TieredKVCache(layout, pages, residual=res, shared=self.shared))
             if controllers[i].params.fixed_bits is not None:  # a pinned layer can never hold a higher tier
                 self.stores[-1].max_tier = controllers[i].params.fixed_bits
-            self.krefs.append(krefs[i] if krefs else torch.zeros(kref_window, h, d, dtype=torch.float32, device=dev))
-            self.stashes.append(stashes[i] if stashes else
-                                torch.zeros(canary_max_q, num_q_heads, d, dtype=model_dtype, device=dev))
+            self.krefs.append(krefs[i] if krefs else self._kref_all[i])
+            self.stashes.append(stashes[i] if stashes else self._stash_all[i])
         self.canary_max_q = canary_max_q
         self.cap = cap
         tail = cap * (4 + 3 * len(caches)) + 64
@@ -208,6 +213,28 @@ class GroupRunner:
         has_dec = decode is not None and dec[0].size > 0
         return StepMeta(write, canary_rows, dviews[0] if has_dec else None, dviews[1] if has_dec else None,
                         dviews[2] if has_dec else None, self.num_splits)
+
+    # -- canary (reference: EchoKVMetadataBuilder._run_canary, backend.py:314-333) --------------
+    def stash_queries(self, layer: int, query: torch.Tensor, meta: StepMeta) -> None:
+        """Keep the step's canary query rows (graph-capturable: indices come from device metadata)."""
+        torch.index_select(query, 0, meta.canary_rows, out=self.stashes[layer])
+
+    def measure_canary(self, nq: int, tp_group=None) -> torch.Tensor | None:
+        """KL at 2/4/8 bits for every layer from the stashed queries and the K_ref rings, averaged
+        over tensor-parallel ranks; float32 ``[L, 3]`` on the device, or None while the rings hold
+        less than one K group.  Must run before the next ``plan_step`` moves the ring cursor."""
+        pl = self.shared.planner
+        if pl.kref_fill < self.layout.k_group:
+            return None
+        kref = self._kref_all if self._kref_all is not None else torch.stack(self.krefs)
+        stash = self._stash_all if self._stash_all is not None else torch.stack(self.stashes)
+        deltas = canary_kl_ring(stash[:, :nq], kref, pl.kref_pos, pl.kref_fill, self.layout.k_group, self.scale)
+        return tp_mean(deltas, tp_group)
+
+    def observe(self, deltas: torch.Tensor, ctx_len: float) -> None:
+        """Feed a finished measurement to every layer's controller (reads it back to the host)."""
+        for ctl, row in zip(self.controllers, deltas.tolist()):
+            ctl.observe(dict(zip(SUPPORTED_BITS, row)), ctx_len)
 
     # -- device side, per layer ---------------------------------------------------------------
     def write(self, layer: int, key: torch.Tensor, value: torch.Tensor, meta: StepMeta, capturing: bool = False) -> None:
