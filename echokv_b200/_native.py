@@ -57,6 +57,8 @@ lib = _load()
 lib.echokv_last_error.restype = C.c_char_p
 lib.echokv_decode_scratch_bytes.restype = C.c_int64
 lib.echokv_decode_scratch_bytes.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.c_int32]
+lib.echokv_decode_static_scratch_bytes.restype = C.c_int64
+lib.echokv_decode_static_scratch_bytes.argtypes = []
 lib.echokv_demote_scratch_bytes.restype = C.c_int64
 lib.echokv_demote_scratch_bytes.argtypes = [C.POINTER(Layout), C.c_int64]
 
@@ -73,6 +75,8 @@ _SIGS = {
     "echokv_gather": [_LP, _PP, _RP, _P, _P, _I64, _P, _P, _P],
     "echokv_decode": [_LP, _PP, _RP, _P, _I64, _I64, _I32, _P, _P, _I64, _P, _P, _P, _I64, _P, _I64, _I64, _I32,
                       _F, _I32, _I32, _I64, _I32, _P],
+    "echokv_decode_static": [_LP, _PP, _RP, _P, _I64, _I64, _I32, _P, _P, _I64, _P, _P, _P, _I64, _I64, _I32,
+                             _F, _I32, _I32, _I64, _I32, _P],
     "echokv_dequant_dense": [_LP, _PP, _RP, _P, _I64, _P, _I64, _P, _P, _I64, _I64, _I32, _P],
     "echokv_prefill": [_LP, _PP, _RP, _P, _I64, _I64, _I32, _P, _I64, _I32, _P, _I64, _P, _I64, _I64, _I32, _F,
                        _I32, _P],
@@ -90,7 +94,7 @@ lib.echokv_set_decode_path.restype = C.c_int
 if os.environ.get("ECHOKV_B200_DECODE_PATH"):  # experiments: see echokv_set_decode_path
     lib.echokv_set_decode_path(int(os.environ["ECHOKV_B200_DECODE_PATH"], 0))
 
-EXPORTS = sorted(list(_SIGS) + ["echokv_set_decode_path", "echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
+EXPORTS = sorted(list(_SIGS) + ["echokv_set_decode_path", "echokv_decode_static_scratch_bytes", "echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
                                 "echokv_demote_scratch_bytes"])
 
 

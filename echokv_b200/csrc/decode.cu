@@ -110,4 +110,51 @@ int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const 
   return check_launch("decode merge");
 }
 
+
+// ---- decode without any allocation by the caller ------------------------------------------------
+// Some callers of echokv_decode cannot provide scratch memory: code that runs inside another
+// framework's memory pool with allocation forbidden at that point (for example while that
+// framework is capturing or replaying its own graphs, or in a plugin that is handed only the
+// input and output buffers), or a C host that links this library but not a CUDA allocator.  For
+// them the split partials live in a fixed array inside the library itself.
+#define ECHOKV_STATIC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char g_static_decode_scratch[ECHOKV_STATIC_SCRATCH_BYTES];
+
+int64_t echokv_decode_static_scratch_bytes(void) { return (int64_t)ECHOKV_STATIC_SCRATCH_BYTES; }
+
+int echokv_decode_static(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                         const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype, const int64_t* q_rows,
+                         const int32_t* block_table, int64_t bt_s0, const int64_t* bt_rows, const int64_t* lens,
+                         void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype, float softmax_scale,
+                         int32_t num_splits, int32_t blocks_per_split, int64_t num_seqs, int32_t num_q_heads,
+                         void* stream) {
+  if (num_seqs <= 0) return ECHOKV_OK;
+  if (!layout) return set_error(ECHOKV_E_ARGUMENT, "decode_static: layout is null");
+  const int64_t need = echokv_decode_scratch_bytes(num_seqs, num_q_heads, layout->head_size, num_splits);
+  if (need <= 0 || need > (int64_t)ECHOKV_STATIC_SCRATCH_BYTES)
+    return set_error(ECHOKV_E_UNSUPPORTED,
+                     "decode_static: %lld sequences x %d query heads x %d splits need %lld bytes of split partials, "
+                     "the built-in scratch holds %lld; use echokv_decode with caller-provided scratch",
+                     (long long)num_seqs, num_q_heads, num_splits, (long long)need,
+                     (long long)ECHOKV_STATIC_SCRATCH_BYTES);
+  // The array's name is only a host-side handle; its device address is looked up once per device,
+  // with that device current.
+  constexpr int MAX_DEVICES = 64;
+  static void* device_ptr[MAX_DEVICES] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return set_error(ECHOKV_E_CUDA, "decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= MAX_DEVICES) return set_error(ECHOKV_E_UNSUPPORTED, "decode_static: device index %d", dev);
+  if (!device_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_decode_scratch);
+    if (e != cudaSuccess || !p)
+      return set_error(ECHOKV_E_CUDA, "decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    device_ptr[dev] = p;
+  }
+  return echokv_decode(layout, pages, residual, query, q_s0, q_s1, q_dtype, q_rows, block_table, bt_s0, bt_rows, lens,
+                       device_ptr[dev], (int64_t)ECHOKV_STATIC_SCRATCH_BYTES, out, o_s0, o_s1, out_dtype, softmax_scale,
+                       num_splits, blocks_per_split, num_seqs, num_q_heads, stream);
+}
+
 }  // extern "C"

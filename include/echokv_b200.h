@@ -159,6 +159,26 @@ int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const 
                   float softmax_scale, int32_t num_splits, int32_t blocks_per_split,
                   int64_t num_seqs, int32_t num_q_heads, void* stream);
 
+/* echokv_decode for callers that cannot allocate scratch (it has no counterpart in the reference,
+ * which allocates its split buffers with torch on every call).  Meant for hosts that are not
+ * allowed to allocate device memory where they call this: a plugin running inside another
+ * framework's frozen memory pool, or a plain C host without a CUDA allocator of its own.  The
+ * split partials go to a fixed 8 MiB array inside the library (each GPU that loads the library
+ * holds those 8 MiB until the process exits), so the call is rejected with ECHOKV_E_UNSUPPORTED when
+ * echokv_decode_scratch_bytes(num_seqs, num_q_heads, head_size, num_splits) exceeds
+ * echokv_decode_static_scratch_bytes().  It calls no allocating routine.  The first call on a device
+ * looks up the array's device address (with that device current); make that first call outside
+ * any stream capture.  All calls on a device share the one array: it keeps the previous call's
+ * partials (nothing in it needs to start at zero, every value the merge reads is written first by
+ * the same call), and two calls whose kernels overlap on the GPU (different streams) race on it. */
+int64_t echokv_decode_static_scratch_bytes(void);
+int echokv_decode_static(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                         const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype, const int64_t* q_rows,
+                         const int32_t* block_table, int64_t bt_s0, const int64_t* bt_rows, const int64_t* lens,
+                         void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
+                         float softmax_scale, int32_t num_splits, int32_t blocks_per_split,
+                         int64_t num_seqs, int32_t num_q_heads, void* stream);
+
 /* Kernel selection of echokv_decode: 0 (default) picks the tensor-core kernel when the shape fits
  * (head_size 128, v_group 32, 1/2/4/8 KV heads, <= 8 query heads per KV head) and the generic
  * CUDA-core kernel otherwise; 1 always takes the generic kernel.  Returns the previous setting.
