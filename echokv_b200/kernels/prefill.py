@@ -64,19 +64,63 @@ def build_rows(prefill, req_of, device):
     return packed[0], packed[1], packed[2], (max(lens) if lens else 0)
 
 
+def build_dense(prefill, req_of, block_size: int, device):
+    """Dense-path metadata, once per step for all layers: the dequantization work list, the total
+    context rows, the chunk table ``[n, 4]`` int32 (q_start, q_end, ctx, dense_start) on the device and
+    the longest chunk.  Contexts are packed back to back in ``prefill`` order; the fourth field of the
+    incoming tuples is recomputed, not trusted."""
+    packed, at = [], 0
+    for qs, qe, ctx, _ in prefill:
+        packed.append((qs, qe, ctx, at))
+        at += ctx
+    chunks = to_device(torch.tensor(packed, dtype=torch.int32).reshape(-1, 4), device)
+    return build_dequant_work(packed, req_of, block_size, device), at, chunks, max(qe - qs for qs, qe, _, _ in packed)
+
+
+def dense_attention(query: torch.Tensor, k: torch.Tensor, v: torch.Tensor, chunks: torch.Tensor, max_chunk: int,
+                    out: torch.Tensor, softmax_scale: float) -> None:
+    """Bottom-right causal attention of each chunk's queries over its dense context (``csrc/prefill.cu``).
+    ``query [T, Hq, D]`` and ``k``/``v [total_ctx, H, D]`` share one 16-bit dtype; ``out [T, Hq, D]``."""
+    N.require_cuda(query, k, v, chunks, out)
+    if query.dtype != k.dtype or k.dtype != v.dtype or k.stride() != v.stride():
+        raise ValueError("query, K and V must share a dtype and K, V a layout")
+    if query.stride(2) != 1 or k.stride(2) != 1 or out.stride(2) != 1:
+        raise ValueError("the head dimension must be contiguous")
+    N.check(N.lib.echokv_prefill(
+        query.data_ptr(), query.stride(0), query.stride(1), k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1),
+        N.dtype_code(query.dtype), chunks.data_ptr(), chunks.shape[0], max_chunk, out.data_ptr(), out.stride(0),
+        out.stride(1), N.dtype_code(out.dtype), softmax_scale, query.shape[1], k.shape[1], query.shape[2],
+        N.stream_ptr(query.device)))
+
+
+def dense_supported(store, query: torch.Tensor) -> bool:
+    return query.dtype in (torch.float16, torch.bfloat16) and store.layout.head_size in (64, 128)
+
+
 def prefill_attention(store, query: torch.Tensor, output: torch.Tensor, prefill, req_of, block_table: torch.Tensor,
                       softmax_scale: float, tiles=None, gather=None, dense=None, rows=None) -> None:
     """Write attention for every prefill chunk into ``output [T, Hq, D]``.
 
     ``prefill`` holds ``(q_start, q_end, ctx, dense_start)`` per chunk and ``req_of`` the
-    block-table row of each.  ``rows`` (from ``build_rows``) lets the metadata builder prepare
-    the row path's indices once per step for all layers.
+    block-table row of each.  ``dense`` (from ``build_dense``) selects the dense path; ``rows``
+    (from ``build_rows``) lets the metadata builder prepare the row path's indices once per step
+    for all layers.  With neither, chunks longer than ``ROW_PATH_MAX_CHUNK`` take the dense path
+    when the dtype and head size allow it.  ``tiles`` and ``gather`` belong to the reference's
+    Triton and PyTorch paths and are ignored.
     """
     if not prefill:
+        return
+    out3 = output.view(output.shape[0], -1, query.shape[-1])
+    if dense is None and rows is None and dense_supported(store, query) and \
+            max(qe - qs for qs, qe, _, _ in prefill) > ROW_PATH_MAX_CHUNK:
+        dense = build_dense(prefill, req_of, store.layout.block_size, query.device)
+    if dense is not None and dense_supported(store, query):
+        work, total, chunks, max_chunk = dense
+        k, v = dequant_dense(store, work, total, block_table, query.dtype)
+        dense_attention(query, k, v, chunks, max_chunk, out3, softmax_scale)
         return
     if rows is None:
         rows = build_rows(prefill, req_of, query.device)
     q_rows, reqs, lens, max_len = rows
-    out3 = output.view(output.shape[0], -1, query.shape[-1])
     decode_attention(store, query, block_table, lens, softmax_scale, q_rows=q_rows, bt_rows=reqs, out=out3,
                      max_len=max_len)

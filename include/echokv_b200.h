@@ -193,15 +193,16 @@ int echokv_dequant_dense(const echokv_layout* layout, const echokv_pages* pages,
                          const int32_t* work, int64_t n_work, const int32_t* block_table, int64_t bt_s0,
                          void* k_out, void* v_out, int64_t out_s0, int64_t out_s1, int32_t out_dtype, void* stream);
 
-/* Chunked-prefill attention of query chunks over their whole stored context, bottom-right
- * causal -- prefill_attention (kernels/prefill.py:170-207, oracle :210-236).  `chunks`
- * int32 [n_chunks, 4]: q_start, q_end, ctx, block-table row.  query/out [T, Hq, D]. */
-int echokv_prefill(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
-                   const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype,
-                   const int32_t* chunks, int64_t n_chunks, int32_t max_chunk_len,
-                   const int32_t* block_table, int64_t bt_s0,
-                   void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
-                   float softmax_scale, int32_t num_q_heads, void* stream);
+/* Chunked-prefill attention over dense contexts: the attention step of the dense path of
+ * prefill_attention (kernels/prefill.py:118-167; the reference calls a flash-attention library
+ * there, :145-153; oracle :210-236).  k_dense / v_dense [total_ctx, H, D] are what
+ * echokv_dequant_dense wrote, in the query's dtype (float16 or bfloat16).  `chunks` int32
+ * [n_chunks, 4] (16-byte aligned): q_start, q_end, ctx, dense row of the context's first key.
+ * Query i of a chunk of nq sees keys 0 .. ctx - nq + i.  query/out [T, Hq, D]; head_size 64 or 128. */
+int echokv_prefill(const void* query, int64_t q_s0, int64_t q_s1, const void* k_dense, const void* v_dense,
+                   int64_t kv_s0, int64_t kv_s1, int32_t dtype, const int32_t* chunks, int64_t n_chunks,
+                   int32_t max_chunk_len, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
+                   float softmax_scale, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_size, void* stream);
 
 /* Canary attention-KL estimator, batched over layers -- canary_kl (canary.py:59-89).
  * query [L, nq, Hq, D] of q_dtype, kref float32 [L, W, H, D] oldest key first (ring
