@@ -30,7 +30,6 @@ namespace mma {
 constexpr int D = 128;          // head size of this kernel
 constexpr int NG = 4;           // V groups per head (v_group 32)
 constexpr int TILE = 16;        // tokens per tile
-constexpr int MAX_STAGES = 24;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;  // bounded spin on every mbarrier wait
 
 struct StageInfo {
@@ -41,17 +40,15 @@ struct StageInfo {
   long long res_slot;
 };
 
-// One published tile: what to copy and how to read it.
-struct alignas(16) TileDesc {  // 16-byte aligned: the four leading ints are read with one 128-bit load
-  int bits, n_valid, in_res, pos0;   // n_valid: 1..16 tokens, 0 = skip (tier above the bound), -1 = end of work
+// What the producer tells the consumers about a staged tile (stored at `o_hdr` of the stage).
+struct alignas(16) StageHeader {
+  int bits, n_valid, in_res, pos0;   // n_valid: 1..16 tokens, 0 = skip (tier above the caller's bound)
   long long res_slot;
-  const unsigned char *vs_src, *vm_src, *ks_src, *km_src;
-  const unsigned char* row_src[TILE];
+  long long pad;
 };
-constexpr int ND = 32;  // descriptor ring slots (one per lane of the descriptor warp)
-constexpr int HDR_BYTES = 1024;  // 2 * ND mbarriers + the remap lock
-static_assert(2 * ND * 8 + 4 <= HDR_BYTES, "barriers and lock must fit the header");
-static_assert(sizeof(TileDesc) % 16 == 0, "descriptor slots must stay 16-byte aligned");
+constexpr int MAX_NS = 8;        // stage ring slots at most
+constexpr int HDR_BYTES = 256;   // 2 * MAX_NS mbarriers + the remap lock
+static_assert(2 * MAX_NS * 8 + 4 <= HDR_BYTES, "barriers and lock must fit the header");
 
 struct Params {
   LayoutDev L;
@@ -59,7 +56,7 @@ struct Params {
   const uint8_t* pages;
   DecodeArgs A;
   int H, NS, max_bits, num_seqs;
-  int stage_bytes, o_vs, o_vm, o_ks, o_km;  // stage layout (bytes from the stage base)
+  int stage_bytes, o_vs, o_vm, o_ks, o_km, o_hdr;  // stage layout (bytes from the stage base)
   int* status;                             // device status word (0 ok), may be null
   int q_vec16;                             // 16-bit queries whose rows can be read with 16-byte loads
   int debug;                               // experiments only: 1 skip the math, 2 skip the copies
@@ -91,12 +88,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
   return false;
 }
-__device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+// The same bounded wait for a thread that expects to wait long (the producer is usually a whole
+// ring ahead): each try may suspend the thread for up to `ns` nanoseconds instead of spinning.
+__device__ __forceinline__ bool mbar_wait_long(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  const uint32_t a = smem_u32(bar);
+  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(a), "r"(parity), "r"(ns) : "memory");
+    if (ok) return true;
+  }
+  return false;
 }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 // Compile-time loop: the index is an integral constant, so it can feed template arguments.
 template <class F, int... I>
@@ -224,7 +233,6 @@ template <> struct Unpack<2> {
 // that sit in mantissa bits 0..7, 64 for nibbles in bits 4..7) and the offsets are cancelled
 // exactly by a twin MMA whose A operand is the constant -OFF (products are exact in the fp32
 // accumulator), which is cheaper than one fp16 subtract per pair.
-constexpr uint32_t H2_N1024 = 0xe400e400u, H2_N64 = 0xd400d400u;
 __device__ __forceinline__ void raw8(uint32_t w, uint32_t (&o)[2]) {
   o[0] = prmt(w, 0x64646464u, 0x4140u);
   o[1] = prmt(w, 0x64646464u, 0x4342u);
@@ -253,7 +261,6 @@ __device__ __forceinline__ int acc_channel(int mt, int r, int half) {
 // that the 128-bit fragment loads of two neighbouring rows fall into different bank halves.
 constexpr int QT_ROW = D * 2 + 64;   // tier copy: rows padded so 128-bit fragment loads of two rows hit different bank halves
 constexpr int QN_ROW = D * 2 + 16;   // natural copy: rows padded for ldmatrix over the 8 query rows
-constexpr int Q_ROWS_MAX = 9;          // up to 8 query heads per KV head + one shared zero row
 __host__ __device__ constexpr int q_head_bytes(int rows) { return rows * (QT_ROW + QN_ROW); }
 constexpr int REMAP_ROW = D + 4;                      // floats per query head in the canonical layout
 constexpr int REMAP_BYTES = 8 * REMAP_ROW * 4;
@@ -634,16 +641,16 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
 // ---- the kernel ------------------------------------------------------------------------------
 // Persistent: CTA c walks the work items c, c + gridDim.x, ... in split-major order (item =
 // split * num_seqs + seq), so neighbouring CTAs work on different sequences of similar length and
-// the short tail splits come last.  H consumer warps (one per KV head) + one descriptor warp.
+// the short tail splits come last.  H consumer warps (one per KV head) + one producer warp.
 //
-// The descriptor warp runs ahead of the consumers: it resolves block table -> page header ->
-// chunk ids -> residual map for up to 32 blocks at a time (the dependent global loads of the next
-// batch are in flight while the current one is consumed) and publishes one TileDesc per 16-token
-// tile in a small ring.  The consumers stream the data themselves: all their threads issue
-// 16-byte cp.async copies for tile t + NS - 1 into the stage ring (token rows padded by 16 bytes
-// so ldmatrix over 8 rows is conflict free) and then compute tile t, with one named barrier per
-// tile.  Spreading the copies over every warp keeps enough loads in flight; a single issuing
-// warp (or one bulk-copy request per token row) could not.
+// The producer warp runs ahead of the consumers.  It resolves block table -> page header -> chunk
+// ids -> residual map for up to 32 blocks at a time, one block per lane (the dependent global
+// loads of the next batch are in flight while the current one is worked off), and then feeds the
+// stage ring tile by tile: wait until every consumer warp has released the stage, write the tile's
+// header, and start the tile's copies as bulk asynchronous copies that report their bytes to the
+// stage's `full` mbarrier -- lane t copies token row t (to a slot padded by 16 bytes so ldmatrix over
+// 8 rows is conflict free), lanes 16.. copy the V / K stats.  Consumers only wait for `full`,
+// compute, and arrive on `empty`; there is no CTA-wide barrier in the loop.
 __device__ __forceinline__ bool item_range(const Params& P, int item, int& seq, int& split, int64_t& seq_len,
                                            int& b_start, int& b_end) {
   seq = item % P.num_seqs;
@@ -702,30 +709,6 @@ __device__ __forceinline__ void write_partial(const Params& P, const WarpState& 
   }
 }
 
-// Named barrier 1 over the consumer threads that also ORs a per-thread flag: every thread learns
-// whether any of them gave up on a wait, so they all leave the pipeline at the same point.
-__device__ __forceinline__ bool bar_or(int nthreads, bool flag) {
-  uint32_t any;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.or.pred p, 1, %2, q;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(any) : "r"((uint32_t)flag), "r"(nthreads) : "memory");
-  return any != 0;
-}
-
-__device__ __forceinline__ void cp_wait(int pending) {  // wait until at most `pending` groups are in flight
-  switch (pending) {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-  }
-}
-
 template <int H>
 __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H == 2 ? 5 : 8))) decode_mma_kernel(const Params P) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -733,21 +716,19 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
   const DecodeArgs& A = P.A;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int NS = P.NS;
-  constexpr int N_CONS = H * 32;
   const int n_items = P.num_seqs * A.num_splits;
 
-  // shared memory: [barriers | lock][descriptors][remap][q copies per head][stage ring]
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  uint64_t* empty = full + ND;
-  int* lock = reinterpret_cast<int*>(empty + ND);
-  TileDesc* desc = reinterpret_cast<TileDesc*>(smem + HDR_BYTES);
-  float* remap = reinterpret_cast<float*>(smem + HDR_BYTES + ND * sizeof(TileDesc));
+  // shared memory: [barriers | lock][remap][q copies per head][stage ring]
+  uint64_t* sfull = reinterpret_cast<uint64_t*>(smem);   // stage ring: header written, copies landed
+  uint64_t* sempty = sfull + MAX_NS;                     // stage ring: every consumer warp is done with the stage
+  int* lock = reinterpret_cast<int*>(sempty + MAX_NS);
+  float* remap = reinterpret_cast<float*>(smem + HDR_BYTES);
   unsigned char* qs = reinterpret_cast<unsigned char*>(remap) + REMAP_BYTES;
   const int q_rows = A.gqa + 1;
   unsigned char* ring = qs + H * q_head_bytes(q_rows);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < ND; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, H); }
+    for (int s = 0; s < MAX_NS; ++s) { mbar_init(sfull + s, 1); mbar_init(sempty + s, H); }
     *lock = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -755,19 +736,20 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
     const int n16 = (NS * P.stage_bytes) / 16;
     uint4* z = reinterpret_cast<uint4*>(ring);
     for (int i = threadIdx.x; i < n16; i += (H + 1) * 32) z[i] = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the bulk copies write the same bytes later
   }
   __syncthreads();
 
   bool ok = true, bad_tier = false;
   if (warp == H) {
-    if (P.debug == 3) return;  // experiment: consumers make up their own addresses
-    // ===================== descriptor warp =====================
-    // Lane-parallel: a unit is the next <= 32 tiles of an item; lane l resolves tile l of the unit
-    // (its block's metadata comes by shuffle from the lane that loaded it) and publishes it in its
-    // own ring slot, so a whole unit costs about as many instructions as one tile would serially.
+    // ===================== producer warp =====================
     const int tpb = L.BS / TILE;                     // tiles per block
-    const int U = tpb >= 32 ? 1 : 32 / tpb;          // blocks per unit
-    int tile = 0;                                    // tiles published by this CTA so far
+    const int U = tpb >= 32 ? 1 : 32 / tpb;          // blocks per unit (a unit is at most 32 tiles)
+    const bool contig = L.BS == TILE && L.KG == TILE;  // a tile's four stats arrays form one run in the page
+    const uint32_t ring_u = smem_u32(ring);
+    int st = 0, round = 0;                           // next stage to fill and how often it has been filled
+    uint32_t st_u = ring_u;
+    int issued = 0;
     int item = blockIdx.x, seq = 0, split = 0, b_start = 0, b_end = 0, base = 0;
     int64_t seq_len = 0, bt_row = 0;
     bool have = false;
@@ -794,65 +776,87 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
       // tokens of the unit: all blocks are full except possibly the item's last one
       const int unit_tok = (int)min((int64_t)nb * L.BS, u_len - (int64_t)u_base * L.BS);
       const int unit_tiles = (unit_tok + TILE - 1) / TILE;
-      const int kb = lane / tpb, tb = lane - kb * tpb;   // this lane's block within the unit, tile within the block
-      const int kblk = __shfl_sync(0xffffffffu, cur.blk, kb);
-      int bits = __shfl_sync(0xffffffffu, cur.bits, kb);
-      const int c1 = __shfl_sync(0xffffffffu, cur.c1, kb), c2 = __shfl_sync(0xffffffffu, cur.c2, kb),
-                c3 = __shfl_sync(0xffffffffu, cur.c3, kb);
-      const long long ks_slot = __shfl_sync(0xffffffffu, cur.rslot, kb);
-      const int kgrp = __shfl_sync(0xffffffffu, cur.rgrp, kb);
-      if (lane < unit_tiles) {
-        const int my_tile = tile + lane;
-        const int slot = my_tile % ND;
-        if (my_tile >= ND && !mbar_wait(empty + slot, ((my_tile / ND) - 1) & 1)) ok = false;
-        if (ok) {
-          if (bits != 2 && bits != 4 && bits != 8) bits = 2;  // never opened: stay inside the page
-          const bool too_wide = bits > P.max_bits;             // the caller's tier bound was wrong
-          if (too_wide) { bits = P.max_bits; bad_tier = true; }  // such tiles are published empty
-          const int row_bytes = 32 * H * bits;
-          const int tpc = (2 * L.BS) / bits;
-          const int t0 = tb * TILE;
-          const int blk_tok = min(L.BS, unit_tok - kb * L.BS);
-          const int grp = t0 / L.KG;
+      int tiles_left = unit_tiles;
+      for (int kb = 0; kb < nb && ok; ++kb) {  // blocks of the unit; the block's metadata sits in lane kb
+        const int kblk = __shfl_sync(0xffffffffu, cur.blk, kb);
+        int bits = __shfl_sync(0xffffffffu, cur.bits, kb);
+        const int c1 = __shfl_sync(0xffffffffu, cur.c1, kb), c2 = __shfl_sync(0xffffffffu, cur.c2, kb),
+                  c3 = __shfl_sync(0xffffffffu, cur.c3, kb);
+        const long long ks_slot = __shfl_sync(0xffffffffu, cur.rslot, kb);
+        const int kgrp = __shfl_sync(0xffffffffu, cur.rgrp, kb);
+        if (bits != 2 && bits != 4 && bits != 8) bits = 2;  // never opened: stay inside the page
+        const bool too_wide = bits > P.max_bits;             // the caller's tier bound was wrong
+        if (too_wide) { bits = P.max_bits; bad_tier = true; }  // such tiles are staged empty
+        const uint32_t row_bytes = 32u * H * bits;
+        const int tpc = (2 * L.BS) / bits;                    // tokens per chunk (a multiple of 4: block_size % 16 == 0)
+        const int blk_tok = min(L.BS, unit_tok - kb * L.BS);
+        const unsigned char* page = P.pages + (int64_t)kblk * L.PS;
+        // this lane's token row of the block's first tile: chunk index and position inside the chunk
+        int jc = 0, in_chunk = lane;
+        while (in_chunk >= tpc) { in_chunk -= tpc; ++jc; }
+        int t0 = 0, grp = 0, g_pos = 0;                       // first token of the tile, its K group, position in the group
+        const int n_bt = min(tpb, tiles_left);
+        for (int tb = 0; tb < n_bt && ok; ++tb) {
+          const int n_valid = too_wide ? 0 : min(TILE, blk_tok - t0);
           const bool in_res = ks_slot >= 0 && grp == kgrp;
-          const unsigned char* page = P.pages + (int64_t)kblk * L.PS;
-          TileDesc& d = desc[slot];
-          int jc = t0 / tpc, in_chunk = t0 - jc * tpc;      // chunk of the tile's first token, position inside it
-          const unsigned char* chunk = nullptr;
-          for (int t = 0; t < TILE; ++t) {
-            if (t == 0 || in_chunk == tpc) {
-              if (t) { ++jc; in_chunk = 0; }
-              int64_t pg = kblk, cs = 0;
-              if (jc > 0) { const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3); pg = id / L.KC; cs = id - pg * L.KC; }
-              chunk = P.pages + pg * L.PS + L.o_data + cs * L.CB;
-            }
-            d.row_src[t] = chunk + (int64_t)in_chunk * row_bytes;
-            ++in_chunk;
+          if (round > 0 && !(P.debug & 4 ? mbar_wait(sempty + st, (round - 1) & 1)
+                                         : mbar_wait_long(sempty + st, (round - 1) & 1, 500u))) { ok = false; break; }
+          const uint32_t bar = smem_u32(sfull + st);
+          const bool copy = n_valid > 0 && (P.debug & 3) != 2;
+          if (lane == 0) {
+            StageHeader* hd = reinterpret_cast<StageHeader*>(ring + (size_t)st * P.stage_bytes + P.o_hdr);
+            *reinterpret_cast<int4*>(hd) = make_int4(bits, n_valid, in_res ? 1 : 0, g_pos);
+            hd->res_slot = ks_slot;
+            if (copy) mbar_expect_tx(sfull + st, n_valid * row_bytes + H * (2 * TILE * NG * 2 + 2 * D * 2));
+            else mbar_arrive(sfull + st);
           }
-          const bool contig = L.BS == TILE && L.KG == TILE;  // the tile's four stats arrays form one run
-          d.bits = bits; d.n_valid = too_wide ? 0 : min(TILE, blk_tok - t0);
-          d.in_res = (in_res ? 1 : 0) | (contig ? 2 : 0);
-          d.pos0 = t0 % L.KG; d.res_slot = ks_slot;
-          d.vs_src = page + L.o_vs + (int64_t)t0 * H * NG * 2;
-          d.vm_src = page + L.o_vm + (int64_t)t0 * H * NG * 2;
-          d.ks_src = page + L.o_ks + (int64_t)grp * H * D * 2;
-          d.km_src = page + L.o_km + (int64_t)grp * H * D * 2;
-          mbar_arrive(full + slot);
+          __syncwarp();
+          if (copy) {
+            if (lane < n_valid) {  // token row `lane` of the tile
+              int64_t pg = kblk, cs = 0;
+              if (jc > 0) {
+                const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3);
+                const int q = L.KC == 4 ? id >> 2 : (L.KC == 2 ? id >> 1 : (L.KC == 1 ? id : id / 3));
+                pg = q; cs = id - q * L.KC;
+              }
+              bulk_copy(st_u + lane * (row_bytes + 16), P.pages + pg * L.PS + L.o_data + cs * L.CB + (int64_t)in_chunk * row_bytes,
+                        row_bytes, bar);
+            } else if (contig) {
+              if (lane == 16) bulk_copy(st_u + P.o_vs, page + L.o_vs, H * (2 * TILE * NG * 2 + 2 * D * 2), bar);
+            } else if (lane >= 16 && lane < 20) {
+              const int which = lane - 16;  // vs, vm, ks, km
+              const bool isv = which < 2;
+              const int64_t src_off = (which == 0 ? L.o_vs : which == 1 ? L.o_vm : which == 2 ? L.o_ks : L.o_km) +
+                                      (isv ? (int64_t)t0 * H * NG * 2 : (int64_t)grp * H * D * 2);
+              const int dst_off = which == 0 ? P.o_vs : which == 1 ? P.o_vm : which == 2 ? P.o_ks : P.o_km;
+              bulk_copy(st_u + dst_off, page + src_off, isv ? H * TILE * NG * 2 : H * D * 2, bar);
+            }
+          }
+          ++issued;
+          if (++st == NS) { st = 0; st_u = ring_u; ++round; } else { st_u += P.stage_bytes; }
+          // next tile of the block
+          t0 += TILE;
+          in_chunk += TILE;
+          while (in_chunk >= tpc) { in_chunk -= tpc; ++jc; }
+          g_pos += TILE;
+          if (g_pos >= L.KG) { g_pos = 0; ++grp; }
         }
+        tiles_left -= n_bt;
       }
-      tile += unit_tiles;
       ok = !__any_sync(0xffffffffu, !ok);
     }
-    if (ok && lane == 0) {  // terminal descriptor: no more tiles for this CTA
-      const int slot = tile % ND;
-      if (tile < ND || mbar_wait(empty + slot, ((tile / ND) - 1) & 1)) { desc[slot].n_valid = -1; mbar_arrive(full + slot); }
-      else ok = false;
+    if (!ok) {
+      // A wait gave up: copies already started may still be landing; give each stage its (bounded)
+      // time before the CTA's shared memory goes away.
+      for (int s = 0; s < NS; ++s) {
+        const int uses = issued > s ? (issued - s + NS - 1) / NS : 0;
+        if (uses > 0) mbar_wait(sfull + s, (uses - 1) & 1);
+      }
     }
   } else {
     // ===================== consumers: warp h owns KV head h =====================
     const int h = warp;
     const int r = lane >> 2;
-    const int tid = threadIdx.x;  // 0 .. N_CONS - 1
     QView qv;
     qv.rows = q_rows;
     qv.qn = qs + h * q_head_bytes(q_rows);
@@ -867,82 +871,9 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
     const LaneConst lc = lane_const(H, h, lane);
     const uint32_t ring_u = smem_u32(ring);
     const uint32_t stage_bytes = P.stage_bytes;
-    const uint32_t stats_off = P.o_vs;  // [vs | vm | ks | km] are contiguous in a stage
-    constexpr int STAT16 = (2 * TILE * H * NG * 2 + 2 * H * D * 2) / 16;  // 16-byte pieces of a tile's stats
-    constexpr int TOK_PER_WARP = TILE / H > 0 ? TILE / H : 1;
-    bool ended = false;
-    // issue side of the stage pipeline: slot counters advance without divisions
-    int is_st = 0, is_ds = 0, is_par = 0;   // stage / descriptor slot / descriptor parity of the next tile to issue
-    uint32_t is_sb = ring_u;
-    // Issue this thread's share of the copies of the next tile (or an empty group past the end).
-    int dbg_issued = 0, dbg_total = 0;
-    if (P.debug == 3) {
-      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-        int seq, split, b_start, b_end; int64_t seq_len;
-        if (item_range(P, item, seq, split, seq_len, b_start, b_end))
-          dbg_total += (int)((min(seq_len, (int64_t)b_end * L.BS) - (int64_t)b_start * L.BS + TILE - 1) / TILE);
-      }
-    }
-    auto issue = [&]() {
-      if (P.debug == 3) {  // experiment: synthetic INT4 tile addresses, no descriptor handshake
-        if (dbg_issued < dbg_total) {
-          const int64_t blk = ((int64_t)(blockIdx.x * 977 + dbg_issued * 131) % L.NB);
-          const unsigned char* pg = P.pages + blk * L.PS;
-          const unsigned char* pg2 = P.pages + ((blk * 7 + 3) % L.NB) * L.PS;
-          const uint32_t row_bytes = 32u * H * 4;
-#pragma unroll
-          for (int k = 0; k < TOK_PER_WARP; ++k) {
-            const int t = h + k * H;
-            const unsigned char* src = (t < 8 ? pg + L.o_data + t * row_bytes : pg2 + L.o_data + 8192 + (t - 8) * row_bytes) + lane * 16;
-            const uint32_t dst = is_sb + t * (row_bytes + 16) + lane * 16;
-            for (uint32_t o = lane * 16; o < row_bytes; o += 512) cp_async16(dst + (o - lane * 16), src + (o - lane * 16));
-          }
-          for (int i = tid; i < STAT16; i += N_CONS) cp_async16(is_sb + stats_off + i * 16, pg + L.o_vs + i * 16);
-        }
-        ++dbg_issued;
-      } else
-      if (!ended && ok) {
-        if (!mbar_wait(full + is_ds, is_par)) ok = false;
-        const TileDesc& d = desc[is_ds];
-        const int4 hd = *reinterpret_cast<const int4*>(&d);  // bits, n_valid, in_res, pos0
-        if (ok && hd.y < 0) ended = true;
-        if (ok && !ended && P.debug != 2) {
-          const uint32_t row_bytes = 32u * H * hd.x;
-          // token rows: warp h copies tokens h, h + H, ... (each row to its padded slot)
-#pragma unroll
-          for (int k = 0; k < TOK_PER_WARP; ++k) {
-            const int t = h + k * H;
-            if (t < hd.y) {
-              const unsigned char* src = d.row_src[t] + lane * 16;
-              const uint32_t dst = is_sb + t * (row_bytes + 16) + lane * 16;
-              for (uint32_t o = lane * 16; o < row_bytes; o += 512) cp_async16(dst + (o - lane * 16), src + (o - lane * 16));
-            }
-          }
-          // stats: when the tile is a whole block of 16 tokens the four arrays are one contiguous run
-          if (hd.z & 2) {
-            for (int i = tid; i < STAT16; i += N_CONS) cp_async16(is_sb + stats_off + i * 16, d.vs_src + i * 16);
-          } else {
-            constexpr int NV = (TILE * H * NG * 2) / 16, NK = (H * D * 2) / 16;
-            for (int i = tid; i < NV; i += N_CONS) {
-              cp_async16(is_sb + P.o_vs + i * 16, d.vs_src + i * 16);
-              cp_async16(is_sb + P.o_vm + i * 16, d.vm_src + i * 16);
-            }
-            for (int i = tid; i < NK; i += N_CONS) {
-              cp_async16(is_sb + P.o_ks + i * 16, d.ks_src + i * 16);
-              cp_async16(is_sb + P.o_km + i * 16, d.km_src + i * 16);
-            }
-          }
-        }
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      if (++is_st == NS) { is_st = 0; is_sb = ring_u; } else { is_sb += stage_bytes; }
-      if (++is_ds == ND) { is_ds = 0; is_par ^= 1; }
-    };
-    for (int x = 0; x < NS - 1; ++x) issue();  // prologue: NS - 1 tiles in flight
-    int c_st = 0, c_ds = 0;                      // stage / descriptor slot of the tile being consumed
+    int c_st = 0, c_round = 0;                  // stage being consumed and how often it has been consumed
     uint32_t c_sb = ring_u;
-    bool stop = false;  // uniform over the consumer threads (decided at the per-tile barrier)
-    for (int item = blockIdx.x; item < n_items && !stop; item += gridDim.x) {
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       int seq, split, b_start, b_end;
       int64_t seq_len;
       if (!item_range(P, item, seq, split, seq_len, b_start, b_end)) continue;
@@ -995,36 +926,35 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
       w.m0 = w.m1 = -INFINITY;
       w.bits = 0;
       w.qbits = 0;
-      for (int t = 0; t < n_tiles; ++t) {
-        cp_wait(NS - 2);                 // this thread's copies of the tile have landed
-        stop = bar_or(N_CONS, !ok);      // ... and everyone's; all warps are done with the previous tile
-        if (stop) break;
-        issue();                         // refill the stage the previous tile used
-        const TileDesc& d = desc[c_ds];
-        const int4 hd = *reinterpret_cast<const int4*>(&d);
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        if (!mbar_wait(sfull + c_st, c_round & 1)) { ok = false; break; }  // header written, copies landed
         StageInfo si;
-        si.bits = hd.x; si.n_valid = hd.y; si.in_res = hd.z & 1; si.pos0 = hd.w; si.res_slot = d.res_slot;
+        {
+          uint32_t hd[4];
+          lds128<0>(hd, c_sb + P.o_hdr);
+          si.bits = (int)hd[0]; si.n_valid = (int)hd[1]; si.in_res = (int)hd[2]; si.pos0 = (int)hd[3];
+          const uint2 rs = lds64<16>(c_sb + P.o_hdr);
+          si.res_slot = (long long)(((unsigned long long)rs.y << 32) | rs.x);
+        }
         TileView tv;
         tv.krow = c_sb + (si.bits == 8 ? lc.k8 : (si.bits == 4 ? lc.k4 : lc.k2));
         tv.vrow = c_sb + (si.bits == 8 ? lc.v8 : (si.bits == 4 ? lc.v4 : lc.v2));
         tv.vs = c_sb + P.o_vs + lc.vs_off; tv.vm = c_sb + P.o_vm + lc.vm_off;
         tv.ks = c_sb + P.o_ks + lc.ksm_off; tv.km = c_sb + P.o_km + lc.ksm_off; tv.tok = lc.tok;
-        if (si.n_valid > 0 && P.debug != 1 && P.debug != 3) {
+        if (si.n_valid > 0 && (P.debug & 3) != 1) {
           if (si.bits == 4) process_tile<4>(P, tv, si, qv, h, lane, w, remap, lock, ok);
           else if (si.bits == 8) process_tile<8>(P, tv, si, qv, h, lane, w, remap, lock, ok);
           else process_tile<2>(P, tv, si, qv, h, lane, w, remap, lock, ok);
         }
         __syncwarp();
-        if (lane == 0 && P.debug != 3) mbar_arrive(empty + c_ds);
-        if (++c_st == NS) { c_st = 0; c_sb = ring_u; } else { c_sb += stage_bytes; }
-        if (++c_ds == ND) c_ds = 0;
+        if (lane == 0) mbar_arrive(sempty + c_st);
+        if (++c_st == NS) { c_st = 0; c_sb = ring_u; ++c_round; } else { c_sb += stage_bytes; }
       }
-      if (stop) break;
+      if (!ok) break;
       if (w.bits == 4) write_partial<4>(P, w, seq, split, h, lane);
       else if (w.bits == 8) write_partial<8>(P, w, seq, split, h, lane);
       else write_partial<2>(P, w, seq, split, h, lane);
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
   if ((!ok || bad_tier) && lane == 0 && P.status) atomicExch(P.status, bad_tier ? 2 : 1);
 }
@@ -1040,7 +970,7 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   *handled = false;
   if ((g_decode_path & 15) == 1) return ECHOKV_OK;
   const int H = L.H;
-  if (L.D != D || L.VG != 32 || L.KG % TILE || L.BS % TILE || L.BS > 32 * TILE || A.gqa > 8) return ECHOKV_OK;
+  if (L.D != D || L.VG != 32 || L.KG % TILE || L.BS % TILE || A.gqa > 8) return ECHOKV_OK;
   if (!(H == 1 || H == 2 || H == 4 || H == 8)) return ECHOKV_OK;
   if ((R.s_slot | R.s_pos | R.s_head) & 3) return ECHOKV_OK;                 // 8-byte residual loads
   if ((reinterpret_cast<uintptr_t>(R.base) & 15) != 0) return ECHOKV_OK;
@@ -1056,12 +986,12 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   P.o_vm = P.o_vs + TILE * H * NG * 2;
   P.o_ks = P.o_vm + TILE * H * NG * 2;
   P.o_km = P.o_ks + H * D * 2;
-  P.stage_bytes = (P.o_km + H * D * 2 + 127) / 128 * 128;
+  P.o_hdr = P.o_km + H * D * 2;
+  P.stage_bytes = (P.o_hdr + (int)sizeof(StageHeader) + 127) / 128 * 128;
   P.status = status;
   P.q_vec16 = (A.q_dt != ECHOKV_DT_F32) && (reinterpret_cast<uintptr_t>(A.q) % 16 == 0) && A.q_s0 % 8 == 0 && A.q_s1 % 8 == 0;
   P.debug = (g_decode_path >> 4) & 15;
-  if (P.debug == 3 && P.max_bits < 4) P.debug = 0;  // the synthetic-address experiment copies INT4-sized rows
-  const int fixed = HDR_BYTES + ND * (int)sizeof(TileDesc) + REMAP_BYTES + H * q_head_bytes(A.gqa + 1);
+  const int fixed = HDR_BYTES + REMAP_BYTES + H * q_head_bytes(A.gqa + 1);
   static int max_smem = -1, num_sms = 0;
   if (max_smem < 0) {
     int dev = 0;
