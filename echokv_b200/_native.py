@@ -15,7 +15,8 @@ from pathlib import Path
 import torch
 
 _HERE = Path(__file__).resolve().parent
-LIB_PATH = _HERE / "libechokv_b200.so"
+# ECHOKV_B200_LIB names another build of the same sources to load instead (e.g. an instrumented one).
+LIB_PATH = Path(os.environ["ECHOKV_B200_LIB"]) if os.environ.get("ECHOKV_B200_LIB") else _HERE / "libechokv_b200.so"
 
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2
 _DT = {torch.float32: DT_F32, torch.float16: DT_F16, torch.bfloat16: DT_BF16}

@@ -5,7 +5,7 @@ using namespace echokv;
 
 namespace echokv {
 int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
-                      int64_t num_seqs, int max_tier, int* status, cudaStream_t st, bool* handled);
+                      int64_t num_seqs, int max_tier, int* counter, int* status, cudaStream_t st, bool* handled);
 
 // out[q_rows[seq], head] = splits merged in split order (kernels/decode.py:226-262).
 __global__ void decode_merge_kernel(DecodeArgs A, int BS, int D) {
@@ -54,7 +54,9 @@ extern "C" {
 
 int64_t echokv_decode_scratch_bytes(int64_t num_seqs, int32_t num_q_heads, int32_t head_size, int32_t num_splits) {
   if (num_seqs <= 0 || num_q_heads <= 0 || head_size <= 0 || num_splits <= 0) return 0;
-  return num_seqs * num_q_heads * (int64_t)num_splits * (head_size + 2) * (int64_t)sizeof(float);
+  // split partials (accumulators + running max / sum), then 256 bytes of work-queue state
+  const int64_t partials = num_seqs * num_q_heads * (int64_t)num_splits * (head_size + 2) * (int64_t)sizeof(float);
+  return (partials + 15) / 16 * 16 + 256;
 }
 
 int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
@@ -92,7 +94,9 @@ int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const 
   const uint8_t* pg = (const uint8_t*)pages->base;
 
   bool handled = false;
-  rc = launch_decode_mma(L, R, pg, A, num_seqs, pages->max_tier, nullptr, st, &handled);
+  int* counter = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(scratch) +
+                                        echokv_decode_scratch_bytes(num_seqs, num_q_heads, L.D, num_splits) - 256);
+  rc = launch_decode_mma(L, R, pg, A, num_seqs, pages->max_tier, counter, nullptr, st, &handled);
   if (rc) return rc;
   if (!handled) {
     dim3 grid((unsigned)num_seqs, (unsigned)L.H, (unsigned)num_splits);

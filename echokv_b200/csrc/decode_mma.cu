@@ -27,6 +27,15 @@
 namespace echokv {
 namespace mma {
 
+#ifdef ECHOKV_PROFILE
+__device__ long long g_prof[1024 * 8];
+#define PROF_T(x) const long long x = clock64()
+#define PROF_ADD(acc, a, b) acc += (b) - (a)
+#else
+#define PROF_T(x)
+#define PROF_ADD(acc, a, b)
+#endif
+
 constexpr int D = 128;          // head size of this kernel
 constexpr int NG = 4;           // V groups per head (v_group 32)
 constexpr int TILE = 16;        // tokens per tile
@@ -41,13 +50,22 @@ struct StageInfo {
 };
 
 // What the producer tells the consumers about a staged tile (stored at `o_hdr` of the stage).
+constexpr int F_RES = 1, F_FIRST = 2, F_LAST = 4;  // K from the residual buffer / first / last tile of a work item
 struct alignas(16) StageHeader {
-  int bits, n_valid, in_res, pos0;   // n_valid: 1..16 tokens, 0 = skip (tier above the caller's bound)
+  int bits, n_valid, flags, pos0;   // n_valid: 1..16 tokens, 0 = skip (tier above the caller's bound), -1 = no more work
   long long res_slot;
-  long long pad;
+  int seq, split;
 };
+// The producer's own notes for one tile of the unit it is working off: the header and every copy source.
+struct alignas(16) TilePlan {
+  StageHeader hdr;
+  const unsigned char* stats[4];    // V scale, V min, K scale, K min of the tile (one run from stats[0] when contiguous)
+  const unsigned char* row_src[TILE];
+};
+constexpr int UNIT = 32;         // tiles planned at a time (one per producer lane)
 constexpr int MAX_NS = 8;        // stage ring slots at most
 constexpr int HDR_BYTES = 256;   // 2 * MAX_NS mbarriers + the remap lock
+static_assert(sizeof(StageHeader) == 32 && sizeof(TilePlan) % 16 == 0, "16-byte copies of headers");
 static_assert(2 * MAX_NS * 8 + 4 <= HDR_BYTES, "barriers and lock must fit the header");
 
 struct Params {
@@ -58,6 +76,7 @@ struct Params {
   int H, NS, max_bits, num_seqs;
   int stage_bytes, o_vs, o_vm, o_ks, o_km, o_hdr;  // stage layout (bytes from the stage base)
   int* status;                             // device status word (0 ok), may be null
+  int* counter;                            // next unclaimed work item (zero at launch)
   int q_vec16;                             // 16-bit queries whose rows can be read with 16-byte loads
   int debug;                               // experiments only: 1 skip the math, 2 skip the copies
 };
@@ -84,21 +103,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(a), "r"(parity) : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-// The same bounded wait for a thread that expects to wait long (the producer is usually a whole
-// ring ahead): each try may suspend the thread for up to `ns` nanoseconds instead of spinning.
-__device__ __forceinline__ bool mbar_wait_long(uint64_t* bar, uint32_t parity, uint32_t ns) {
-  const uint32_t a = smem_u32(bar);
-  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(a), "r"(parity), "r"(ns) : "memory");
     if (ok) return true;
   }
   return false;
@@ -639,18 +643,21 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
 }
 
 // ---- the kernel ------------------------------------------------------------------------------
-// Persistent: CTA c walks the work items c, c + gridDim.x, ... in split-major order (item =
-// split * num_seqs + seq), so neighbouring CTAs work on different sequences of similar length and
-// the short tail splits come last.  H consumer warps (one per KV head) + one producer warp.
+// Persistent CTAs claim work items (item = split * num_seqs + seq, so neighbouring CTAs work on
+// different sequences and the short tail splits come last) from a global counter, which evens out
+// the speed differences between SMs.  H consumer warps (one per KV head) + one producer warp.
 //
 // The producer warp runs ahead of the consumers.  It resolves block table -> page header -> chunk
 // ids -> residual map for up to 32 blocks at a time, one block per lane (the dependent global
-// loads of the next batch are in flight while the current one is worked off), and then feeds the
+// loads of the next batch are in flight while the current one is worked off), plans up to 32 tiles
+// in parallel (lane l writes tile l's header and copy sources to shared memory) and then feeds the
 // stage ring tile by tile: wait until every consumer warp has released the stage, write the tile's
 // header, and start the tile's copies as bulk asynchronous copies that report their bytes to the
 // stage's `full` mbarrier -- lane t copies token row t (to a slot padded by 16 bytes so ldmatrix over
 // 8 rows is conflict free), lanes 16.. copy the V / K stats.  Consumers only wait for `full`,
-// compute, and arrive on `empty`; there is no CTA-wide barrier in the loop.
+// compute, and arrive on `empty`; the header tells them where a work item starts (load the query,
+// reset the accumulators) and ends (write the split's partial result).  There is no CTA-wide barrier
+// in the loop.
 __device__ __forceinline__ bool item_range(const Params& P, int item, int& seq, int& split, int64_t& seq_len,
                                            int& b_start, int& b_end) {
   seq = item % P.num_seqs;
@@ -718,11 +725,12 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
   const int NS = P.NS;
   const int n_items = P.num_seqs * A.num_splits;
 
-  // shared memory: [barriers | lock][remap][q copies per head][stage ring]
+  // shared memory: [barriers | lock][tile plans][remap][q copies per head][stage ring]
   uint64_t* sfull = reinterpret_cast<uint64_t*>(smem);   // stage ring: header written, copies landed
   uint64_t* sempty = sfull + MAX_NS;                     // stage ring: every consumer warp is done with the stage
   int* lock = reinterpret_cast<int*>(sempty + MAX_NS);
-  float* remap = reinterpret_cast<float*>(smem + HDR_BYTES);
+  TilePlan* plan = reinterpret_cast<TilePlan*>(smem + HDR_BYTES);
+  float* remap = reinterpret_cast<float*>(smem + HDR_BYTES + UNIT * sizeof(TilePlan));
   unsigned char* qs = reinterpret_cast<unsigned char*>(remap) + REMAP_BYTES;
   const int q_rows = A.gqa + 1;
   unsigned char* ring = qs + H * q_head_bytes(q_rows);
@@ -744,107 +752,145 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
   if (warp == H) {
     // ===================== producer warp =====================
     const int tpb = L.BS / TILE;                     // tiles per block
-    const int U = tpb >= 32 ? 1 : 32 / tpb;          // blocks per unit (a unit is at most 32 tiles)
+    const int U = tpb >= UNIT ? 1 : UNIT / tpb;      // blocks per unit
     const bool contig = L.BS == TILE && L.KG == TILE;  // a tile's four stats arrays form one run in the page
     const uint32_t ring_u = smem_u32(ring);
+    const uint32_t stat_bytes = H * (2 * TILE * NG * 2 + 2 * D * 2);
     int st = 0, round = 0;                           // next stage to fill and how often it has been filled
     uint32_t st_u = ring_u;
     int issued = 0;
-    int item = blockIdx.x, seq = 0, split = 0, b_start = 0, b_end = 0, base = 0;
+    int seq = 0, split = 0, b_start = 0, b_end = 0, base = 0;
     int64_t seq_len = 0, bt_row = 0;
     bool have = false;
-    auto advance = [&]() {  // move (item, base) to the next unit; false when the CTA is out of work
+    auto advance = [&]() {  // move to the next unit (claiming a new item when needed); false when there is no work left
       if (have && base + U < b_end) { base += U; return true; }
-      if (have) item += gridDim.x;
-      for (; item < n_items; item += gridDim.x) {
-        if (item_range(P, item, seq, split, seq_len, b_start, b_end)) {
+      for (;;) {
+        int it = 0;
+        if (lane == 0) it = atomicAdd(P.counter, 1);
+        it = __shfl_sync(0xffffffffu, it, 0);
+        if (it >= n_items) { have = false; return false; }
+        if (item_range(P, it, seq, split, seq_len, b_start, b_end)) {
           base = b_start; bt_row = A.bt_rows ? A.bt_rows[seq] : seq; have = true;
           return true;
         }
       }
-      return false;
     };
+#ifdef ECHOKV_PROFILE
+    long long p_wait = 0, p_meta = 0, p_plan = 0;
+    const long long p_begin = clock64();
+#endif
     bool more = advance();
     BlockMeta nxt = more ? load_meta(P, bt_row, lane < U ? base + lane : b_end, b_end) : BlockMeta{};
     while (more && ok) {
       const BlockMeta cur = nxt;
-      const int u_base = base, u_end = b_end;
+      const int u_base = base, u_end = b_end, u_seq = seq, u_split = split;
+      const bool u_first = base == b_start, u_last = base + U >= b_end;
       const int64_t u_len = seq_len;
+      PROF_T(m0);
       more = advance();
       if (more) nxt = load_meta(P, bt_row, lane < U ? base + lane : b_end, b_end);
+      PROF_T(m1);
+      PROF_ADD(p_meta, m0, m1);
       const int nb = min(U, u_end - u_base);
       // tokens of the unit: all blocks are full except possibly the item's last one
       const int unit_tok = (int)min((int64_t)nb * L.BS, u_len - (int64_t)u_base * L.BS);
       const int unit_tiles = (unit_tok + TILE - 1) / TILE;
-      int tiles_left = unit_tiles;
-      for (int kb = 0; kb < nb && ok; ++kb) {  // blocks of the unit; the block's metadata sits in lane kb
-        const int kblk = __shfl_sync(0xffffffffu, cur.blk, kb);
-        int bits = __shfl_sync(0xffffffffu, cur.bits, kb);
-        const int c1 = __shfl_sync(0xffffffffu, cur.c1, kb), c2 = __shfl_sync(0xffffffffu, cur.c2, kb),
-                  c3 = __shfl_sync(0xffffffffu, cur.c3, kb);
-        const long long ks_slot = __shfl_sync(0xffffffffu, cur.rslot, kb);
-        const int kgrp = __shfl_sync(0xffffffffu, cur.rgrp, kb);
-        if (bits != 2 && bits != 4 && bits != 8) bits = 2;  // never opened: stay inside the page
-        const bool too_wide = bits > P.max_bits;             // the caller's tier bound was wrong
-        if (too_wide) { bits = P.max_bits; bad_tier = true; }  // such tiles are staged empty
-        const uint32_t row_bytes = 32u * H * bits;
-        const int tpc = (2 * L.BS) / bits;                    // tokens per chunk (a multiple of 4: block_size % 16 == 0)
-        const int blk_tok = min(L.BS, unit_tok - kb * L.BS);
-        const unsigned char* page = P.pages + (int64_t)kblk * L.PS;
-        // this lane's token row of the block's first tile: chunk index and position inside the chunk
-        int jc = 0, in_chunk = lane;
-        while (in_chunk >= tpc) { in_chunk -= tpc; ++jc; }
-        int t0 = 0, grp = 0, g_pos = 0;                       // first token of the tile, its K group, position in the group
-        const int n_bt = min(tpb, tiles_left);
-        for (int tb = 0; tb < n_bt && ok; ++tb) {
-          const int n_valid = too_wide ? 0 : min(TILE, blk_tok - t0);
+      {  // plan: lane l takes tile l of the unit (its block's metadata sits in lane kb)
+        const int kb = tpb == 1 ? lane : lane / tpb, tb = lane - kb * tpb;
+        const int src = kb < 32 ? kb : 31;
+        const int kblk = __shfl_sync(0xffffffffu, cur.blk, src);
+        int bits = __shfl_sync(0xffffffffu, cur.bits, src);
+        const int c1 = __shfl_sync(0xffffffffu, cur.c1, src), c2 = __shfl_sync(0xffffffffu, cur.c2, src),
+                  c3 = __shfl_sync(0xffffffffu, cur.c3, src);
+        const long long ks_slot = __shfl_sync(0xffffffffu, cur.rslot, src);
+        const int kgrp = __shfl_sync(0xffffffffu, cur.rgrp, src);
+        if (lane < unit_tiles) {
+          if (bits != 2 && bits != 4 && bits != 8) bits = 2;  // never opened: stay inside the page
+          const bool too_wide = bits > P.max_bits;             // the caller's tier bound was wrong
+          if (too_wide) { bits = P.max_bits; bad_tier = true; }  // such tiles are staged empty
+          const int row_bytes = 32 * H * bits;
+          const int tpc = (2 * L.BS) / bits;
+          const int t0 = tb * TILE;
+          const int blk_tok = min(L.BS, unit_tok - kb * L.BS);
+          const int grp = t0 / L.KG;
           const bool in_res = ks_slot >= 0 && grp == kgrp;
-          if (round > 0 && !(P.debug & 4 ? mbar_wait(sempty + st, (round - 1) & 1)
-                                         : mbar_wait_long(sempty + st, (round - 1) & 1, 500u))) { ok = false; break; }
-          const uint32_t bar = smem_u32(sfull + st);
-          const bool copy = n_valid > 0 && (P.debug & 3) != 2;
-          if (lane == 0) {
-            StageHeader* hd = reinterpret_cast<StageHeader*>(ring + (size_t)st * P.stage_bytes + P.o_hdr);
-            *reinterpret_cast<int4*>(hd) = make_int4(bits, n_valid, in_res ? 1 : 0, g_pos);
-            hd->res_slot = ks_slot;
-            if (copy) mbar_expect_tx(sfull + st, n_valid * row_bytes + H * (2 * TILE * NG * 2 + 2 * D * 2));
-            else mbar_arrive(sfull + st);
-          }
-          __syncwarp();
-          if (copy) {
-            if (lane < n_valid) {  // token row `lane` of the tile
+          const unsigned char* page = P.pages + (int64_t)kblk * L.PS;
+          TilePlan& d = plan[lane];
+          int jc = t0 / tpc, in_chunk = t0 - jc * tpc;      // chunk of the tile's first token, position inside it
+          const unsigned char* chunk = nullptr;
+          for (int t = 0; t < TILE; ++t) {
+            if (t == 0 || in_chunk == tpc) {
+              if (t) { ++jc; in_chunk = 0; }
               int64_t pg = kblk, cs = 0;
-              if (jc > 0) {
-                const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3);
-                const int q = L.KC == 4 ? id >> 2 : (L.KC == 2 ? id >> 1 : (L.KC == 1 ? id : id / 3));
-                pg = q; cs = id - q * L.KC;
-              }
-              bulk_copy(st_u + lane * (row_bytes + 16), P.pages + pg * L.PS + L.o_data + cs * L.CB + (int64_t)in_chunk * row_bytes,
-                        row_bytes, bar);
-            } else if (contig) {
-              if (lane == 16) bulk_copy(st_u + P.o_vs, page + L.o_vs, H * (2 * TILE * NG * 2 + 2 * D * 2), bar);
-            } else if (lane >= 16 && lane < 20) {
-              const int which = lane - 16;  // vs, vm, ks, km
-              const bool isv = which < 2;
-              const int64_t src_off = (which == 0 ? L.o_vs : which == 1 ? L.o_vm : which == 2 ? L.o_ks : L.o_km) +
-                                      (isv ? (int64_t)t0 * H * NG * 2 : (int64_t)grp * H * D * 2);
-              const int dst_off = which == 0 ? P.o_vs : which == 1 ? P.o_vm : which == 2 ? P.o_ks : P.o_km;
-              bulk_copy(st_u + dst_off, page + src_off, isv ? H * TILE * NG * 2 : H * D * 2, bar);
+              if (jc > 0) { const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3); pg = id / L.KC; cs = id - pg * L.KC; }
+              chunk = P.pages + pg * L.PS + L.o_data + cs * L.CB;
             }
+            d.row_src[t] = chunk + (int64_t)in_chunk * row_bytes;
+            ++in_chunk;
           }
-          ++issued;
-          if (++st == NS) { st = 0; st_u = ring_u; ++round; } else { st_u += P.stage_bytes; }
-          // next tile of the block
-          t0 += TILE;
-          in_chunk += TILE;
-          while (in_chunk >= tpc) { in_chunk -= tpc; ++jc; }
-          g_pos += TILE;
-          if (g_pos >= L.KG) { g_pos = 0; ++grp; }
+          d.hdr.bits = bits; d.hdr.n_valid = too_wide ? 0 : min(TILE, blk_tok - t0);
+          d.hdr.flags = (in_res ? F_RES : 0) | (u_first && lane == 0 ? F_FIRST : 0) | (u_last && lane == unit_tiles - 1 ? F_LAST : 0);
+          d.hdr.pos0 = t0 - grp * L.KG; d.hdr.res_slot = ks_slot; d.hdr.seq = u_seq; d.hdr.split = u_split;
+          d.stats[0] = page + L.o_vs + (int64_t)t0 * H * NG * 2;
+          d.stats[1] = page + L.o_vm + (int64_t)t0 * H * NG * 2;
+          d.stats[2] = page + L.o_ks + (int64_t)grp * H * D * 2;
+          d.stats[3] = page + L.o_km + (int64_t)grp * H * D * 2;
         }
-        tiles_left -= n_bt;
+        __syncwarp();
       }
+      PROF_T(m2);
+      PROF_ADD(p_plan, m1, m2);
+      for (int ti = 0; ti < unit_tiles; ++ti) {
+        const TilePlan& d = plan[ti];
+        const int4 h0 = *reinterpret_cast<const int4*>(&d.hdr);   // bits, n_valid, flags, pos0
+        const uint32_t row_bytes = 32u * H * h0.x;
+        const bool copy = h0.y > 0 && (P.debug & 3) != 2;
+        PROF_T(w0);
+        if (round > 0 && !mbar_wait(sempty + st, (round - 1) & 1)) { ok = false; break; }
+        PROF_T(w1);
+        PROF_ADD(p_wait, w0, w1);
+        const uint32_t bar = smem_u32(sfull + st);
+        if (lane == 0) {
+          int4* hd = reinterpret_cast<int4*>(ring + (size_t)st * P.stage_bytes + P.o_hdr);
+          hd[0] = h0;
+          hd[1] = reinterpret_cast<const int4*>(&d.hdr)[1];
+          if (copy) mbar_expect_tx(sfull + st, h0.y * row_bytes + stat_bytes);
+          else mbar_arrive(sfull + st);
+        }
+        __syncwarp();
+        if (copy) {
+          if (lane < h0.y) bulk_copy(st_u + lane * (row_bytes + 16), d.row_src[lane], row_bytes, bar);
+          else if (contig) { if (lane == 16) bulk_copy(st_u + P.o_vs, d.stats[0], stat_bytes, bar); }
+          else if (lane >= 16 && lane < 20) {
+            const int which = lane - 16;  // vs, vm, ks, km
+            const int dst_off = which == 0 ? P.o_vs : which == 1 ? P.o_vm : which == 2 ? P.o_ks : P.o_km;
+            bulk_copy(st_u + dst_off, d.stats[which], which < 2 ? H * TILE * NG * 2 : H * D * 2, bar);
+          }
+        }
+        ++issued;
+        if (++st == NS) { st = 0; st_u = ring_u; ++round; } else { st_u += P.stage_bytes; }
+      }
+      __syncwarp();  // every lane is done reading the plans before the next unit overwrites them
       ok = !__any_sync(0xffffffffu, !ok);
     }
+    if (ok) {  // no more work: tell the consumers
+      if (round == 0 || mbar_wait(sempty + st, (round - 1) & 1)) {
+        if (lane == 0) {
+          reinterpret_cast<int4*>(ring + (size_t)st * P.stage_bytes + P.o_hdr)[0] = make_int4(2, -1, 0, 0);
+          mbar_arrive(sfull + st);
+        }
+      } else {
+        ok = false;
+      }
+    }
+#ifdef ECHOKV_PROFILE
+    if (lane == 0 && blockIdx.x < 1024) {
+      g_prof[blockIdx.x * 8 + 0] = clock64() - p_begin;
+      g_prof[blockIdx.x * 8 + 1] = p_wait;
+      g_prof[blockIdx.x * 8 + 2] = p_meta;
+      g_prof[blockIdx.x * 8 + 7] = p_plan;
+    }
+#endif
     if (!ok) {
       // A wait gave up: copies already started may still be landing; give each stage its (bounded)
       // time before the CTA's shared memory goes away.
@@ -873,15 +919,34 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
     const uint32_t stage_bytes = P.stage_bytes;
     int c_st = 0, c_round = 0;                  // stage being consumed and how often it has been consumed
     uint32_t c_sb = ring_u;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-      int seq, split, b_start, b_end;
-      int64_t seq_len;
-      if (!item_range(P, item, seq, split, seq_len, b_start, b_end)) continue;
-      const int n_tok = (int)(min(seq_len, (int64_t)b_end * L.BS) - (int64_t)b_start * L.BS);
-      const int n_tiles = (n_tok + TILE - 1) / TILE;
-      // this head's queries -> fp16, pre-multiplied by softmax_scale * log2(e); rows >= gqa are zero.
-      // All global loads are issued before the first use so the item pays one memory latency.
+#ifdef ECHOKV_PROFILE
+    long long c_wait = 0, c_math = 0, c_item = 0;
+    const long long c_begin = clock64();
+#endif
+    WarpState w;
+    w.bits = 0; w.qbits = 0;
+    int seq = 0;
+    while (ok) {
+      PROF_T(w0);
+      if (!mbar_wait(sfull + c_st, c_round & 1)) { ok = false; break; }  // header written, copies landed
+      PROF_T(w1);
+      PROF_ADD(c_wait, w0, w1);
+      StageInfo si;
+      int flags, split;
       {
+        uint32_t hd[4], ex[4];
+        lds128<0>(hd, c_sb + P.o_hdr);
+        lds128<16>(ex, c_sb + P.o_hdr);
+        si.bits = (int)hd[0]; si.n_valid = (int)hd[1]; flags = (int)hd[2]; si.pos0 = (int)hd[3];
+        si.in_res = flags & F_RES;
+        si.res_slot = (long long)(((unsigned long long)ex[1] << 32) | ex[0]);
+        if (flags & F_FIRST) seq = (int)ex[2];
+        split = (int)ex[3];
+      }
+      if (si.n_valid < 0) break;  // no more work for this CTA
+      if (flags & F_FIRST) {
+        // this head's queries -> fp16, pre-multiplied by softmax_scale * log2(e); rows >= gqa are zero.
+        // All global loads are issued before the first use so the item pays one memory latency.
         const int64_t q_row = A.q_rows ? A.q_rows[seq] : seq;
         __syncwarp();
         if (P.q_vec16) {  // 16-bit queries, 16-byte aligned rows: lane l loads 8 channels of rows l / 16, + 2, + 4, + 6
@@ -918,43 +983,46 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
           }
         }
         __syncwarp();
-      }
-      WarpState w;
 #pragma unroll
-      for (int mt = 0; mt < 8; ++mt) { w.acc[mt][0] = w.acc[mt][1] = w.acc[mt][2] = w.acc[mt][3] = 0.f; }
-      w.bl[0] = w.bl[1] = w.bl[2] = w.bl[3] = 0.f;
-      w.m0 = w.m1 = -INFINITY;
-      w.bits = 0;
-      w.qbits = 0;
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        if (!mbar_wait(sfull + c_st, c_round & 1)) { ok = false; break; }  // header written, copies landed
-        StageInfo si;
-        {
-          uint32_t hd[4];
-          lds128<0>(hd, c_sb + P.o_hdr);
-          si.bits = (int)hd[0]; si.n_valid = (int)hd[1]; si.in_res = (int)hd[2]; si.pos0 = (int)hd[3];
-          const uint2 rs = lds64<16>(c_sb + P.o_hdr);
-          si.res_slot = (long long)(((unsigned long long)rs.y << 32) | rs.x);
-        }
-        TileView tv;
-        tv.krow = c_sb + (si.bits == 8 ? lc.k8 : (si.bits == 4 ? lc.k4 : lc.k2));
-        tv.vrow = c_sb + (si.bits == 8 ? lc.v8 : (si.bits == 4 ? lc.v4 : lc.v2));
-        tv.vs = c_sb + P.o_vs + lc.vs_off; tv.vm = c_sb + P.o_vm + lc.vm_off;
-        tv.ks = c_sb + P.o_ks + lc.ksm_off; tv.km = c_sb + P.o_km + lc.ksm_off; tv.tok = lc.tok;
-        if (si.n_valid > 0 && (P.debug & 3) != 1) {
-          if (si.bits == 4) process_tile<4>(P, tv, si, qv, h, lane, w, remap, lock, ok);
-          else if (si.bits == 8) process_tile<8>(P, tv, si, qv, h, lane, w, remap, lock, ok);
-          else process_tile<2>(P, tv, si, qv, h, lane, w, remap, lock, ok);
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(sempty + c_st);
-        if (++c_st == NS) { c_st = 0; c_sb = ring_u; ++c_round; } else { c_sb += stage_bytes; }
+        for (int mt = 0; mt < 8; ++mt) { w.acc[mt][0] = w.acc[mt][1] = w.acc[mt][2] = w.acc[mt][3] = 0.f; }
+        w.bl[0] = w.bl[1] = w.bl[2] = w.bl[3] = 0.f;
+        w.m0 = w.m1 = -INFINITY;
+        w.bits = 0;
+        w.qbits = 0;
       }
-      if (!ok) break;
-      if (w.bits == 4) write_partial<4>(P, w, seq, split, h, lane);
-      else if (w.bits == 8) write_partial<8>(P, w, seq, split, h, lane);
-      else write_partial<2>(P, w, seq, split, h, lane);
+      PROF_T(w2);
+      PROF_ADD(c_item, w1, w2);
+      TileView tv;
+      tv.krow = c_sb + (si.bits == 8 ? lc.k8 : (si.bits == 4 ? lc.k4 : lc.k2));
+      tv.vrow = c_sb + (si.bits == 8 ? lc.v8 : (si.bits == 4 ? lc.v4 : lc.v2));
+      tv.vs = c_sb + P.o_vs + lc.vs_off; tv.vm = c_sb + P.o_vm + lc.vm_off;
+      tv.ks = c_sb + P.o_ks + lc.ksm_off; tv.km = c_sb + P.o_km + lc.ksm_off; tv.tok = lc.tok;
+      if (si.n_valid > 0 && (P.debug & 3) != 1) {
+        if (si.bits == 4) process_tile<4>(P, tv, si, qv, h, lane, w, remap, lock, ok);
+        else if (si.bits == 8) process_tile<8>(P, tv, si, qv, h, lane, w, remap, lock, ok);
+        else process_tile<2>(P, tv, si, qv, h, lane, w, remap, lock, ok);
+      }
+      __syncwarp();
+      PROF_T(w3);
+      PROF_ADD(c_math, w2, w3);
+      if (lane == 0) mbar_arrive(sempty + c_st);
+      if (++c_st == NS) { c_st = 0; c_sb = ring_u; ++c_round; } else { c_sb += stage_bytes; }
+      if (flags & F_LAST) {
+        if (w.bits == 4) write_partial<4>(P, w, seq, split, h, lane);
+        else if (w.bits == 8) write_partial<8>(P, w, seq, split, h, lane);
+        else write_partial<2>(P, w, seq, split, h, lane);
+        PROF_T(w4);
+        PROF_ADD(c_item, w3, w4);
+      }
     }
+#ifdef ECHOKV_PROFILE
+    if (lane == 0 && h == 0 && blockIdx.x < 1024) {
+      g_prof[blockIdx.x * 8 + 3] = clock64() - c_begin;
+      g_prof[blockIdx.x * 8 + 4] = c_wait;
+      g_prof[blockIdx.x * 8 + 5] = c_math;
+      g_prof[blockIdx.x * 8 + 6] = c_item;
+    }
+#endif
   }
   if ((!ok || bad_tier) && lane == 0 && P.status) atomicExch(P.status, bad_tier ? 2 : 1);
 }
@@ -965,7 +1033,7 @@ static int g_decode_path = 0;  // 0: pick by shape, 1: always the generic kernel
 
 // Chooses the tensor-core kernel when the shape fits; otherwise leaves `handled` false.
 int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
-                      int64_t num_seqs, int max_tier, int* status, cudaStream_t st, bool* handled) {
+                      int64_t num_seqs, int max_tier, int* counter, int* status, cudaStream_t st, bool* handled) {
   using namespace mma;
   *handled = false;
   if ((g_decode_path & 15) == 1) return ECHOKV_OK;
@@ -989,9 +1057,10 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   P.o_hdr = P.o_km + H * D * 2;
   P.stage_bytes = (P.o_hdr + (int)sizeof(StageHeader) + 127) / 128 * 128;
   P.status = status;
+  P.counter = counter;
   P.q_vec16 = (A.q_dt != ECHOKV_DT_F32) && (reinterpret_cast<uintptr_t>(A.q) % 16 == 0) && A.q_s0 % 8 == 0 && A.q_s1 % 8 == 0;
   P.debug = (g_decode_path >> 4) & 15;
-  const int fixed = HDR_BYTES + REMAP_BYTES + H * q_head_bytes(A.gqa + 1);
+  const int fixed = HDR_BYTES + UNIT * (int)sizeof(TilePlan) + REMAP_BYTES + H * q_head_bytes(A.gqa + 1);
   static int max_smem = -1, num_sms = 0;
   if (max_smem < 0) {
     int dev = 0;
@@ -1026,6 +1095,7 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   int64_t grid = (int64_t)num_sms * per_sm;
   const int64_t n_items = num_seqs * (int64_t)A.num_splits;
   if (grid > n_items) grid = n_items;
+  if (cudaMemsetAsync(counter, 0, sizeof(int), st) != cudaSuccess) return check_launch("decode (work counter)");
   switch (H) {
     case 1: decode_mma_kernel<1><<<(unsigned)grid, 2 * 32, smem_bytes, st>>>(P); break;
     case 2: decode_mma_kernel<2><<<(unsigned)grid, 3 * 32, smem_bytes, st>>>(P); break;
@@ -1039,6 +1109,12 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
 }
 
 }  // namespace echokv
+
+#ifdef ECHOKV_PROFILE
+extern "C" int echokv_debug_prof(long long* dst, int n) {
+  return (int)cudaMemcpyFromSymbol(dst, echokv::mma::g_prof, sizeof(long long) * n);
+}
+#endif
 
 extern "C" int echokv_set_decode_path(int path) {
   const int old = echokv::g_decode_path;

@@ -140,9 +140,11 @@ int echokv_demote_blocks(const echokv_layout* layout, const echokv_pages* pages,
 int echokv_gather(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
                   const int64_t* blk, const int64_t* off, int64_t n, float* k_out, float* v_out, void* stream);
 
-/* Bytes of scratch echokv_decode needs for its split partials: acc float32
+/* Bytes of scratch echokv_decode needs: the split partials, acc float32
  * [S, Hq, num_splits, D] then (m, l) float32 [S, Hq, num_splits, 2]
- * (kernels/decode.py:306-307 allocates the same two tensors per call). */
+ * (kernels/decode.py:306-307 allocates the same two tensors per call), rounded up to 16 bytes,
+ * plus 256 bytes of work-queue state (the counter persistent CTAs claim work items from; the
+ * call zeroes it itself with a memset node on `stream`). */
 int64_t echokv_decode_scratch_bytes(int64_t num_seqs, int32_t num_q_heads, int32_t head_size, int32_t num_splits);
 
 /* Split-K paged decode attention + merge -- decode_attention / _decode_triton
