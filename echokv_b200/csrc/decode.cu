@@ -7,8 +7,14 @@ namespace echokv {
 int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
                       int64_t num_seqs, int max_tier, int* counter, int* status, cudaStream_t st, bool* handled);
 
-// out[q_rows[seq], head] = splits merged in split order (kernels/decode.py:226-262).
+// out[q_rows[seq], head] = splits merged in split order (kernels/decode.py:226-262).  One CTA per
+// (sequence, query head): the log-sum-exp weights of the used splits are computed once into shared
+// memory, then thread d sums channel d over the splits with the loads of a batch of splits in
+// flight together.
+constexpr int MERGE_MAX_SPLITS = 64;
 __global__ void decode_merge_kernel(DecodeArgs A, int BS, int D) {
+  __shared__ float wgt[MERGE_MAX_SPLITS];
+  __shared__ float red[2];
   const int seq = blockIdx.x, head = blockIdx.y;
   const int64_t seq_len = A.lens[seq];
   if (seq_len == 0) return;  // CUDA-graph padding: leave the row alone
@@ -16,9 +22,41 @@ __global__ void decode_merge_kernel(DecodeArgs A, int BS, int D) {
   const int bps = max(A.bps_min, (n_blocks + A.num_splits - 1) / A.num_splits);
   const int used = (n_blocks + bps - 1) / bps;
   const int64_t base = ((int64_t)seq * A.Hq + head) * A.num_splits;
+  const int64_t o_row = A.q_rows ? A.q_rows[seq] : seq;
+  if (used <= MERGE_MAX_SPLITS) {
+    if (threadIdx.x < 32) {  // warp 0: maximum, weights and the denominator (summed in split order)
+      float m = -INFINITY;
+      for (int s = threadIdx.x; s < used; s += 32) m = fmaxf(m, A.ml[(base + s) * 2]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      for (int s = threadIdx.x; s < used; s += 32) wgt[s] = exp2f(A.ml[(base + s) * 2] - m);
+      __syncwarp();
+      if (threadIdx.x == 0) {
+        float lt = 0.f;
+        for (int s = 0; s < used; ++s) lt += A.ml[(base + s) * 2 + 1] * wgt[s];
+        red[0] = lt;
+      }
+    }
+    __syncthreads();
+    const float lt = red[0];
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      const float* src = A.acc + base * D + d;
+      float a = 0.f;
+      int s = 0;
+      for (; s + 8 <= used; s += 8) {
+        float x[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) x[k] = src[(int64_t)(s + k) * D];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) a += x[k] * wgt[s + k];
+      }
+      for (; s < used; ++s) a += src[(int64_t)s * D] * wgt[s];
+      st_dt(A.out, A.out_dt, o_row * A.o_s0 + (int64_t)head * A.o_s1 + d, a / lt);
+    }
+    return;
+  }
   float mt = -INFINITY;
   for (int s = 0; s < used; ++s) mt = fmaxf(mt, A.ml[(base + s) * 2]);
-  const int64_t o_row = A.q_rows ? A.q_rows[seq] : seq;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float a = 0.f, lt = 0.f;
     for (int s = 0; s < used; ++s) {

@@ -29,11 +29,14 @@ namespace mma {
 
 #ifdef ECHOKV_PROFILE
 __device__ long long g_prof[1024 * 8];
+__device__ unsigned long long g_phase[8];
 #define PROF_T(x) const long long x = clock64()
 #define PROF_ADD(acc, a, b) acc += (b) - (a)
+#define PROF_PHASE(k, a, b) if (h == 0 && lane == 0) atomicAdd(&g_phase[k], (unsigned long long)((b) - (a)))
 #else
 #define PROF_T(x)
 #define PROF_ADD(acc, a, b)
+#define PROF_PHASE(k, a, b)
 #endif
 
 constexpr int D = 128;          // head size of this kernel
@@ -600,9 +603,12 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
     w.bits = BITS;
   }
   // scores
+  PROF_T(f0);
   float c[4] = {0.f, 0.f, 0.f, 0.f};
   if (si.in_res) qk_residual(P.R, si, qv.qn_lane, h, lane, c);
   else qk_codes<BITS>(tv, qv.qt_lane, qv.qn_ld, lane, c);
+  PROF_T(f1);
+  PROF_PHASE(0, f0, f1);
   if (r >= si.n_valid) { c[0] = -INFINITY; c[1] = -INFINITY; }
   if (r + 8 >= si.n_valid) { c[2] = -INFINITY; c[3] = -INFINITY; }
   // online softmax over tokens (rows); columns 2j, 2j+1 belong to this lane
@@ -628,6 +634,8 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
   const uint32_t p_lo = pack_h2(ex2(c[0] - n0), ex2(c[1] - n1));   // token r
   const uint32_t p_hi = pack_h2(ex2(c[2] - n0), ex2(c[3] - n1));   // token r + 8
   const uint32_t pb0 = movm_t(p_lo), pb1 = movm_t(p_hi);
+  PROF_T(f2);
+  PROF_PHASE(1, f1, f2);
   // [v_min | ones] rows: bias of V group r (lanes r < NG) and the softmax denominator
   {
     const uint32_t base = tv.vm, tok = tv.tok;  // lanes r >= NG read group 0 and mask it to zero
@@ -639,7 +647,11 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
     const uint32_t keep = r < NG ? 0xffffffffu : 0u;
     mma16816(w.bl, prmt(x0, x1, 0x5410u) & keep, H2_ONE, prmt(x2, x3, 0x5410u) & keep, H2_ONE, pb0, pb1);
   }
+  PROF_T(f3);
+  PROF_PHASE(2, f2, f3);
   pv_codes<BITS>(tv, lane, pb0, pb1, w);
+  PROF_T(f4);
+  PROF_PHASE(3, f3, f4);
 }
 
 // ---- the kernel ------------------------------------------------------------------------------
@@ -1113,6 +1125,11 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
 #ifdef ECHOKV_PROFILE
 extern "C" int echokv_debug_prof(long long* dst, int n) {
   return (int)cudaMemcpyFromSymbol(dst, echokv::mma::g_prof, sizeof(long long) * n);
+}
+extern "C" int echokv_debug_phase(unsigned long long* dst, int reset) {
+  int rc = (int)cudaMemcpyFromSymbol(dst, echokv::mma::g_phase, sizeof(unsigned long long) * 8);
+  if (reset) { unsigned long long z[8] = {}; cudaMemcpyToSymbol(echokv::mma::g_phase, z, sizeof(z)); }
+  return rc;
 }
 #endif
 
