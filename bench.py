@@ -54,10 +54,15 @@ def parse():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph")
     ap.add_argument("--cpu-seqs", type=int, default=4, help="sequences in the CPU-baseline sample")
     ap.add_argument("--canary-interval", type=int, default=8, help="measure the canary KL every N steps (0 = never)")
+    ap.add_argument("--tiers", default="", help="comma list of tiers cycled over the layers instead of the seeded draw "
+                                                "(small profiling cases, e.g. --layers 2 --tiers 4)")
     return ap.parse_args()
 
 
-def tier_vector(layers: int, seed: int) -> list[int]:
+def tier_vector(layers: int, seed: int, fixed: str = "") -> list[int]:
+    if fixed:
+        cyc = [int(x) for x in fixed.split(",")]
+        return [cyc[i % len(cyc)] for i in range(layers)]
     rng = np.random.default_rng(seed)
     return [int(b) for b in rng.choice([8, 4, 2], size=layers, p=[0.25, 0.5, 0.25])]
 
@@ -172,7 +177,7 @@ def run_reference(a) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    tiers = tier_vector(a.layers, a.seed)
+    tiers = tier_vector(a.layers, a.seed, a.tiers)
     cores = os.cpu_count() or 1
     vals = []
     base = None
@@ -217,7 +222,7 @@ def run_b200(a) -> None:
         raise SystemExit(f"{H} KV heads cannot be sharded over {world} ranks")
     h, hq = H // world, HQ // world
 
-    tiers = tier_vector(a.layers, a.seed)
+    tiers = tier_vector(a.layers, a.seed, a.tiers)
     layout = TieredLayout(num_kv_heads=h, head_size=D, block_size=BS, mem_bits=MEM_BITS, k_group=KG, v_group=VG)
     S, ctx, Lr = a.batch, a.ctx, a.layers
     total_steps = a.warmup + a.steps + 4
@@ -393,7 +398,7 @@ def run_b200(a) -> None:
 
     if rank == 0:
         cores = os.cpu_count() or 1
-        base = cpu_baseline(a, tiers, 1, n_seqs=a.cpu_seqs, layers_sample=2)
+        base = cpu_baseline(a, tiers, 1, n_seqs=a.cpu_seqs, layers_sample=2) if a.cpu_seqs > 0 else None
         value = S * a.steps / (ms / 1e3)
         h2d = sum(t.numel() * t.element_size() for t in (q_host, k_host, v_host))
         d2h = out_host.numel() * out_host.element_size()
@@ -408,7 +413,8 @@ def run_b200(a) -> None:
                        "host_cores": cores},
             "roofline": {"bound": "hbm", "achieved": main["gbs"], "peak": peak, "unit": "GB/s", "frac": main["frac"],
                          "traffic": DRAM_TRAFFIC_INT4 if (S, ctx, world) == (64, 4096, 1) else None,
-                         "kernel": "paged decode attention (split kernel + merge), INT4 layers", "peak_source": peak_src,
+                         "kernel": "paged decode attention (counter memset + split kernel + merge per launch), INT4 layers",
+                         "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": main["bytes"], "per_tier": tier_stats},
             "cpu_baseline": base,
             "e2e": {"value": S / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

@@ -1,25 +1,32 @@
 // Tensor-core split-K paged decode attention for sm_100a.
 //
-// One CTA per (sequence, split).  A producer warp streams 16-token tiles of the split's blocks
-// into a shared-memory ring with bulk asynchronous copies (cp.async.bulk + mbarrier
-// complete_tx): every token's [K codes | V codes] row goes to a row padded by 16 bytes (so
-// ldmatrix over 8 token rows is bank-conflict free), plus the tile's V stats and its K group's
-// per-channel stats.  16 consumer warps = H heads x TS token sets; set s takes tiles s, s+TS, ...
-// Per tile a warp
+// Persistent CTAs (a few per SM) claim (sequence, split) work items from a global counter.  A CTA
+// is one producer warp plus H consumer warps, one per KV head.  The producer resolves block table
+// -> page header -> chunk ids -> residual map for up to 32 blocks at a time and streams 16-token
+// tiles into a ring of shared-memory stages with bulk asynchronous copies (cp.async.bulk +
+// mbarrier complete_tx): every token's [K codes | V codes] row goes to a slot padded by 16 bytes
+// (so ldmatrix over 8 token rows is bank-conflict free), plus the tile's V stats and its K group's
+// per-channel stats and a small header (tier, valid tokens, item start / end).  Consumers wait
+// for a stage's `full` barrier, compute, and arrive on its `empty` barrier; nothing in the loop
+// synchronises the whole CTA.  Per tile a consumer warp
 //   * folds the K group's per-channel scale into the query (q' = q * k_scale, fp16) and adds the
 //     constant q . k_min through extra MMA k-steps, so packed K codes feed the tensor cores as
 //     plain integers:  S^T[t, g] = sum_d code[t, d] * q'[g, d] + sum_d k_min[d] * q[g, d];
-//   * unpacks codes to fp16 with mask-or-magic-number tricks (1024 + c etc.) and an exact
-//     subtract, straight from ldmatrix fragments (non-transposed for K, transposed for V so that
-//     register pairs run along tokens);
+//   * turns INT8 / INT4 codes into fp16 operands by masking them in place (a code byte or nibble
+//     alone in a 16-bit lane is the subnormal code * 2^-24; the power of two is undone on the
+//     fp32 scores / accumulators) and INT2 codes with magic-number tricks (1024 + c etc.) and an
+//     exact subtract, straight from ldmatrix fragments (non-transposed for K, transposed for V so
+//     that register pairs run along tokens);
 //   * keeps an online softmax per query head over tokens (the M dimension) with warp shuffles,
 //     transposes P with movmatrix and accumulates O^T[d, g] += V^T[d, t] * P[t, g]; V's per-token
 //     scale is folded into P per V group (INT8/INT4) or into the codes (INT2), V's min and the
 //     softmax denominator come from one more MMA against [v_min | ones].
 // Accumulator registers map to channels in a tier-specific order (it follows how ldmatrix deals
 // out packed codes); when consecutive blocks differ in tier the warp re-maps its accumulators
-// through shared memory.  Token sets are merged in set order and splits in split order, so a
-// sequence's result depends on its own length only.
+// through shared memory.  A split's tiles are accumulated in order by one warp and splits are
+// merged in split order, so a sequence's result depends on its own length only, not on which CTA
+// ran which item.  Every wait on a barrier is bounded; a wait that gives up ends the CTA's work
+// and raises the status word.
 #include <utility>
 
 #include "decode_generic.cuh"
@@ -135,6 +142,9 @@ template <int OFF>
 __device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(OFF));
+}
+__device__ __forceinline__ void ldsm_x2_t(uint32_t (&r)[2], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
 }
 template <int OFF>
 __device__ __forceinline__ void lds128(uint32_t (&r)[4], uint32_t addr) {
@@ -321,6 +331,8 @@ __device__ __forceinline__ void store_any(const WarpState& w, float* buf, int r,
 struct TileView {
   uint32_t krow, vrow;  // this lane's ldmatrix row address for the K side / V side of the staged rows
   uint32_t vs, vm;      // this lane's V scale (tokens 2j.., all groups) / V min (group r) address
+  uint32_t vs_row;      // V scales of token r (this head, all groups): 8 bytes; token r + 8 is 8 * tok further
+  uint32_t vm_ld;       // ldmatrix row address into the V mins: token (lane & 15), this head's pair of heads
   uint32_t ks, km;      // this head's K scale / min of the tile's group: fp16 [D]
   uint32_t tok;         // bytes between consecutive tokens in the V stats
 };
@@ -328,7 +340,7 @@ struct TileView {
 // Per-lane byte offsets that do not change from tile to tile (computed once per warp).
 struct LaneConst {
   uint32_t k2, k4, k8, v2, v4, v8;  // per tier: offset of this lane's ldmatrix row on the K / V side
-  uint32_t vs_off, vm_off, ksm_off, tok;
+  uint32_t vs_off, vm_off, ksm_off, tok, vs_row, vm_ld;
 };
 __device__ __forceinline__ LaneConst lane_const(int H, int h, int lane) {
   LaneConst c;
@@ -341,6 +353,8 @@ __device__ __forceinline__ LaneConst lane_const(int H, int h, int lane) {
   c.tok = (uint32_t)H * NG * 2;
   c.vs_off = (uint32_t)((2 * j) * H + h) * NG * 2;
   c.vm_off = c.vs_off + (uint32_t)(r < NG ? r : 0) * 2;
+  c.vs_row = (uint32_t)(r * H + h) * NG * 2;
+  c.vm_ld = (uint32_t)((lane & 15) * H + (h & ~1)) * NG * 2;
   c.ksm_off = (uint32_t)h * D * 2;
   return c;
 }
@@ -376,17 +390,17 @@ __device__ __forceinline__ void sub8_t(uint32_t w, uint32_t (&o)[2]) {  // [a.c0
 // group's k_min row broadcast to all 16 token rows (ldmatrix with every row address equal) and
 // whose B fragments are the natural-order query (ldmatrix over the 8 query rows).
 __device__ __forceinline__ void km_term(uint32_t km, uint32_t qn_ld, int lane, float (&c2)[4]) {
-  const uint32_t km_ld = km + (lane < 16 ? 0u : 16u);
+  // One ldmatrix feeds two k-steps: its four 8x8 pieces are channels [0,8) [8,16) [16,24) [24,32) of
+  // the 32-channel slice, each read with all eight row addresses equal (the row is the same for
+  // every token), so the A fragment of a k-step is (piece, piece, next piece, next piece).
+  const uint32_t km_ld = km + (lane >> 3) * 16u;
   static_for<4>([&](auto k2c) {
     constexpr int k2 = decltype(k2c)::value;
-    uint32_t B[4];
+    uint32_t B[4], A[4];
     ldsm_x4<k2 * 64>(B, qn_ld);
-    static_for<2>([&](auto kkc) {
-      constexpr int kk = decltype(kkc)::value;
-      uint32_t A[4];
-      ldsm_x4<(2 * k2 + kk) * 32>(A, km_ld);
-      mma16816(c2, A[0], A[1], A[2], A[3], B[2 * kk], B[2 * kk + 1]);
-    });
+    ldsm_x4<k2 * 64>(A, km_ld);
+    mma16816(c2, A[0], A[0], A[1], A[1], B[0], B[1]);
+    mma16816(c2, A[2], A[2], A[3], A[3], B[2], B[3]);
   });
 }
 
@@ -497,56 +511,69 @@ __device__ __forceinline__ void qk_residual(const ResidualDev& R, const StageInf
 }
 
 // ---- P.V for one tile --------------------------------------------------------------------------
-// pb0 / pb1: B fragments of P (tokens 2j,2j+1 / 2j+8,2j+9 of query head n = lane / 4), fp16.
-template <int BITS>
-__device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t pb0, uint32_t pb1, WarpState& w) {
+// p_lo / p_hi: this lane's probabilities in score layout (token r / r + 8, query heads 2j, 2j + 1), fp16.
+// The B fragments of the MMAs are their 8x8 transposes (tokens 2j,2j+1 / 2j+8,2j+9 of head lane / 4).
+// INT8 / INT4: V's per-token scale of group G multiplies P before the transpose, where a lane needs the
+// scales of just its own two tokens (8 bytes each, all groups), one fragment pair per group.
+// INT2: the scale goes into the codes, which needs it per token pair (the order of the A fragments).
+template <int BITS, int H>
+__device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t p_lo, uint32_t p_hi, uint32_t pb0,
+                                         uint32_t pb1, WarpState& w) {
   const int r = lane >> 2;
-  // V scale of this lane's four tokens, all NG groups: vlo[G] = {vs[2j][G], vs[2j+1][G]}, vhi[G] likewise +8
-  uint32_t vlo[NG], vhi[NG];
-  {
-    uint2 t0, t1, t2, t3;
-    const uint32_t base = tv.vs, tok = tv.tok;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t0.x), "=r"(t0.y) : "r"(base));
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t1.x), "=r"(t1.y) : "r"(base + tok));
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t2.x), "=r"(t2.y) : "r"(base + 8 * tok));
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t3.x), "=r"(t3.y) : "r"(base + 9 * tok));
-    vlo[0] = prmt(t0.x, t1.x, 0x5410u); vlo[1] = prmt(t0.x, t1.x, 0x7632u);
-    vlo[2] = prmt(t0.y, t1.y, 0x5410u); vlo[3] = prmt(t0.y, t1.y, 0x7632u);
-    vhi[0] = prmt(t2.x, t3.x, 0x5410u); vhi[1] = prmt(t2.x, t3.x, 0x7632u);
-    vhi[2] = prmt(t2.y, t3.y, 0x5410u); vhi[3] = prmt(t2.y, t3.y, 0x7632u);
-  }
   const uint32_t vrow = tv.vrow;
-  if constexpr (BITS == 8) {
-    static_for<4>([&](auto ic) {  // pieces 2i, 2i+1 = the two halves of V group i
-      constexpr int i = decltype(ic)::value;
-      uint32_t Q[4];
-      ldsm_x4_t<i * 32>(Q, vrow);
-      const uint32_t b0 = hmul2u(pb0, vlo[i]), b1 = hmul2u(pb1, vhi[i]);
+  if constexpr (BITS != 2) {
+    uint32_t b0[NG], b1[NG];
+    {
+      const uint2 s0 = lds64<0>(tv.vs_row), s1 = lds64<8 * H * NG * 2>(tv.vs_row);
+      b0[0] = movm_t(hmul2u(p_lo, prmt(s0.x, s0.x, 0x1010u))); b0[1] = movm_t(hmul2u(p_lo, prmt(s0.x, s0.x, 0x3232u)));
+      b0[2] = movm_t(hmul2u(p_lo, prmt(s0.y, s0.y, 0x1010u))); b0[3] = movm_t(hmul2u(p_lo, prmt(s0.y, s0.y, 0x3232u)));
+      b1[0] = movm_t(hmul2u(p_hi, prmt(s1.x, s1.x, 0x1010u))); b1[1] = movm_t(hmul2u(p_hi, prmt(s1.x, s1.x, 0x3232u)));
+      b1[2] = movm_t(hmul2u(p_hi, prmt(s1.y, s1.y, 0x1010u))); b1[3] = movm_t(hmul2u(p_hi, prmt(s1.y, s1.y, 0x3232u)));
+    }
+    if constexpr (BITS == 8) {
+      static_for<4>([&](auto ic) {  // pieces 2i, 2i+1 = the two halves of V group i
+        constexpr int i = decltype(ic)::value;
+        uint32_t Q[4];
+        ldsm_x4_t<i * 32>(Q, vrow);
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        uint32_t lo[2], hi[2];
-        sub8_t(Q[2 * e], lo);
-        sub8_t(Q[2 * e + 1], hi);
-        mma16816(w.acc[2 * i + e], lo[0], lo[1], hi[0], hi[1], b0, b1);
-      }
-    });
-  } else if constexpr (BITS == 4) {
-    static_for<2>([&](auto ic) {  // pieces 2i, 2i+1 = V groups 2i, 2i+1
-      constexpr int i = decltype(ic)::value;
-      uint32_t Q[4];
-      ldsm_x4_t<i * 32>(Q, vrow);
+        for (int e = 0; e < 2; ++e) {
+          uint32_t lo[2], hi[2];
+          sub8_t(Q[2 * e], lo);
+          sub8_t(Q[2 * e + 1], hi);
+          mma16816(w.acc[2 * i + e], lo[0], lo[1], hi[0], hi[1], b0[i], b1[i]);
+        }
+      });
+    } else {
+      static_for<2>([&](auto ic) {  // pieces 2i, 2i+1 = V groups 2i, 2i+1
+        constexpr int i = decltype(ic)::value;
+        uint32_t Q[4];
+        ldsm_x4_t<i * 32>(Q, vrow);
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int G = 2 * i + e;
-        const uint32_t b0 = hmul2u(pb0, vlo[G]), b1 = hmul2u(pb1, vhi[G]);
-        uint32_t lo[4], hi[4];
-        sub4(Q[2 * e], lo);
-        sub4(Q[2 * e + 1], hi);
-        mma16816(w.acc[2 * G], lo[0], lo[1], hi[0], hi[1], b0, b1);
-        mma16816(w.acc[2 * G + 1], lo[2], lo[3], hi[2], hi[3], b0, b1);
-      }
-    });
+        for (int e = 0; e < 2; ++e) {
+          const int G = 2 * i + e;
+          uint32_t lo[4], hi[4];
+          sub4(Q[2 * e], lo);
+          sub4(Q[2 * e + 1], hi);
+          mma16816(w.acc[2 * G], lo[0], lo[1], hi[0], hi[1], b0[G], b1[G]);
+          mma16816(w.acc[2 * G + 1], lo[2], lo[3], hi[2], hi[3], b0[G], b1[G]);
+        }
+      });
+    }
   } else {
+    // V scale of this lane's four tokens, all NG groups: vlo[G] = {vs[2j][G], vs[2j+1][G]}, vhi[G] likewise +8
+    uint32_t vlo[NG], vhi[NG];
+    {
+      uint2 t0, t1, t2, t3;
+      const uint32_t base = tv.vs, tok = tv.tok;
+      asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t0.x), "=r"(t0.y) : "r"(base));
+      asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t1.x), "=r"(t1.y) : "r"(base + tok));
+      asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t2.x), "=r"(t2.y) : "r"(base + 8 * tok));
+      asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t3.x), "=r"(t3.y) : "r"(base + 9 * tok));
+      vlo[0] = prmt(t0.x, t1.x, 0x5410u); vlo[1] = prmt(t0.x, t1.x, 0x7632u);
+      vlo[2] = prmt(t0.y, t1.y, 0x5410u); vlo[3] = prmt(t0.y, t1.y, 0x7632u);
+      vhi[0] = prmt(t2.x, t3.x, 0x5410u); vhi[1] = prmt(t2.x, t3.x, 0x7632u);
+      vhi[2] = prmt(t2.y, t3.y, 0x5410u); vhi[3] = prmt(t2.y, t3.y, 0x7632u);
+    }
     uint32_t Q[4];
     ldsm_x4_t<0>(Q, vrow);  // pieces 0, 1 = V groups {0,1}, {2,3}; this lane's channels lie in group 2q + (r >= 4)
 #pragma unroll
@@ -563,6 +590,12 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t 
   }
 }
 
+// Row of the [v_min | ones] MMA that carries the bias of V group G for KV head h: with two or more
+// heads the v_min fragment is read with ldmatrix over pairs of heads (16-byte rows), so the odd head
+// of a pair sits in rows 4..7.
+template <int H>
+__device__ __forceinline__ int bias_row(int G, int h) { return H >= 2 ? G + 4 * (h & 1) : G; }
+
 // A warp's two query copies in shared memory (see QT_ROW / QN_ROW).
 struct QView {
   unsigned char *qn, *qt;      // natural copy [rows][QN_ROW], tier-scaled copy [rows][QT_ROW]
@@ -571,7 +604,7 @@ struct QView {
   uint32_t qn_ld;              // this lane's ldmatrix row address in the natural copy
 };
 
-template <int BITS>
+template <int BITS, int H>
 __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv, const StageInfo& si, const QView& qv,
                                              int h, int lane, WarpState& w, float* remap, int* lock, bool& ok) {
   const int r = lane >> 2, j = lane & 3;
@@ -636,8 +669,12 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
   const uint32_t pb0 = movm_t(p_lo), pb1 = movm_t(p_hi);
   PROF_T(f2);
   PROF_PHASE(1, f1, f2);
-  // [v_min | ones] rows: bias of V group r (lanes r < NG) and the softmax denominator
-  {
+  // [v_min | ones] rows: the bias of every V group and the softmax denominator
+  if constexpr (H >= 2) {
+    uint32_t X[2];
+    ldsm_x2_t(X, tv.vm_ld);  // rows: groups of this pair of heads (row bias_row(G, h) is ours), k: tokens
+    mma16816(w.bl, X[0], H2_ONE, X[1], H2_ONE, pb0, pb1);
+  } else {
     const uint32_t base = tv.vm, tok = tv.tok;  // lanes r >= NG read group 0 and mask it to zero
     uint32_t x0, x1, x2, x3;
     asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x0) : "r"(base));
@@ -649,7 +686,7 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
   }
   PROF_T(f3);
   PROF_PHASE(2, f2, f3);
-  pv_codes<BITS>(tv, lane, pb0, pb1, w);
+  pv_codes<BITS, H>(tv, lane, p_lo, p_hi, pb0, pb1, w);
   PROF_T(f4);
   PROF_PHASE(3, f3, f4);
 }
@@ -696,7 +733,7 @@ __device__ __forceinline__ BlockMeta load_meta(const Params& P, int64_t bt_row, 
   return m;
 }
 
-template <int BITS>
+template <int BITS, int H>
 __device__ __forceinline__ void write_partial(const Params& P, const WarpState& w, int seq, int split, int h, int lane) {
   const int r = lane >> 2, j = lane & 3;
   const DecodeArgs& A = P.A;
@@ -710,8 +747,8 @@ __device__ __forceinline__ void write_partial(const Params& P, const WarpState& 
     if constexpr (BITS == 8) G = mt >> 1;
     else if constexpr (BITS == 4) G = mt >> 1;
     else G = 2 * (mt >> 2) + (r >= 4 ? 1 : 0);
-    const float bias0 = __shfl_sync(0xffffffffu, w.bl[0], G * 4 + j);
-    const float bias1 = __shfl_sync(0xffffffffu, w.bl[1], G * 4 + j);
+    const float bias0 = __shfl_sync(0xffffffffu, w.bl[0], bias_row<H>(G, h) * 4 + j);
+    const float bias1 = __shfl_sync(0xffffffffu, w.bl[1], bias_row<H>(G, h) * 4 + j);
     const int c0 = acc_channel<BITS>(mt, r, 0), c1 = acc_channel<BITS>(mt, r, 1);
     if (g0 < A.gqa) {
       A.acc[o0 * D + c0] = fmaf(w.acc[mt][0], acc_unit<BITS>(0), bias0);
@@ -1009,10 +1046,11 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
       tv.vrow = c_sb + (si.bits == 8 ? lc.v8 : (si.bits == 4 ? lc.v4 : lc.v2));
       tv.vs = c_sb + P.o_vs + lc.vs_off; tv.vm = c_sb + P.o_vm + lc.vm_off;
       tv.ks = c_sb + P.o_ks + lc.ksm_off; tv.km = c_sb + P.o_km + lc.ksm_off; tv.tok = lc.tok;
+      tv.vs_row = c_sb + P.o_vs + lc.vs_row; tv.vm_ld = c_sb + P.o_vm + lc.vm_ld;
       if (si.n_valid > 0 && (P.debug & 3) != 1) {
-        if (si.bits == 4) process_tile<4>(P, tv, si, qv, h, lane, w, remap, lock, ok);
-        else if (si.bits == 8) process_tile<8>(P, tv, si, qv, h, lane, w, remap, lock, ok);
-        else process_tile<2>(P, tv, si, qv, h, lane, w, remap, lock, ok);
+        if (si.bits == 4) process_tile<4, H>(P, tv, si, qv, h, lane, w, remap, lock, ok);
+        else if (si.bits == 8) process_tile<8, H>(P, tv, si, qv, h, lane, w, remap, lock, ok);
+        else process_tile<2, H>(P, tv, si, qv, h, lane, w, remap, lock, ok);
       }
       __syncwarp();
       PROF_T(w3);
@@ -1020,9 +1058,9 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
       if (lane == 0) mbar_arrive(sempty + c_st);
       if (++c_st == NS) { c_st = 0; c_sb = ring_u; ++c_round; } else { c_sb += stage_bytes; }
       if (flags & F_LAST) {
-        if (w.bits == 4) write_partial<4>(P, w, seq, split, h, lane);
-        else if (w.bits == 8) write_partial<8>(P, w, seq, split, h, lane);
-        else write_partial<2>(P, w, seq, split, h, lane);
+        if (w.bits == 4) write_partial<4, H>(P, w, seq, split, h, lane);
+        else if (w.bits == 8) write_partial<8, H>(P, w, seq, split, h, lane);
+        else write_partial<2, H>(P, w, seq, split, h, lane);
         PROF_T(w4);
         PROF_ADD(c_item, w3, w4);
       }
