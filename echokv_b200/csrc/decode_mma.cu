@@ -156,6 +156,26 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
   asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
   return v;
 }
+// The same loads for lanes where `on` holds; the other lanes get zeros and cost no shared-memory
+// traffic (a quarter warp without an active lane issues no wavefront).
+template <int OFF>
+__device__ __forceinline__ void lds128_if(uint32_t (&r)[4], uint32_t addr, uint32_t on) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t"
+      "mov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t"
+      "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%6];\n\t}"
+      : "=&r"(r[0]), "=&r"(r[1]), "=&r"(r[2]), "=&r"(r[3]) : "r"(addr), "r"(on), "n"(OFF));
+}
+template <int OFF>
+__device__ __forceinline__ uint2 lds64_if(uint32_t addr, uint32_t on) {
+  uint2 v;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %3, 0;\n\t"
+      "mov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\t"
+      "@p ld.shared.v2.u32 {%0,%1}, [%2+%4];\n\t}"
+      : "=&r"(v.x), "=&r"(v.y) : "r"(addr), "r"(on), "n"(OFF));
+  return v;
+}
 __device__ __forceinline__ uint32_t movm_t(uint32_t a) {
   uint32_t d;
   asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
@@ -404,8 +424,11 @@ __device__ __forceinline__ void km_term(uint32_t km, uint32_t qn_ld, int lane, f
   });
 }
 
+// `real`: this lane's MMA column (query head lane / 4 of the group) exists; the other lanes' B
+// fragments are zero, so they skip the loads of the query and the K scales.
 template <int BITS>
-__device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t qt_lane, uint32_t qn_ld, int lane, float (&c)[4]) {
+__device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t qt_lane, uint32_t qn_ld, int lane, uint32_t real,
+                                         float (&c)[4]) {
   const int j = lane & 3;
   const uint32_t krow = tv.krow;
   float c2[4] = {0.f, 0.f, 0.f, 0.f};
@@ -418,7 +441,7 @@ __device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t qt_lane, u
       ldsm_x4<i * 32>(R, krow);
       static_for<2>([&](auto ec) {
         constexpr int e = decltype(ec)::value, p = 2 * i + e;
-        const uint2 qw = lds64<32 * p>(qb), sw = lds64<32 * p>(sb);
+        const uint2 qw = lds64_if<32 * p>(qb, real), sw = lds64_if<32 * p>(sb, real);
         uint32_t a[2], b[2];
         sub8(R[2 * e], a);
         sub8(R[2 * e + 1], b);
@@ -436,8 +459,8 @@ __device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t qt_lane, u
       static_for<2>([&](auto ec) {
         constexpr int e = decltype(ec)::value, p = 2 * i + e;
         uint32_t W[4], S[4], Z[4];
-        lds128<64 * p>(W, qb);
-        lds128<64 * p>(S, sb);
+        lds128_if<64 * p>(W, qb, real);
+        lds128_if<64 * p>(S, sb, real);
 #pragma unroll
         for (int k = 0; k < 4; ++k) Z[k] = hmul2u(W[k], S[k]);
         uint32_t a[4], b[4];
@@ -458,10 +481,10 @@ __device__ __forceinline__ void qk_codes(const TileView& tv, uint32_t qt_lane, u
       uint32_t W[8], S[8], Z[8];
       {
         uint32_t t4[4];
-        lds128<128 * p>(t4, qb);      W[0] = t4[0]; W[1] = t4[1]; W[2] = t4[2]; W[3] = t4[3];
-        lds128<128 * p + 16>(t4, qb); W[4] = t4[0]; W[5] = t4[1]; W[6] = t4[2]; W[7] = t4[3];
-        lds128<128 * p>(t4, sb);      S[0] = t4[0]; S[1] = t4[1]; S[2] = t4[2]; S[3] = t4[3];
-        lds128<128 * p + 16>(t4, sb); S[4] = t4[0]; S[5] = t4[1]; S[6] = t4[2]; S[7] = t4[3];
+        lds128_if<128 * p>(t4, qb, real);      W[0] = t4[0]; W[1] = t4[1]; W[2] = t4[2]; W[3] = t4[3];
+        lds128_if<128 * p + 16>(t4, qb, real); W[4] = t4[0]; W[5] = t4[1]; W[6] = t4[2]; W[7] = t4[3];
+        lds128_if<128 * p>(t4, sb, real);      S[0] = t4[0]; S[1] = t4[1]; S[2] = t4[2]; S[3] = t4[3];
+        lds128_if<128 * p + 16>(t4, sb, real); S[4] = t4[0]; S[5] = t4[1]; S[6] = t4[2]; S[7] = t4[3];
       }
 #pragma unroll
       for (int k = 0; k < 8; ++k) Z[k] = hmul2u(W[k], S[k]);
@@ -519,7 +542,6 @@ __device__ __forceinline__ void qk_residual(const ResidualDev& R, const StageInf
 template <int BITS, int H>
 __device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t p_lo, uint32_t p_hi, uint32_t pb0,
                                          uint32_t pb1, WarpState& w) {
-  const int r = lane >> 2;
   const uint32_t vrow = tv.vrow;
   if constexpr (BITS != 2) {
     uint32_t b0[NG], b1[NG];
@@ -560,32 +582,28 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t 
       });
     }
   } else {
-    // V scale of this lane's four tokens, all NG groups: vlo[G] = {vs[2j][G], vs[2j+1][G]}, vhi[G] likewise +8
-    uint32_t vlo[NG], vhi[NG];
+    // The scale multiplies the codes (A fragments: rows = channels, register pairs = tokens 2j, 2j+1 /
+    // 2j+8, 2j+9), and a lane's channels of piece q lie in V group 2q + (r >= 4).  The scales are read in
+    // score layout (token r / r + 8, all groups: 8 bytes each) and transposed into that order with
+    // movmatrix: input column pair j carries group 2q + (j >= 2), so output lane r gets group 2q + (r >= 4).
+    uint32_t sl[2], sh[2];
     {
-      uint2 t0, t1, t2, t3;
-      const uint32_t base = tv.vs, tok = tv.tok;
-      asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t0.x), "=r"(t0.y) : "r"(base));
-      asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t1.x), "=r"(t1.y) : "r"(base + tok));
-      asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t2.x), "=r"(t2.y) : "r"(base + 8 * tok));
-      asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(t3.x), "=r"(t3.y) : "r"(base + 9 * tok));
-      vlo[0] = prmt(t0.x, t1.x, 0x5410u); vlo[1] = prmt(t0.x, t1.x, 0x7632u);
-      vlo[2] = prmt(t0.y, t1.y, 0x5410u); vlo[3] = prmt(t0.y, t1.y, 0x7632u);
-      vhi[0] = prmt(t2.x, t3.x, 0x5410u); vhi[1] = prmt(t2.x, t3.x, 0x7632u);
-      vhi[2] = prmt(t2.y, t3.y, 0x5410u); vhi[3] = prmt(t2.y, t3.y, 0x7632u);
+      const uint2 s0 = lds64<0>(tv.vs_row), s1 = lds64<8 * H * NG * 2>(tv.vs_row);
+      const uint32_t sel = (lane & 2) ? 0x3232u : 0x1010u;
+      sl[0] = movm_t(prmt(s0.x, s0.x, sel)); sl[1] = movm_t(prmt(s0.y, s0.y, sel));
+      sh[0] = movm_t(prmt(s1.x, s1.x, sel)); sh[1] = movm_t(prmt(s1.y, s1.y, sel));
     }
     uint32_t Q[4];
     ldsm_x4_t<0>(Q, vrow);  // pieces 0, 1 = V groups {0,1}, {2,3}; this lane's channels lie in group 2q + (r >= 4)
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
-      const uint32_t sl = r < 4 ? vlo[2 * q] : vlo[2 * q + 1], sh = r < 4 ? vhi[2 * q] : vhi[2 * q + 1];
       uint32_t lo[8], hi[8];
       Unpack<2>::run(Q[2 * q], lo);
       Unpack<2>::run(Q[2 * q + 1], hi);
 #pragma unroll
       for (int u = 0; u < 4; ++u)
-        mma16816(w.acc[4 * q + u], hmul2u(lo[2 * u], sl), hmul2u(lo[2 * u + 1], sl), hmul2u(hi[2 * u], sh),
-                 hmul2u(hi[2 * u + 1], sh), pb0, pb1);
+        mma16816(w.acc[4 * q + u], hmul2u(lo[2 * u], sl[q]), hmul2u(lo[2 * u + 1], sl[q]), hmul2u(hi[2 * u], sh[q]),
+                 hmul2u(hi[2 * u + 1], sh[q]), pb0, pb1);
     }
   }
 }
@@ -639,7 +657,7 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
   PROF_T(f0);
   float c[4] = {0.f, 0.f, 0.f, 0.f};
   if (si.in_res) qk_residual(P.R, si, qv.qn_lane, h, lane, c);
-  else qk_codes<BITS>(tv, qv.qt_lane, qv.qn_ld, lane, c);
+  else qk_codes<BITS>(tv, qv.qt_lane, qv.qn_ld, lane, (uint32_t)(r < P.A.gqa), c);
   PROF_T(f1);
   PROF_PHASE(0, f0, f1);
   if (r >= si.n_valid) { c[0] = -INFINITY; c[1] = -INFINITY; }
