@@ -39,6 +39,7 @@ from echokv_b200.config import load_config
 from echokv_b200.controller import LayerController
 from echokv_b200.host_slots import host_lens_and_slots, is_dummy_step
 from echokv_b200.kernels.decode import decode_attention
+from echokv_b200.kernels.write import gather_rows
 from echokv_b200.kernels.prefill import ROW_PATH_MAX_CHUNK, build_dense, build_rows, prefill_attention
 from echokv_b200.step import GroupRunner, StepMeta
 from echokv_b200.tiered_cache import TieredLayout
@@ -357,7 +358,7 @@ class EchoKVAttentionImpl(AttentionImpl[EchoKVMetadata]):
                              num_splits=md.num_splits)
         # A graph captures the copy unconditionally: its row indices are valid either way.
         if md.fire or _capturing(query):
-            torch.index_select(query, 0, md.canary_rows, out=self.stash)
+            gather_rows(query, md.canary_rows, self.stash)
         return output
 
 

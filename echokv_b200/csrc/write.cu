@@ -15,20 +15,33 @@ __global__ void write_headers_kernel(uint8_t* pages, int64_t ps, const int64_t* 
   *reinterpret_cast<uint4*>(pages + blocks[i] * ps) = h;
 }
 
+// dst row i = src row rows[i], 16 bytes per thread.
+__global__ void gather_rows_kernel(const uint4* __restrict__ src, int64_t src_stride16, const int64_t* __restrict__ rows,
+                                   uint4* __restrict__ dst, int64_t n, int row16) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= n * row16) return;
+  const int64_t r = i / row16;
+  const int c = (int)(i % row16);
+  dst[i] = src[rows[r] * src_stride16 + c];
+}
+
 __global__ void scatter_i64_kernel(int64_t* dst, const int64_t* idx, const int64_t* val, int64_t n) {
   int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (i < n) dst[idx[i]] = val[i];
 }
 
-// One warp per token row (kernels/write.py:171-229 does one program per (row, head)).
-template <typename T>
+// Token rows (kernels/write.py:171-229 does one program per (row, head)).  WIDE: one CTA of four warps
+// per row, a thread per 8 channels, the V group's min / max reduced over its VG / 8 neighbouring lanes
+// by shuffles (needs VG / 8 to be a power of two <= 32); otherwise one warp per row, a lane per V group.
+// Both produce the same bytes: min and max do not depend on the order of reduction.
+template <typename T, bool WIDE>
 __global__ void __launch_bounds__(WT_WARPS * 32)
 write_tokens_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restrict__ key, int64_t k_s0, int64_t k_s1,
                     const T* __restrict__ value, int64_t v_s0, int64_t v_s1, const int64_t* __restrict__ tok,
                     int64_t tok_s0, void* res, int res_dt, int64_t r_s0, int64_t r_s1, int64_t r_s2,
                     float* __restrict__ kref, int64_t kref_s0, int64_t kref_s1, int64_t n_rows, bool vec_in) {
   const int lane = threadIdx.x & 31;
-  const int64_t row = blockIdx.x * (int64_t)WT_WARPS + (threadIdx.x >> 5);
+  const int64_t row = WIDE ? (int64_t)blockIdx.x : blockIdx.x * (int64_t)WT_WARPS + (threadIdx.x >> 5);
   if (row >= n_rows) return;
   const int64_t slot = tok[row];
   if (slot < 0) return;  // padding, or a token that is not stored
@@ -40,31 +53,67 @@ write_tokens_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restric
   const int side_bytes = (L.H * L.D * bits) / 8;
   const int head_bytes = (L.D * bits) / 8;
   uint8_t* page = pages + blk * L.PS;
+  const int units = (L.H * L.D) / 8;  // 8-channel pieces of a row
+  const int first = WIDE ? threadIdx.x : lane, step = WIDE ? WT_WARPS * 32 : 32;
 
-  // V: per token, groups of VG along head_dim; one lane per group.
-  for (int gi = lane; gi < L.H * L.NG; gi += 32) {
-    const int h = gi / L.NG, g = gi % L.NG;
-    const int64_t src = row * v_s0 + h * v_s1 + (int64_t)g * L.VG;
-    float mn = INFINITY, mx = -INFINITY;
-    float x[8];
-    for (int c = 0; c < L.VG; c += 8) {
-      ld8<T>(value, src + c, vec_in, x);
+  if constexpr (WIDE) {
+    // V: per token, groups of VG along head_dim; VG / 8 neighbouring threads share a group.
+    const int upg = L.VG / 8;
+    for (int base = (threadIdx.x >> 5) * 32; base < units; base += step) {
+      const int u = base + lane;
+      const bool on = u < units;
+      const int h = on ? (u * 8) / L.D : 0, d0 = on ? (u * 8) % L.D : 0;
+      float x[8];
+      float mn = INFINITY, mx = -INFINITY;
+      if (on) {
+        ld8<T>(value, row * v_s0 + h * v_s1 + d0, vec_in, x);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) { mn = fminf(mn, x[k]); mx = fmaxf(mx, x[k]); }
-    }
-    __half s16, m16;
-    group_stats(mn, mx, levels, s16, m16);
-    const float sc = __half2float(s16), m = __half2float(m16);
-    const int64_t e = ((int64_t)off * L.H + h) * L.NG + g;
-    reinterpret_cast<__half*>(page + L.o_vs)[e] = s16;
-    reinterpret_cast<__half*>(page + L.o_vm)[e] = m16;
-    uint8_t* dst = pages + rowoff + side_bytes + h * head_bytes + (g * L.VG * bits) / 8;
-    for (int c = 0; c < L.VG; c += 8) {
-      ld8<T>(value, src + c, vec_in, x);
+        for (int k = 0; k < 8; ++k) { mn = fminf(mn, x[k]); mx = fmaxf(mx, x[k]); }
+      }
+      for (int o = 1; o < upg; o <<= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      }
+      if (!on) continue;
+      __half s16, m16;
+      group_stats(mn, mx, levels, s16, m16);
+      const float sc = __half2float(s16), m = __half2float(m16);
+      if (d0 % L.VG == 0) {
+        const int64_t e = ((int64_t)off * L.H + h) * L.NG + d0 / L.VG;
+        reinterpret_cast<__half*>(page + L.o_vs)[e] = s16;
+        reinterpret_cast<__half*>(page + L.o_vm)[e] = m16;
+      }
       uint32_t q[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) q[k] = quant_code(x[k], m, sc, levels);
-      store_packed8(dst + (c * bits) / 8, pack8(q, bits), bits);
+      store_packed8(pages + rowoff + side_bytes + h * head_bytes + (d0 * bits) / 8, pack8(q, bits), bits);
+    }
+  } else {
+    // V: per token, groups of VG along head_dim; one lane per group.
+    for (int gi = lane; gi < L.H * L.NG; gi += 32) {
+      const int h = gi / L.NG, g = gi % L.NG;
+      const int64_t src = row * v_s0 + h * v_s1 + (int64_t)g * L.VG;
+      float mn = INFINITY, mx = -INFINITY;
+      float x[8];
+      for (int c = 0; c < L.VG; c += 8) {
+        ld8<T>(value, src + c, vec_in, x);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { mn = fminf(mn, x[k]); mx = fmaxf(mx, x[k]); }
+      }
+      __half s16, m16;
+      group_stats(mn, mx, levels, s16, m16);
+      const float sc = __half2float(s16), m = __half2float(m16);
+      const int64_t e = ((int64_t)off * L.H + h) * L.NG + g;
+      reinterpret_cast<__half*>(page + L.o_vs)[e] = s16;
+      reinterpret_cast<__half*>(page + L.o_vm)[e] = m16;
+      uint8_t* dst = pages + rowoff + side_bytes + h * head_bytes + (g * L.VG * bits) / 8;
+      for (int c = 0; c < L.VG; c += 8) {
+        ld8<T>(value, src + c, vec_in, x);
+        uint32_t q[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) q[k] = quant_code(x[k], m, sc, levels);
+        store_packed8(dst + (c * bits) / 8, pack8(q, bits), bits);
+      }
     }
   }
 
@@ -74,7 +123,7 @@ write_tokens_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restric
   const int64_t kidx = kref ? tok[3 * tok_s0 + row] : -1;
   if (rslot < 0 && !sealed && kidx < 0) return;
   const int grp = off / L.KG;
-  for (int c = lane; c < (L.H * L.D) / 8; c += 32) {
+  for (int c = first; c < units; c += step) {
     const int h = (c * 8) / L.D, d0 = (c * 8) % L.D;
     float x[8];
     ld8<T>(key, row * k_s0 + h * k_s1 + d0, vec_in, x);
@@ -186,6 +235,19 @@ using namespace echokv;
 
 extern "C" {
 
+int echokv_gather_rows(const void* src, int64_t src_row_stride_bytes, const int64_t* rows, int64_t n, void* dst,
+                       int64_t row_bytes, void* stream) {
+  if (n <= 0 || row_bytes <= 0) return ECHOKV_OK;
+  if (!src || !rows || !dst) return set_error(ECHOKV_E_ARGUMENT, "gather_rows: null pointer");
+  if (row_bytes % 16 || src_row_stride_bytes % 16 || !aligned16(src) || !aligned16(dst))
+    return set_error(ECHOKV_E_ARGUMENT, "gather_rows: rows must be 16-byte aligned multiples of 16 bytes");
+  const int row16 = (int)(row_bytes / 16);
+  const int64_t total = n * row16;
+  gather_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const uint4*)src, src_row_stride_bytes / 16, rows, (uint4*)dst, n, row16);
+  return check_launch("gather_rows");
+}
+
 int echokv_write_headers(const echokv_pages* pages, const int64_t* blocks, const uint8_t* headers, int64_t n,
                          void* stream) {
   if (n <= 0) return ECHOKV_OK;
@@ -216,13 +278,19 @@ int echokv_write_tokens(const echokv_layout* layout, const echokv_pages* pages, 
   rc = make_residual(residual, &R);
   if (rc) return rc;
   if (!key || !value || !tok) return set_error(ECHOKV_E_ARGUMENT, "write_tokens: null pointer");
-  const unsigned grid = (unsigned)((n_rows + WT_WARPS - 1) / WT_WARPS);
+  const int upg = L.VG / 8;  // 8-channel pieces per V group
+  // few rows (a decode step): spread each row over a CTA to shorten the dependent chain; many rows
+  // (prefill chunks): one warp per row keeps more rows in flight per SM
+  const bool wide = n_rows <= 1024 && L.VG % 8 == 0 && upg <= 32 && (upg & (upg - 1)) == 0 && L.D % L.VG == 0;
+  const unsigned grid = wide ? (unsigned)n_rows : (unsigned)((n_rows + WT_WARPS - 1) / WT_WARPS);
   cudaStream_t st = (cudaStream_t)stream;
-#define LAUNCH(T)                                                                                              \
-  write_tokens_kernel<T><<<grid, WT_WARPS * 32, 0, st>>>(                                                      \
+#define ARGS(T)                                                                                                \
       L, (uint8_t*)pages->base, (const T*)key, k_s0, k_s1, (const T*)value, v_s0, v_s1, tok, tok_s0,            \
       const_cast<void*>(R.base), R.dtype, R.s_slot, R.s_pos, R.s_head, kref, kref_s0, kref_s1, n_rows,          \
-      vec_ok<T>(key, k_s0, k_s1) && vec_ok<T>(value, v_s0, v_s1))
+      vec_ok<T>(key, k_s0, k_s1) && vec_ok<T>(value, v_s0, v_s1)
+#define LAUNCH(T)                                                                       \
+  if (wide) write_tokens_kernel<T, true><<<grid, WT_WARPS * 32, 0, st>>>(ARGS(T));      \
+  else write_tokens_kernel<T, false><<<grid, WT_WARPS * 32, 0, st>>>(ARGS(T))
   switch (kv_dtype) {
     case ECHOKV_DT_F32: LAUNCH(float); break;
     case ECHOKV_DT_F16: LAUNCH(__half); break;
@@ -230,6 +298,7 @@ int echokv_write_tokens(const echokv_layout* layout, const echokv_pages* pages, 
     default: return set_error(ECHOKV_E_ARGUMENT, "write_tokens: bad dtype %d", kv_dtype);
   }
 #undef LAUNCH
+#undef ARGS
   return check_launch("write_tokens");
 }
 

@@ -58,3 +58,16 @@ def finalize_k(store, key: torch.Tensor, meta, full_grid: bool = False) -> None:
     N.check(N.lib.echokv_finalize_k(
         store.c_layout, store.c_pages, key.data_ptr(), key.stride(0), key.stride(1), N.dtype_code(key.dtype),
         meta.fin.data_ptr(), meta.fin_count.data_ptr(), store.c_res, n, N.stream_ptr(key.device)))
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[i] = src[rows[i]]`` along dim 0 (the canary's query stash; graph-capturable, indices on the device)."""
+    N.require_cuda(src, rows, out)
+    row_bytes = out[0].numel() * out.element_size()
+    if (src.dtype != out.dtype or src.shape[1:] != out.shape[1:] or not out.is_contiguous() or not src[0].is_contiguous()
+            or rows.dtype != torch.long or rows.numel() < out.shape[0] or row_bytes % 16
+            or (src.stride(0) * src.element_size()) % 16 or src.data_ptr() % 16 or out.data_ptr() % 16):
+        torch.index_select(src, 0, rows[: out.shape[0]], out=out)  # shapes the vector kernel does not take
+        return
+    N.check(N.lib.echokv_gather_rows(src.data_ptr(), src.stride(0) * src.element_size(), rows.data_ptr(), out.shape[0],
+                                     out.data_ptr(), row_bytes, N.stream_ptr(src.device)))

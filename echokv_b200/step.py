@@ -24,6 +24,7 @@ from echokv_b200.canary import canary_kl_ring, tp_mean
 from echokv_b200.controller import LayerController
 from echokv_b200.quant import SUPPORTED_BITS
 from echokv_b200.kernels.decode import BLOCKS_PER_SPLIT, decode_attention
+from echokv_b200.kernels.write import gather_rows
 from echokv_b200.tiered_cache import TieredKVCache, TieredLayout
 from echokv_b200.write_plan import SharedState, WriteMeta
 
@@ -217,7 +218,7 @@ class GroupRunner:
     # -- canary (reference: EchoKVMetadataBuilder._run_canary, backend.py:314-333) --------------
     def stash_queries(self, layer: int, query: torch.Tensor, meta: StepMeta) -> None:
         """Keep the step's canary query rows (graph-capturable: indices come from device metadata)."""
-        torch.index_select(query, 0, meta.canary_rows, out=self.stashes[layer])
+        gather_rows(query, meta.canary_rows, self.stashes[layer])
 
     def measure_canary(self, nq: int, tp_group=None) -> torch.Tensor | None:
         """KL at 2/4/8 bits for every layer from the stashed queries and the K_ref rings, averaged

@@ -206,6 +206,12 @@ int echokv_prefill(const void* query, int64_t q_s0, int64_t q_s1, const void* k_
                    int32_t max_chunk_len, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
                    float softmax_scale, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_size, void* stream);
 
+/* dst row i = src row rows[i] for n rows of row_bytes bytes (rows 16-byte aligned, a multiple of 16
+ * bytes long): the copy of the canary's query rows, torch.index_select(query, 0, canary_rows, out=stash)
+ * in EchoKVAttentionImpl.forward (backend.py:632-634).  `rows` int64 [n] on the device. */
+int echokv_gather_rows(const void* src, int64_t src_row_stride_bytes, const int64_t* rows, int64_t n, void* dst,
+                       int64_t row_bytes, void* stream);
+
 /* Canary attention-KL estimator, batched over layers -- canary_kl (canary.py:59-89).
  * query [L, nq, Hq, D] of q_dtype, kref float32 [L, W, H, D] oldest key first (ring
  * already unrolled: row (ring_pos + i) % W when ring_fill == W).  Scores the last
