@@ -660,8 +660,10 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
   else qk_codes<BITS>(tv, qv.qt_lane, qv.qn_ld, lane, (uint32_t)(r < P.A.gqa), c);
   PROF_T(f1);
   PROF_PHASE(0, f0, f1);
-  if (r >= si.n_valid) { c[0] = -INFINITY; c[1] = -INFINITY; }
-  if (r + 8 >= si.n_valid) { c[2] = -INFINITY; c[3] = -INFINITY; }
+  if (si.n_valid < TILE) {  // a partial tile (the sequence's last): tokens past the end do not count
+    if (r >= si.n_valid) { c[0] = -INFINITY; c[1] = -INFINITY; }
+    if (r + 8 >= si.n_valid) { c[2] = -INFINITY; c[3] = -INFINITY; }
+  }
   // online softmax over tokens (rows); columns 2j, 2j+1 belong to this lane
   float t0 = fmaxf(c[0], c[2]), t1 = fmaxf(c[1], c[3]);
 #pragma unroll
@@ -803,7 +805,7 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
   unsigned char* ring = qs + H * q_head_bytes(q_rows);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < MAX_NS; ++s) { mbar_init(sfull + s, 1); mbar_init(sempty + s, H); }
+    for (int s = 0; s < MAX_NS; ++s) { mbar_init(sfull + s, 1); mbar_init(sempty + s, H * 32); }
     *lock = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -911,7 +913,11 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
         const TilePlan& d = plan[ti];
         const int4 h0 = *reinterpret_cast<const int4*>(&d.hdr);   // bits, n_valid, flags, pos0
         const uint32_t row_bytes = 32u * H * h0.x;
+#ifdef ECHOKV_PROFILE
         const bool copy = h0.y > 0 && (P.debug & 3) != 2;
+#else
+        const bool copy = h0.y > 0;
+#endif
         PROF_T(w0);
         if (round > 0 && !mbar_wait(sempty + st, (round - 1) & 1)) { ok = false; break; }
         PROF_T(w1);
@@ -981,7 +987,9 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
       qv.qn_ld = smem_u32(qv.qn + ld_row * QN_ROW + (lane >> 3) * 16);
       for (int i = lane; i < D / 2; i += 32) *reinterpret_cast<uint32_t*>(qv.qn + A.gqa * QN_ROW + i * 4) = 0u;
     }
-    const LaneConst lc = lane_const(H, h, lane);
+    LaneConst lc = lane_const(H, h, lane);
+    // fold the stage offsets of the stats arrays in: [vs | vm | ks | km] follow the token rows
+    lc.vs_off += P.o_vs; lc.vs_row += P.o_vs; lc.vm_off += P.o_vm; lc.vm_ld += P.o_vm; lc.ksm_off += P.o_ks;
     const uint32_t ring_u = smem_u32(ring);
     const uint32_t stage_bytes = P.stage_bytes;
     int c_st = 0, c_round = 0;                  // stage being consumed and how often it has been consumed
@@ -1062,10 +1070,14 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
       TileView tv;
       tv.krow = c_sb + (si.bits == 8 ? lc.k8 : (si.bits == 4 ? lc.k4 : lc.k2));
       tv.vrow = c_sb + (si.bits == 8 ? lc.v8 : (si.bits == 4 ? lc.v4 : lc.v2));
-      tv.vs = c_sb + P.o_vs + lc.vs_off; tv.vm = c_sb + P.o_vm + lc.vm_off;
-      tv.ks = c_sb + P.o_ks + lc.ksm_off; tv.km = c_sb + P.o_km + lc.ksm_off; tv.tok = lc.tok;
-      tv.vs_row = c_sb + P.o_vs + lc.vs_row; tv.vm_ld = c_sb + P.o_vm + lc.vm_ld;
+      tv.vs = c_sb + lc.vs_off; tv.vm = c_sb + lc.vm_off;
+      tv.ks = c_sb + lc.ksm_off; tv.km = tv.ks + H * D * 2; tv.tok = H * NG * 2;
+      tv.vs_row = c_sb + lc.vs_row; tv.vm_ld = c_sb + lc.vm_ld;
+#ifdef ECHOKV_PROFILE
       if (si.n_valid > 0 && (P.debug & 3) != 1) {
+#else
+      if (si.n_valid > 0) {
+#endif
         if (si.bits == 4) process_tile<4, H>(P, tv, si, qv, h, lane, w, remap, lock, ok);
         else if (si.bits == 8) process_tile<8, H>(P, tv, si, qv, h, lane, w, remap, lock, ok);
         else process_tile<2, H>(P, tv, si, qv, h, lane, w, remap, lock, ok);
@@ -1073,7 +1085,7 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
       __syncwarp();
       PROF_T(w3);
       PROF_ADD(c_math, w2, w3);
-      if (lane == 0) mbar_arrive(sempty + c_st);
+      mbar_arrive(sempty + c_st);  // every lane arrives (the barrier counts threads): no branch, no warp sync needed
       if (++c_st == NS) { c_st = 0; c_sb = ring_u; ++c_round; } else { c_sb += stage_bytes; }
       if (flags & F_LAST) {
         if (w.bits == 4) write_partial<4, H>(P, w, seq, split, h, lane);

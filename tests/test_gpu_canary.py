@@ -41,3 +41,24 @@ def test_ring_cursor_equals_unrolled_view_and_bf16_inputs():
     assert sub.shape == (1,) and sub.dtype == torch.float32
     with pytest.raises(ValueError):
         canary_kl_ring(q, ring, 0, 10, 16, 0.1)
+
+
+def test_gather_rows_equals_index_select():
+    """The canary's query stash (backend.py:632-634 in the reference is an index_select)."""
+    import torch
+    from echokv_b200.kernels.write import gather_rows
+
+    g = torch.Generator("cuda").manual_seed(5)
+    q = torch.randn(70, 32, 128, device="cuda", generator=g).bfloat16()
+    rows = torch.tensor([69, 0, 3, 3, 41, 7, 0, 0], device="cuda")
+    out = torch.zeros(8, 32, 128, device="cuda", dtype=torch.bfloat16)
+    gather_rows(q, rows, out)
+    assert torch.equal(out, q[rows])
+    part = q[:, :6, :]  # a view with a larger row stride than the row itself
+    out2 = torch.zeros(5, 6, 128, device="cuda", dtype=torch.bfloat16)
+    gather_rows(part, rows, out2)
+    assert torch.equal(out2, part[rows[:5]])
+    odd = torch.randn(9, 3, 5, device="cuda", generator=g)  # rows that are not a multiple of 16 bytes
+    out3 = torch.zeros(2, 3, 5, device="cuda")
+    gather_rows(odd, rows[1:3], out3)
+    assert torch.equal(out3, odd[rows[1:3]])

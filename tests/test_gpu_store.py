@@ -49,6 +49,28 @@ def test_full_grid_masked_launch_stores_same_bytes(name):
     compare_store(sc, got, run_oracle(sc), load_golden(sc.name))
 
 
+def test_bulk_write_over_1024_rows_takes_the_warp_per_row_kernel():
+    """Steps of more than 1,024 rows use the warp-per-row shape of the token kernel, smaller ones the
+    CTA-per-row shape: both must store the bytes the oracle stores (mixed tiers, a partial last group)."""
+    from cuda_runner import run_cuda
+
+    rng = np.random.default_rng(77)
+    h, d, bs, n = 2, 128, 32, 1100
+    blocks = -(-n // bs)
+    sp = S.StoreSpec(h=h, d=d, bs=bs, mem_bits=8, kg=32, vg=32, num_blocks=blocks + 2, residual_slots=4, dtype="bf16",
+                     kref_window=32)
+    k = S.round_to(rng.standard_normal((n, h, d), dtype=np.float32), "bf16")
+    v = S.round_to(rng.standard_normal((n, h, d), dtype=np.float32) * 3, "bf16")
+    perm = rng.permutation(blocks + 2)[:blocks]
+    pos = np.arange(n)
+    slots = perm[pos // bs].astype(np.int64) * bs + pos % bs
+    pad = np.full(1500, -1, dtype=np.int64)  # a second step of padding rows only: nothing is stored
+    sc = S.Scenario("bulk_1100", sp, [(k, v, slots, 4), (np.tile(k[:1], (1500, 1, 1)), np.tile(v[:1], (1500, 1, 1)), pad, 8)])
+    sc.use_kref = True
+    got = run_cuda(sc)
+    compare_store(sc, got, run_oracle(sc))
+
+
 def test_layout_errors_and_cpu_tensors_rejected():
     import torch
 
