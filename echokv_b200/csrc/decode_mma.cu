@@ -365,16 +365,19 @@ struct LaneConst {
 __device__ __forceinline__ LaneConst lane_const(int H, int h, int lane) {
   LaneConst c;
   const int r = lane >> 2, j = lane & 3, mi = lane >> 3;
-  // row stride = [K codes | V codes] of all heads + 16 bytes of padding = 32 * H * bits + 16
-  const uint32_t row = (lane & 7) + 8 * (mi & 1), piece = (mi >> 1) * 16u;
-  c.k2 = row * (64u * H + 16u) + h * 32u + piece;   c.v2 = c.k2 + 32u * H;
-  c.k4 = row * (128u * H + 16u) + h * 64u + piece;  c.v4 = c.k4 + 64u * H;
-  c.k8 = row * (256u * H + 16u) + h * 128u + piece; c.v8 = c.k8 + 128u * H;
+  // Token rows are staged in pairs (tokens 2p, 2p+1 back to back, as they lie in the page, then 16 bytes
+  // of padding), and the MMA's token rows are permuted to match: row rho of the first eight is token
+  // 2 * rho, row rho of the second eight is token 2 * rho + 1.  The eight rows one ldmatrix piece reads
+  // are then 2 * row_bytes + 16 apart: conflict free.  row_bytes = 32 * H * bits.
+  const uint32_t pr = lane & 7, odd = mi & 1, piece = (mi >> 1) * 16u;
+  c.k2 = pr * (128u * H + 16u) + odd * (64u * H) + h * 32u + piece;    c.v2 = c.k2 + 32u * H;
+  c.k4 = pr * (256u * H + 16u) + odd * (128u * H) + h * 64u + piece;   c.v4 = c.k4 + 64u * H;
+  c.k8 = pr * (512u * H + 16u) + odd * (256u * H) + h * 128u + piece;  c.v8 = c.k8 + 128u * H;
   c.tok = (uint32_t)H * NG * 2;
-  c.vs_off = (uint32_t)((2 * j) * H + h) * NG * 2;
+  c.vs_off = (uint32_t)((4 * j) * H + h) * NG * 2;
   c.vm_off = c.vs_off + (uint32_t)(r < NG ? r : 0) * 2;
-  c.vs_row = (uint32_t)(r * H + h) * NG * 2;
-  c.vm_ld = (uint32_t)((lane & 15) * H + (h & ~1)) * NG * 2;
+  c.vs_row = (uint32_t)(2 * r * H + h) * NG * 2;  // token 2r; token 2r + 1 (MMA row r + 8) is one token further
+  c.vm_ld = (uint32_t)((2 * (lane & 7) + ((lane >> 3) & 1)) * H + (h & ~1)) * NG * 2;  // k-order: tokens 0,2,..,14 then 1,3,..,15
   c.ksm_off = (uint32_t)h * D * 2;
   return c;
 }
@@ -518,9 +521,9 @@ __device__ __forceinline__ uint32_t res_pair(const ResidualDev& R, int64_t e) {
 __device__ __forceinline__ void qk_residual(const ResidualDev& R, const StageInfo& si, uint32_t qn_lane, int h, int lane,
                                             float (&c)[4]) {
   const int r = lane >> 2, j = lane & 3;
-  const bool v0 = r < si.n_valid, v1 = r + 8 < si.n_valid;
-  const int64_t e0 = si.res_slot * R.s_slot + (int64_t)(si.pos0 + r) * R.s_pos + h * R.s_head;
-  const int64_t e1 = e0 + 8 * R.s_pos;
+  const bool v0 = 2 * r < si.n_valid, v1 = 2 * r + 1 < si.n_valid;  // MMA rows r / r + 8 are tokens 2r / 2r + 1
+  const int64_t e0 = si.res_slot * R.s_slot + (int64_t)(si.pos0 + 2 * r) * R.s_pos + h * R.s_head;
+  const int64_t e1 = e0 + R.s_pos;
   const uint32_t qb = qn_lane + j * 8;
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
@@ -546,7 +549,7 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t 
   if constexpr (BITS != 2) {
     uint32_t b0[NG], b1[NG];
     {
-      const uint2 s0 = lds64<0>(tv.vs_row), s1 = lds64<8 * H * NG * 2>(tv.vs_row);
+      const uint2 s0 = lds64<0>(tv.vs_row), s1 = lds64<H * NG * 2>(tv.vs_row);
       b0[0] = movm_t(hmul2u(p_lo, prmt(s0.x, s0.x, 0x1010u))); b0[1] = movm_t(hmul2u(p_lo, prmt(s0.x, s0.x, 0x3232u)));
       b0[2] = movm_t(hmul2u(p_lo, prmt(s0.y, s0.y, 0x1010u))); b0[3] = movm_t(hmul2u(p_lo, prmt(s0.y, s0.y, 0x3232u)));
       b1[0] = movm_t(hmul2u(p_hi, prmt(s1.x, s1.x, 0x1010u))); b1[1] = movm_t(hmul2u(p_hi, prmt(s1.x, s1.x, 0x3232u)));
@@ -588,7 +591,7 @@ __device__ __forceinline__ void pv_codes(const TileView& tv, int lane, uint32_t 
     // movmatrix: input column pair j carries group 2q + (j >= 2), so output lane r gets group 2q + (r >= 4).
     uint32_t sl[2], sh[2];
     {
-      const uint2 s0 = lds64<0>(tv.vs_row), s1 = lds64<8 * H * NG * 2>(tv.vs_row);
+      const uint2 s0 = lds64<0>(tv.vs_row), s1 = lds64<H * NG * 2>(tv.vs_row);
       const uint32_t sel = (lane & 2) ? 0x3232u : 0x1010u;
       sl[0] = movm_t(prmt(s0.x, s0.x, sel)); sl[1] = movm_t(prmt(s0.y, s0.y, sel));
       sh[0] = movm_t(prmt(s1.x, s1.x, sel)); sh[1] = movm_t(prmt(s1.y, s1.y, sel));
@@ -661,8 +664,8 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
   PROF_T(f1);
   PROF_PHASE(0, f0, f1);
   if (si.n_valid < TILE) {  // a partial tile (the sequence's last): tokens past the end do not count
-    if (r >= si.n_valid) { c[0] = -INFINITY; c[1] = -INFINITY; }
-    if (r + 8 >= si.n_valid) { c[2] = -INFINITY; c[3] = -INFINITY; }
+    if (2 * r >= si.n_valid) { c[0] = -INFINITY; c[1] = -INFINITY; }      // MMA row r is token 2r
+    if (2 * r + 1 >= si.n_valid) { c[2] = -INFINITY; c[3] = -INFINITY; }  // MMA row r + 8 is token 2r + 1
   }
   // online softmax over tokens (rows); columns 2j, 2j+1 belong to this lane
   float t0 = fmaxf(c[0], c[2]), t1 = fmaxf(c[1], c[3]);
@@ -697,10 +700,10 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
   } else {
     const uint32_t base = tv.vm, tok = tv.tok;  // lanes r >= NG read group 0 and mask it to zero
     uint32_t x0, x1, x2, x3;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x0) : "r"(base));
-    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x1) : "r"(base + tok));
-    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x2) : "r"(base + 8 * tok));
-    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x3) : "r"(base + 9 * tok));
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x0) : "r"(base));            // token 4j     (k slot 2j)
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x1) : "r"(base + 2 * tok));  // token 4j + 2 (k slot 2j + 1)
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x2) : "r"(base + tok));      // token 4j + 1 (k slot 2j + 8)
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x3) : "r"(base + 3 * tok));  // token 4j + 3 (k slot 2j + 9)
     const uint32_t keep = r < NG ? 0xffffffffu : 0u;
     mma16816(w.bl, prmt(x0, x1, 0x5410u) & keep, H2_ONE, prmt(x2, x3, 0x5410u) & keep, H2_ONE, pb0, pb1);
   }
@@ -932,7 +935,8 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
         }
         __syncwarp();
         if (copy) {
-          if (lane < h0.y) bulk_copy(st_u + lane * (row_bytes + 16), d.row_src[lane], row_bytes, bar);
+          // lane p < 8 copies tokens 2p and 2p + 1 in one piece (neighbours in their chunk: a chunk holds an even number of tokens)
+          if (lane < 8) { if (2 * lane < h0.y) bulk_copy(st_u + lane * (2 * row_bytes + 16), d.row_src[2 * lane], (2 * lane + 1 < h0.y ? 2u : 1u) * row_bytes, bar); }
           else if (contig) { if (lane == 16) bulk_copy(st_u + P.o_vs, d.stats[0], stat_bytes, bar); }
           else if (lane >= 16 && lane < 20) {
             const int which = lane - 16;  // vs, vm, ks, km
