@@ -4,9 +4,10 @@
 // is one producer warp plus H consumer warps, one per KV head.  The producer resolves block table
 // -> page header -> chunk ids -> residual map for up to 32 blocks at a time and streams 16-token
 // tiles into a ring of shared-memory stages with bulk asynchronous copies (cp.async.bulk +
-// mbarrier complete_tx): every token's [K codes | V codes] row goes to a slot padded by 16 bytes
-// (so ldmatrix over 8 token rows is bank-conflict free), plus the tile's V stats and its K group's
-// per-channel stats and a small header (tier, valid tokens, item start / end).  Consumers wait
+// mbarrier complete_tx): the [K codes | V codes] rows of two neighbouring tokens go to a slot padded
+// by 16 bytes (the MMA's token rows are permuted -- even tokens first, then odd -- so that ldmatrix
+// over 8 rows stays bank-conflict free), plus the tile's V stats and its K group's per-channel stats
+// and a small header (tier, valid tokens, item start / end).  Consumers wait
 // for a stage's `full` barrier, compute, and arrive on its `empty` barrier; nothing in the loop
 // synchronises the whole CTA.  Per tile a consumer warp
 //   * folds the K group's per-channel scale into the query (q' = q * k_scale, fp16) and adds the
@@ -725,8 +726,8 @@ __device__ __forceinline__ void process_tile(const Params& P, const TileView& tv
 // in parallel (lane l writes tile l's header and copy sources to shared memory) and then feeds the
 // stage ring tile by tile: wait until every consumer warp has released the stage, write the tile's
 // header, and start the tile's copies as bulk asynchronous copies that report their bytes to the
-// stage's `full` mbarrier -- lane t copies token row t (to a slot padded by 16 bytes so ldmatrix over
-// 8 rows is conflict free), lanes 16.. copy the V / K stats.  Consumers only wait for `full`,
+// stage's `full` mbarrier -- lane p < 8 copies token rows 2p and 2p + 1 in one piece (to a slot padded
+// by 16 bytes), lanes 16.. copy the V / K stats.  Consumers only wait for `full`,
 // compute, and arrive on `empty`; the header tells them where a work item starts (load the query,
 // reset the accumulators) and ends (write the split's partial result).  There is no CTA-wide barrier
 // in the loop.
