@@ -37,8 +37,8 @@ sys.path.insert(0, str(ROOT))
 HQ, H, D, BS, KG, VG, MEM_BITS = 32, 8, 128, 16, 16, 32, 8
 METRIC = "decode tokens/s/GPU at INT4 KV; paged-decode attention HBM GB/s vs peak"
 # dram__bytes_read.sum + dram__bytes_write.sum of one INT4 decode launch at batch 64 x ctx 4096 from the
-# ncu capture summarised under profiles/ (reads 378 MB of pages, writes 16 MB of split partials)
-DRAM_TRAFFIC_INT4 = 394_000_000
+# ncu capture summarised under profiles/ (reads 376 MB of pages, writes 14 MB of split partials)
+DRAM_TRAFFIC_INT4 = 390_500_000
 
 
 def parse():
