@@ -54,6 +54,7 @@ def parse():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph")
     ap.add_argument("--cpu-seqs", type=int, default=4, help="sequences in the CPU-baseline sample")
     ap.add_argument("--canary-interval", type=int, default=8, help="measure the canary KL every N steps (0 = never)")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill probe (configuration 3 shape)")
     ap.add_argument("--tiers", default="", help="comma list of tiers cycled over the layers instead of the seeded draw "
                                                 "(small profiling cases, e.g. --layers 2 --tiers 4)")
     return ap.parse_args()
@@ -171,6 +172,69 @@ def cpu_baseline(a, tiers, workers: int, n_seqs: int, layers_sample: int) -> dic
     return {"value": a.batch / step_seconds, "unit": "tokens/s", "cores": workers, "kind": "port",
             "sample": f"{n_seqs} sequences x {layers_sample} layers of ctx {a.ctx} (one-token write + decode attention, "
                       f"numpy oracle), scaled to batch {a.batch} x {a.layers} layers; context build untimed; wall {wall:.1f}s"}
+
+
+def prefill_probe(dev, peaks: dict, seed: int) -> dict:
+    """Chunked prefill at the shape of configuration 3 (8 sequences, a 512-token chunk at the end of a context of
+    8,704 stored tokens, layers at INT4 and INT8): dense dequantization + the attention kernel, timed with CUDA
+    events; the tensor-pipe figure counts the attention kernel's FLOPs only."""
+    import torch
+
+    from echokv_b200.controller import ControllerParams, LayerController
+    from echokv_b200.kernels.prefill import build_dense, dense_attention, dequant_dense
+    from echokv_b200.step import GroupRunner
+    from echokv_b200.tiered_cache import TieredLayout
+
+    S, nq, prefix = 8, 512, 8192
+    ctx = prefix + nq
+    tiers = [4, 8]
+    layout = TieredLayout(num_kv_heads=H, head_size=D, block_size=BS, mem_bits=MEM_BITS, k_group=KG, v_group=VG)
+    bps = -(-ctx // BS)
+    nb = S * bps + 8
+    page = BS * TieredLayout.per_token_bytes(H, D, MEM_BITS, KG, VG)
+    caches = [torch.zeros(nb, page, dtype=torch.uint8, device=dev) for _ in tiers]
+    ctl = [LayerController(ControllerParams(fixed_bits=b)) for b in tiers]
+    runner = GroupRunner(layout, caches, HQ, D ** -0.5, ctl, residual_slots=S + 16, model_dtype=torch.bfloat16,
+                         cap=64, max_model_len=bps * BS)
+    table_np = np.random.default_rng(seed + 7).permutation(nb)[: S * bps].reshape(S, bps).astype(np.int32)
+    table = torch.from_numpy(table_np).to(dev)
+    gen = torch.Generator(device=dev).manual_seed(seed + 300)
+    for c0 in range(0, ctx, 512):
+        pos = np.arange(c0, min(ctx, c0 + 512))
+        slots = (table_np[:, pos // BS].astype(np.int64) * BS + pos % BS).reshape(-1)
+        meta = runner.plan_step(slots)
+        for l in range(len(tiers)):
+            k = torch.randn(slots.size, H, D, device=dev, generator=gen).bfloat16()
+            v = torch.randn(slots.size, H, D, device=dev, generator=gen).bfloat16()
+            runner.write(l, k, v, meta)
+    q = torch.randn(S * nq, HQ, D, device=dev, generator=gen).bfloat16()
+    out = torch.empty_like(q)
+    prefill = [(i * nq, (i + 1) * nq, ctx, 0) for i in range(S)]
+    work, total, chunks, max_chunk = build_dense(prefill, list(range(S)), BS, dev)
+
+    def timed(fn, reps=3):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    dq_ms, at_ms = [], []
+    for st in runner.stores:
+        kv = dequant_dense(st, work, total, table, torch.bfloat16)
+        dq_ms.append(timed(lambda: dequant_dense(st, work, total, table, torch.bfloat16)))
+        at_ms.append(timed(lambda: dense_attention(q, kv[0], kv[1], chunks, max_chunk, out, D ** -0.5)))
+    flops = 4 * HQ * D * S * sum(ctx - nq + i + 1 for i in range(nq))
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    t = float(np.mean(at_ms))
+    return {"workload": f"{S} sequences x {nq}-token chunk over {ctx} stored tokens, layers INT4 / INT8 (configuration 3 shape)",
+            "attention_ms_per_layer": t, "dequant_ms_per_layer": float(np.mean(dq_ms)), "tflops": flops / t / 1e9,
+            "peak_tflops": peak, "frac": flops / t / 1e9 / peak,
+            "peak_source": "measured" if "bf16_tflops" in peaks else "fallback", "bound": "tensor"}
 
 
 def run_reference(a) -> None:
@@ -395,6 +459,9 @@ def run_b200(a) -> None:
             t = float(np.mean(ts))
             tier_stats[f"int{b}"] = {"ms": t, "gbs": nbytes / t / 1e6, "frac": nbytes / t / 1e6 / peak, "bytes": nbytes}
     main = tier_stats.get("int4") or next(iter(tier_stats.values()))
+    prefill = None
+    if rank == 0 and world == 1 and not a.no_prefill:
+        prefill = prefill_probe(dev, peaks, a.seed)
 
     if rank == 0:
         cores = os.cpu_count() or 1
@@ -422,6 +489,7 @@ def run_b200(a) -> None:
             "canary": {"interval": a.canary_interval, "fires": canary["fires"],
                        "last": None if canary["pending"] is None else [round(x, 6) for x in canary["pending"][0].tolist()]},
             "clocks": clocks,
+            "prefill": prefill,
             "write": {"gbs": write_bytes / write_ms / 1e6, "ms_total": write_ms, "what": "bulk quantize-on-write of the context"},
         }))
     if world > 1:
