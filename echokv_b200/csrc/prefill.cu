@@ -17,9 +17,7 @@ using namespace echokv;
 
 namespace {
 
-constexpr int BM = 128;  // rows per CTA
-constexpr int BN = 64;   // keys per tile
-constexpr int NWARP = BM / 16;
+constexpr int NWARP = 8;
 
 struct PrefillArgs {
   const void *q, *k, *v;
@@ -82,38 +80,41 @@ __device__ __forceinline__ uint32_t swz(int r, int c) {
   return (uint32_t)(r * (D * 2) + ((c ^ (r & 7)) << 4));
 }
 
-template <typename T, int D>
-__global__ void __launch_bounds__(NWARP * 32, 2) prefill_dense_kernel(PrefillArgs A) {
-  constexpr int CH = D / 8;         // 16-byte chunks per row
-  constexpr int KS = D / 16;        // k-steps of Q K^T
-  constexpr int TILE_BYTES = BN * D * 2;
+// MT m-tiles of 16 rows per warp (a warp's K / V fragments feed MT x as many MMAs), BNK keys per tile,
+// NST stages of K / V in flight; one CTA-wide barrier per tile.
+template <typename T, int D, int MT, int BNK, int NST>
+__global__ void __launch_bounds__(NWARP * 32, MT == 1 ? 2 : 1) prefill_dense_kernel(PrefillArgs A) {
+  constexpr int BMR = NWARP * 16 * MT;  // rows per CTA
+  constexpr int CH = D / 8;             // 16-byte chunks per row
+  constexpr int KS = D / 16;            // k-steps of Q K^T
+  constexpr int TILE_BYTES = BNK * D * 2;
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* q_s = smem;                           // [BM][D]
-  unsigned char* k_s = smem + BM * D * 2;              // [2][BN][D]
-  unsigned char* v_s = k_s + 2 * TILE_BYTES;           // [2][BN][D]
+  unsigned char* q_s = smem;                           // [BMR][D]
+  unsigned char* k_s = smem + BMR * D * 2;             // [NST][BNK][D]
+  unsigned char* v_s = k_s + NST * TILE_BYTES;         // [NST][BNK][D]
 
   const int4 ck = reinterpret_cast<const int4*>(A.chunks)[blockIdx.z];
   const int q0 = ck.x, nq = ck.y - ck.x, ctx = ck.z;
   const int64_t dense0 = ck.w;
   const int gqa = A.gqa, h = blockIdx.y;
   const int rows = nq * gqa;
-  const int row0 = blockIdx.x * BM;
+  const int row0 = blockIdx.x * BMR;
   if (row0 >= rows) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
 
   // Keys this CTA can see: up to the causal limit of its last row.
-  const int last_tok = min(nq - 1, (row0 + BM - 1) / gqa);
+  const int last_tok = min(nq - 1, (row0 + BMR - 1) / gqa);
   const int n_keys = min(ctx, ctx - nq + last_tok + 1);
-  const int n_tiles = (n_keys + BN - 1) / BN;
+  const int n_tiles = (n_keys + BNK - 1) / BNK;
 
   const T* qp = reinterpret_cast<const T*>(A.q);
   const T* kp = reinterpret_cast<const T*>(A.k) + dense0 * A.kv_s0 + (int64_t)h * A.kv_s1;
   const T* vp = reinterpret_cast<const T*>(A.v) + dense0 * A.kv_s0 + (int64_t)h * A.kv_s1;
 
   auto load_tile = [&](int tile, int stage) {
-    const int key0 = tile * BN;
-    for (int i = tid; i < BN * CH; i += NWARP * 32) {
+    const int key0 = tile * BNK;
+    for (int i = tid; i < BNK * CH; i += NWARP * 32) {
       int r = i / CH, c = i % CH;
       bool on = key0 + r < n_keys;
       int64_t src = (int64_t)(on ? key0 + r : 0) * A.kv_s0 + c * 8;
@@ -123,66 +124,88 @@ __global__ void __launch_bounds__(NWARP * 32, 2) prefill_dense_kernel(PrefillArg
     }
   };
 
-  // Q tile (rows past the end are zero) and the first K/V tile.
-  for (int i = tid; i < BM * CH; i += NWARP * 32) {
+  // Q tile (rows past the end are zero) and the first NST - 1 K/V tiles.
+  for (int i = tid; i < BMR * CH; i += NWARP * 32) {
     int r = i / CH, c = i % CH;
     int row = row0 + r;
     bool on = row < rows;
     int tok = on ? row / gqa : 0, hq = on ? h * gqa + row % gqa : 0;
     cp16(smem_u32(q_s) + swz<D>(r, c), qp + (int64_t)(q0 + tok) * A.q_s0 + (int64_t)hq * A.q_s1 + c * 8, on);
   }
-  load_tile(0, 0);
-  asm volatile("cp.async.commit_group;" ::: "memory");
-
-  float o[D / 8][4];
 #pragma unroll
-  for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-
-  // Causal limits of this thread's two rows (g and g + 8 of the warp's 16).
-  int lim[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    int row = row0 + warp * 16 + g + 8 * i;
-    lim[i] = row < rows ? ctx - nq + row / gqa : -1;  // last visible key
+  for (int st = 0; st < NST - 1; ++st) {
+    if (st < n_tiles) load_tile(st, st);
+    asm volatile("cp.async.commit_group;" ::: "memory");
   }
-  const int warp_lim = ctx - nq + min(nq - 1, (row0 + warp * 16 + 15) / gqa);
+
+  float o[MT][D / 8][4];
+#pragma unroll
+  for (int mi = 0; mi < MT; ++mi)
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) o[mi][j][0] = o[mi][j][1] = o[mi][j][2] = o[mi][j][3] = 0.f;
+  float m_run[MT][2], l_run[MT][2];
+  int lim[MT][2];  // causal limits of this thread's rows (g and g + 8 of each m-tile): last visible key
+  const int wrow0 = row0 + warp * 16 * MT;
+#pragma unroll
+  for (int mi = 0; mi < MT; ++mi)
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      m_run[mi][i] = -INFINITY; l_run[mi][i] = 0.f;
+      int row = wrow0 + 16 * mi + g + 8 * i;
+      lim[mi][i] = row < rows ? ctx - nq + row / gqa : -1;
+    }
+  const int warp_lim = ctx - nq + min(nq - 1, (wrow0 + 16 * MT - 1) / gqa);
+  int min_lim = lim[0][0];
+#pragma unroll
+  for (int mi = 0; mi < MT; ++mi) min_lim = min(min_lim, min(lim[mi][0], lim[mi][1]));
 
   for (int tile = 0; tile < n_tiles; ++tile) {
-    const int stage = tile & 1;
-    if (tile + 1 < n_tiles) load_tile(tile + 1, stage ^ 1);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    const int stage = tile % NST;
+    // this thread's copies of the tile have landed; after the barrier everyone's have, and everyone is
+    // done with the previous tile, whose stage the next load overwrites
+    asm volatile("cp.async.wait_group %0;" ::"n"(NST - 2) : "memory");
     __syncthreads();
+    if (tile + NST - 1 < n_tiles) load_tile(tile + NST - 1, (tile + NST - 1) % NST);
+    asm volatile("cp.async.commit_group;" ::: "memory");
 
-    const int key0 = tile * BN;
-    if (key0 <= warp_lim) {
-      const uint32_t kb = smem_u32(k_s) + stage * TILE_BYTES, vb = smem_u32(v_s) + stage * TILE_BYTES;
-      float s[BN / 8][4];
+    const int key0 = tile * BNK;
+    if (key0 > warp_lim) continue;
+    const uint32_t kb = smem_u32(k_s) + stage * TILE_BYTES, vb = smem_u32(v_s) + stage * TILE_BYTES;
+    float s[MT][BNK / 8][4];
 #pragma unroll
-      for (int j = 0; j < BN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
-      for (int ks = 0; ks < KS; ++ks) {
-        uint32_t a[4];
-        ldsm4(smem_u32(q_s) + swz<D>(warp * 16 + (lane & 15), 2 * ks + (lane >> 4)), a);
+      for (int j = 0; j < BNK / 8; ++j) s[mi][j][0] = s[mi][j][1] = s[mi][j][2] = s[mi][j][3] = 0.f;
 #pragma unroll
-        for (int jp = 0; jp < BN / 16; ++jp) {
-          uint32_t b[4];
-          ldsm4(kb + swz<D>(jp * 16 + (lane & 7) + 8 * (lane >> 4), 2 * ks + ((lane >> 3) & 1)), b);
-          Mma<T>::run(s[2 * jp], a, b[0], b[1]);
-          Mma<T>::run(s[2 * jp + 1], a, b[2], b[3]);
+    for (int ks = 0; ks < KS; ++ks) {
+      uint32_t a[MT][4];
+#pragma unroll
+      for (int mi = 0; mi < MT; ++mi)
+        ldsm4(smem_u32(q_s) + swz<D>(warp * 16 * MT + 16 * mi + (lane & 15), 2 * ks + (lane >> 4)), a[mi]);
+#pragma unroll
+      for (int jp = 0; jp < BNK / 16; ++jp) {
+        uint32_t b[4];
+        ldsm4(kb + swz<D>(jp * 16 + (lane & 7) + 8 * (lane >> 4), 2 * ks + ((lane >> 3) & 1)), b);
+#pragma unroll
+        for (int mi = 0; mi < MT; ++mi) {
+          Mma<T>::run(s[mi][2 * jp], a[mi], b[0], b[1]);
+          Mma<T>::run(s[mi][2 * jp + 1], a[mi], b[2], b[3]);
         }
       }
-      // scale, mask, running max
-      const bool edge = key0 + BN - 1 > min(lim[0], lim[1]) || key0 + BN > n_keys;
-      float mx[2] = {m_run[0], m_run[1]};
+    }
+    // scale, mask, running max / sum per m-tile
+    const bool edge = key0 + BNK - 1 > min_lim || key0 + BNK > n_keys;
+    uint32_t p[MT][BNK / 16][4];
 #pragma unroll
-      for (int j = 0; j < BN / 8; ++j) {
+    for (int mi = 0; mi < MT; ++mi) {
+      float mx[2] = {m_run[mi][0], m_run[mi][1]};
+#pragma unroll
+      for (int j = 0; j < BNK / 8; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          float x = s[j][e] * A.scale_log2;
-          if (edge && key0 + 8 * j + 2 * t + (e & 1) > lim[e >> 1]) x = -INFINITY;
-          s[j][e] = x;
+          float x = s[mi][j][e] * A.scale_log2;
+          if (edge && key0 + 8 * j + 2 * t + (e & 1) > lim[mi][e >> 1]) x = -INFINITY;
+          s[mi][j][e] = x;
           mx[e >> 1] = fmaxf(mx[e >> 1], x);
         }
       }
@@ -192,80 +215,92 @@ __global__ void __launch_bounds__(NWARP * 32, 2) prefill_dense_kernel(PrefillArg
         mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
         mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
         base[i] = mx[i] == -INFINITY ? 0.f : mx[i];  // a row with nothing visible yet
-        corr[i] = ex2(m_run[i] - base[i]);
-        m_run[i] = mx[i];
+        corr[i] = ex2(m_run[mi][i] - base[i]);
+        m_run[mi][i] = mx[i];
       }
-      uint32_t p[BN / 16][4];
 #pragma unroll
-      for (int j = 0; j < BN / 8; ++j) {
-        float e0 = ex2(s[j][0] - base[0]), e1 = ex2(s[j][1] - base[0]);
-        float e2 = ex2(s[j][2] - base[1]), e3 = ex2(s[j][3] - base[1]);
+      for (int j = 0; j < BNK / 8; ++j) {
+        float e0 = ex2(s[mi][j][0] - base[0]), e1 = ex2(s[mi][j][1] - base[0]);
+        float e2 = ex2(s[mi][j][2] - base[1]), e3 = ex2(s[mi][j][3] - base[1]);
         sum[0] += e0 + e1;
         sum[1] += e2 + e3;
-        p[j >> 1][(j & 1) * 2] = Mma<T>::pack(e0, e1);
-        p[j >> 1][(j & 1) * 2 + 1] = Mma<T>::pack(e2, e3);
+        p[mi][j >> 1][(j & 1) * 2] = Mma<T>::pack(e0, e1);
+        p[mi][j >> 1][(j & 1) * 2 + 1] = Mma<T>::pack(e2, e3);
       }
 #pragma unroll
-      for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * corr[i] + sum[i];
+      for (int i = 0; i < 2; ++i) l_run[mi][i] = l_run[mi][i] * corr[i] + sum[i];
 #pragma unroll
       for (int j = 0; j < D / 8; ++j) {
-        o[j][0] *= corr[0]; o[j][1] *= corr[0];
-        o[j][2] *= corr[1]; o[j][3] *= corr[1];
+        o[mi][j][0] *= corr[0]; o[mi][j][1] *= corr[0];
+        o[mi][j][2] *= corr[1]; o[mi][j][3] *= corr[1];
       }
+    }
 #pragma unroll
-      for (int kk = 0; kk < BN / 16; ++kk) {
+    for (int kk = 0; kk < BNK / 16; ++kk) {
 #pragma unroll
-        for (int jp = 0; jp < D / 16; ++jp) {
-          uint32_t b[4];
-          ldsm4t(vb + swz<D>(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * jp + (lane >> 4)), b);
-          Mma<T>::run(o[2 * jp], p[kk], b[0], b[1]);
-          Mma<T>::run(o[2 * jp + 1], p[kk], b[2], b[3]);
+      for (int jp = 0; jp < D / 16; ++jp) {
+        uint32_t b[4];
+        ldsm4t(vb + swz<D>(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * jp + (lane >> 4)), b);
+#pragma unroll
+        for (int mi = 0; mi < MT; ++mi) {
+          Mma<T>::run(o[mi][2 * jp], p[mi][kk], b[0], b[1]);
+          Mma<T>::run(o[mi][2 * jp + 1], p[mi][kk], b[2], b[3]);
         }
       }
     }
-    __syncthreads();  // everyone is done with this stage before the next load overwrites it
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 
   // normalise and store
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    float l = l_run[i];
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    int row = row0 + warp * 16 + g + 8 * i;
-    if (row >= rows) continue;
-    float inv = l > 0.f ? 1.f / l : 0.f;
-    int tok = row / gqa, hq = h * gqa + row % gqa;
-    int64_t base_o = (int64_t)(q0 + tok) * A.o_s0 + (int64_t)hq * A.o_s1;
+  for (int mi = 0; mi < MT; ++mi)
 #pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
-      float x0 = o[j][2 * i] * inv, x1 = o[j][2 * i + 1] * inv;
-      int d = 8 * j + 2 * t;
-      if (A.out_dtype == ECHOKV_DT_F32) {
-        *reinterpret_cast<float2*>(reinterpret_cast<float*>(A.out) + base_o + d) = make_float2(x0, x1);
-      } else if (A.out_dtype == ECHOKV_DT_F16) {
-        *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(A.out) + base_o + d) = __floats2half2_rn(x0, x1);
-      } else {
-        *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(A.out) + base_o + d) =
-            __floats2bfloat162_rn(x0, x1);
+    for (int i = 0; i < 2; ++i) {
+      float l = l_run[mi][i];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      int row = wrow0 + 16 * mi + g + 8 * i;
+      if (row >= rows) continue;
+      float inv = l > 0.f ? 1.f / l : 0.f;
+      int tok = row / gqa, hq = h * gqa + row % gqa;
+      int64_t base_o = (int64_t)(q0 + tok) * A.o_s0 + (int64_t)hq * A.o_s1;
+#pragma unroll
+      for (int j = 0; j < D / 8; ++j) {
+        float x0 = o[mi][j][2 * i] * inv, x1 = o[mi][j][2 * i + 1] * inv;
+        int d = 8 * j + 2 * t;
+        if (A.out_dtype == ECHOKV_DT_F32) {
+          *reinterpret_cast<float2*>(reinterpret_cast<float*>(A.out) + base_o + d) = make_float2(x0, x1);
+        } else if (A.out_dtype == ECHOKV_DT_F16) {
+          *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(A.out) + base_o + d) = __floats2half2_rn(x0, x1);
+        } else {
+          *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(A.out) + base_o + d) =
+              __floats2bfloat162_rn(x0, x1);
+        }
       }
     }
-  }
 }
 
-template <typename T, int D>
-int launch(const PrefillArgs& A, int64_t n_chunks, int max_rows, int H, cudaStream_t st) {
-  constexpr int SMEM = BM * D * 2 + 4 * BN * D * 2;
+template <typename T, int D, int MT, int BNK, int NST>
+int launch_cfg(const PrefillArgs& A, int64_t n_chunks, int max_rows, int H, cudaStream_t st) {
+  constexpr int BMR = NWARP * 16 * MT;
+  constexpr int SMEM = BMR * D * 2 + 2 * NST * BNK * D * 2;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
-    cudaFuncSetAttribute(prefill_dense_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaFuncSetAttribute(prefill_dense_kernel<T, D, MT, BNK, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     configured[dev] = true;
   }
-  dim3 grid((max_rows + BM - 1) / BM, H, (unsigned)n_chunks);
-  prefill_dense_kernel<T, D><<<grid, NWARP * 32, SMEM, st>>>(A);
+  dim3 grid((max_rows + BMR - 1) / BMR, H, (unsigned)n_chunks);
+  prefill_dense_kernel<T, D, MT, BNK, NST><<<grid, NWARP * 32, SMEM, st>>>(A);
   return check_launch("prefill");
+}
+
+// Long chunks: 32 rows per warp (256 per CTA), 32-key tiles, three stages; short ones: 16 rows per warp.
+template <typename T, int D>
+int launch(const PrefillArgs& A, int64_t n_chunks, int max_rows, int H, cudaStream_t st) {
+  if (max_rows > 128) return launch_cfg<T, D, 2, 32, 3>(A, n_chunks, max_rows, H, st);
+  return launch_cfg<T, D, 1, 64, 2>(A, n_chunks, max_rows, H, st);
 }
 
 }  // namespace
