@@ -3,7 +3,7 @@
 Run in a container that has the reference checkout (it is imported unchanged,
 CPU torch path, Triton disabled) -- not needed at test time:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 For every scenario in ``scenarios.py`` the reference's TieredKVCache /
 decode_attention_torch / prefill_attention_torch / canary_kl / LayerController
@@ -26,7 +26,9 @@ HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ECHOKV_REFERENCE", "")
+if not REF:
+    sys.exit("usage: make_golden.py <path of a checkout of the reference> (or set ECHOKV_REFERENCE)")
 os.environ["ECHOKV_DISABLE_TRITON"] = "1"
 sys.path.insert(0, REF)
 
