@@ -54,6 +54,8 @@ def parse():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a CUDA graph")
     ap.add_argument("--cpu-seqs", type=int, default=4, help="sequences in the CPU-baseline sample")
     ap.add_argument("--canary-interval", type=int, default=8, help="measure the canary KL every N steps (0 = never)")
+    ap.add_argument("--stock", action="store_true", help="also time the image's flash-attention library over a bf16 KV cache "
+                                                         "of the same shape (off by default: third-party kernels)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill probe (configuration 3 shape)")
     ap.add_argument("--tiers", default="", help="comma list of tiers cycled over the layers instead of the seeded draw "
                                                 "(small profiling cases, e.g. --layers 2 --tiers 4)")
@@ -235,6 +237,44 @@ def prefill_probe(dev, peaks: dict, seed: int) -> dict:
             "attention_ms_per_layer": t, "dequant_ms_per_layer": float(np.mean(dq_ms)), "tflops": flops / t / 1e9,
             "peak_tflops": peak, "frac": flops / t / 1e9 / peak,
             "peak_source": "measured" if "bf16_tflops" in peaks else "fallback", "bound": "tensor"}
+
+
+def stock_bf16_probe(dev, S: int, ctx: int, seed: int):
+    """The "stock" bar: the same decode step's attention over an uncompressed bf16 KV cache with the
+    flash-attention library that ships with the image (a library call, not part of this package).  Returns
+    None when the library is missing or has no kernel for this GPU."""
+    import torch
+
+    try:
+        from flash_attn import flash_attn_with_kvcache
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"flash_attn import failed: {type(e).__name__}"}
+    try:
+        gen = torch.Generator(device=dev).manual_seed(seed + 500)
+        layers = 2  # alternate so that nothing is served from L2 (1.08 GB of K+V per layer)
+        kc = [torch.randn(S, ctx + 16, H, D, device=dev, generator=gen).bfloat16() for _ in range(layers)]
+        vc = [torch.randn(S, ctx + 16, H, D, device=dev, generator=gen).bfloat16() for _ in range(layers)]
+        q = torch.randn(S, 1, HQ, D, device=dev, generator=gen).bfloat16()
+        lens = torch.full((S,), ctx + 1, dtype=torch.int32, device=dev)
+
+        def run():
+            for l in range(layers):
+                flash_attn_with_kvcache(q, kc[l], vc[l], cache_seqlens=lens, softmax_scale=D ** -0.5, causal=True)
+
+        run()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (3 * layers)
+        nbytes = S * (ctx + 1) * H * D * 2 * 2
+        return {"what": "flash_attn_with_kvcache over a contiguous bf16 KV cache, same batch / context / heads",
+                "ms_per_layer": ms, "gbs": nbytes / ms / 1e6, "bytes_per_layer": nbytes}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:120]}"}
 
 
 def run_reference(a) -> None:
@@ -462,6 +502,7 @@ def run_b200(a) -> None:
     prefill = None
     if rank == 0 and world == 1 and not a.no_prefill:
         prefill = prefill_probe(dev, peaks, a.seed)
+    stock = stock_bf16_probe(dev, S, ctx, a.seed) if (rank == 0 and world == 1 and a.stock) else None
 
     if rank == 0:
         cores = os.cpu_count() or 1
@@ -490,6 +531,7 @@ def run_b200(a) -> None:
                        "last": None if canary["pending"] is None else [round(x, 6) for x in canary["pending"][0].tolist()]},
             "clocks": clocks,
             "prefill": prefill,
+            "stock_bf16_decode": stock,
             "write": {"gbs": write_bytes / write_ms / 1e6, "ms_total": write_ms, "what": "bulk quantize-on-write of the context"},
         }))
     if world > 1:
