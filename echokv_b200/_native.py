@@ -81,6 +81,7 @@ _SIGS = {
     "echokv_dequant_dense": [_LP, _PP, _RP, _P, _I64, _P, _I64, _P, _P, _I64, _I64, _I32, _P],
     "echokv_prefill": [_P, _I64, _I64, _P, _P, _I64, _I64, _I32, _P, _I64, _I32, _P, _I64, _I64, _I32, _F, _I32, _I32,
                        _I32, _P],
+    "echokv_set_decode_events": [_P, _P],
     "echokv_gather_rows": [_P, _I64, _P, _I64, _P, _I64, _P],
     "echokv_canary_kl": [_P, _I32, _I64, _I64, _I64, _P, _I64, _I64, _I64, _I32, _I32, _I32, _I32, _I32, _I32, _I32,
                          _I32, _I32, _F, _P, _P],

@@ -1115,6 +1115,7 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
 }  // namespace mma
 
 static int g_decode_path = 0;  // 0: pick by shape, 1: always the generic kernel
+static cudaEvent_t g_ev_before = nullptr, g_ev_after = nullptr;  // optional timing hook around the split kernel
 
 // Chooses the tensor-core kernel when the shape fits; otherwise leaves `handled` false.
 int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
@@ -1181,12 +1182,14 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   const int64_t n_items = num_seqs * (int64_t)A.num_splits;
   if (grid > n_items) grid = n_items;
   if (cudaMemsetAsync(counter, 0, sizeof(int), st) != cudaSuccess) return check_launch("decode (work counter)");
+  if (g_ev_before) cudaEventRecord(g_ev_before, st);
   switch (H) {
     case 1: decode_mma_kernel<1><<<(unsigned)grid, 2 * 32, smem_bytes, st>>>(P); break;
     case 2: decode_mma_kernel<2><<<(unsigned)grid, 3 * 32, smem_bytes, st>>>(P); break;
     case 4: decode_mma_kernel<4><<<(unsigned)grid, 5 * 32, smem_bytes, st>>>(P); break;
     default: decode_mma_kernel<8><<<(unsigned)grid, 9 * 32, smem_bytes, st>>>(P); break;
   }
+  if (g_ev_after) cudaEventRecord(g_ev_after, st);
   int rc = check_launch("decode (tensor-core kernel)");
   if (rc) return rc;
   *handled = true;
@@ -1205,6 +1208,12 @@ extern "C" int echokv_debug_phase(unsigned long long* dst, int reset) {
   return rc;
 }
 #endif
+
+extern "C" int echokv_set_decode_events(void* before, void* after) {
+  echokv::g_ev_before = reinterpret_cast<cudaEvent_t>(before);
+  echokv::g_ev_after = reinterpret_cast<cudaEvent_t>(after);
+  return ECHOKV_OK;
+}
 
 extern "C" int echokv_set_decode_path(int path) {
   const int old = echokv::g_decode_path;

@@ -187,6 +187,13 @@ int echokv_decode_static(const echokv_layout* layout, const echokv_pages* pages,
  * No counterpart in the reference (its Triton autotuner plays this role, kernels/decode.py:265-280). */
 int echokv_set_decode_path(int path);
 
+/* Timing hook: while set, every echokv_decode call that takes the tensor-core kernel records the CUDA
+ * events `before` / `after` (cudaEvent_t) on its stream right around the split kernel (after the counter
+ * memset, before the merge), so a benchmark can time that kernel alone with events on the launching
+ * stream.  Pass two null pointers to clear.  Process-wide, not thread-safe, not for use during stream
+ * capture.  No counterpart in the reference. */
+int echokv_set_decode_events(void* before, void* after);
+
 /* Dequantize whole contexts into dense [total_ctx, H, D] K and V of `out_dtype`
  * -- dequant_dense / _dequant_kernel (kernels/prefill.py:90-115, :329-369).
  * `work` int32 [n_work, 4]: request (block-table row), block index, dense row of the
