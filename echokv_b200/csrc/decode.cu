@@ -13,7 +13,7 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
 // flight together.
 constexpr int MERGE_MAX_SPLITS = 64;
 __global__ void decode_merge_kernel(DecodeArgs A, int BS, int D) {
-  __shared__ float wgt[MERGE_MAX_SPLITS];
+  __shared__ float wgt[MERGE_MAX_SPLITS], den[MERGE_MAX_SPLITS];
   __shared__ float red[2];
   const int seq = blockIdx.x, head = blockIdx.y;
   const int64_t seq_len = A.lens[seq];
@@ -25,33 +25,45 @@ __global__ void decode_merge_kernel(DecodeArgs A, int BS, int D) {
   const int64_t o_row = A.q_rows ? A.q_rows[seq] : seq;
   if (used <= MERGE_MAX_SPLITS) {
     if (threadIdx.x < 32) {  // warp 0: maximum, weights and the denominator (summed in split order)
+      float2 ml[MERGE_MAX_SPLITS / 32];
       float m = -INFINITY;
-      for (int s = threadIdx.x; s < used; s += 32) m = fmaxf(m, A.ml[(base + s) * 2]);
+#pragma unroll
+      for (int k = 0; k < MERGE_MAX_SPLITS / 32; ++k) {
+        const int s = threadIdx.x + 32 * k;
+        ml[k] = s < used ? *reinterpret_cast<const float2*>(A.ml + (base + s) * 2) : make_float2(-INFINITY, 0.f);
+        m = fmaxf(m, ml[k].x);
+      }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-      for (int s = threadIdx.x; s < used; s += 32) wgt[s] = exp2f(A.ml[(base + s) * 2] - m);
+#pragma unroll
+      for (int k = 0; k < MERGE_MAX_SPLITS / 32; ++k) {
+        const int s = threadIdx.x + 32 * k;
+        if (s < used) {
+          const float w = exp2f(ml[k].x - m);
+          wgt[s] = w;
+          den[s] = ml[k].y * w;
+        }
+      }
       __syncwarp();
       if (threadIdx.x == 0) {
         float lt = 0.f;
-        for (int s = 0; s < used; ++s) lt += A.ml[(base + s) * 2 + 1] * wgt[s];
+        for (int s = 0; s < used; ++s) lt += den[s];
         red[0] = lt;
       }
     }
-    __syncthreads();
-    const float lt = red[0];
+    // every thread has the loads of its channel in flight while warp 0 works out the weights
+    constexpr int BATCH = 32;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
       const float* src = A.acc + base * D + d;
+      float x[BATCH];
+#pragma unroll
+      for (int k = 0; k < BATCH; ++k) x[k] = k < used ? src[(int64_t)k * D] : 0.f;
+      __syncthreads();  // weights and denominator are ready (uniform: every thread of the CTA has a channel when D >= blockDim)
       float a = 0.f;
-      int s = 0;
-      for (; s + 8 <= used; s += 8) {
-        float x[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) x[k] = src[(int64_t)(s + k) * D];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) a += x[k] * wgt[s + k];
-      }
-      for (; s < used; ++s) a += src[(int64_t)s * D] * wgt[s];
-      st_dt(A.out, A.out_dt, o_row * A.o_s0 + (int64_t)head * A.o_s1 + d, a / lt);
+      for (int k = 0; k < BATCH; ++k) a += k < used ? x[k] * wgt[k] : 0.f;
+      for (int s = BATCH; s < used; ++s) a += src[(int64_t)s * D] * wgt[s];
+      st_dt(A.out, A.out_dt, o_row * A.o_s0 + (int64_t)head * A.o_s1 + d, a / red[0]);
     }
     return;
   }

@@ -83,9 +83,10 @@ write_tokens_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restric
         reinterpret_cast<__half*>(page + L.o_vs)[e] = s16;
         reinterpret_cast<__half*>(page + L.o_vm)[e] = m16;
       }
+      const float rsc = __frcp_rn(sc);
       uint32_t q[8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) q[k] = quant_code(x[k], m, sc, levels);
+      for (int k = 0; k < 8; ++k) q[k] = quant_code_r(x[k], m, sc, rsc, levels);
       store_packed8(pages + rowoff + side_bytes + h * head_bytes + (d0 * bits) / 8, pack8(q, bits), bits);
     }
   } else {
@@ -107,11 +108,12 @@ write_tokens_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restric
       reinterpret_cast<__half*>(page + L.o_vs)[e] = s16;
       reinterpret_cast<__half*>(page + L.o_vm)[e] = m16;
       uint8_t* dst = pages + rowoff + side_bytes + h * head_bytes + (g * L.VG * bits) / 8;
+      const float rsc = __frcp_rn(sc);
       for (int c = 0; c < L.VG; c += 8) {
         ld8<T>(value, src + c, vec_in, x);
         uint32_t q[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) q[k] = quant_code(x[k], m, sc, levels);
+        for (int k = 0; k < 8; ++k) q[k] = quant_code_r(x[k], m, sc, rsc, levels);
         store_packed8(dst + (c * bits) / 8, pack8(q, bits), bits);
       }
     }
@@ -196,11 +198,12 @@ finalize_k_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restrict_
       for (int k = 0; k < 8; ++k) { mn[k] = fminf(mn[k], x[k]); mx[k] = fmaxf(mx[k], x[k]); }
     }
     __align__(16) __half s16[8], m16[8];
-    float sc[8], m[8];
+    float sc[8], m[8], rsc[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       group_stats(mn[k], mx[k], levels, s16[k], m16[k]);
       sc[k] = __half2float(s16[k]); m[k] = __half2float(m16[k]);
+      rsc[k] = __frcp_rn(sc[k]);
     }
     const int64_t e = ((int64_t)grp * L.H + h) * L.D + d0;
     *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(page + L.o_ks) + e) = *reinterpret_cast<uint4*>(s16);
@@ -209,7 +212,7 @@ finalize_k_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restrict_
       load(p);
       uint32_t q[8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) q[k] = quant_code(x[k], m[k], sc[k], levels);
+      for (int k = 0; k < 8; ++k) q[k] = quant_code_r(x[k], m[k], sc[k], rsc[k], levels);
       const int64_t ro = row_offset(pages, L, blk, grp * L.KG + p, bits);
       store_packed8(pages + ro + h * head_bytes + (d0 * bits) / 8, pack8(q, bits), bits);
     }

@@ -89,3 +89,24 @@ def test_layout_known_offsets():
     for bad in (dict(block_size=8, mem_bits=4), dict(block_size=32, mem_bits=5), dict(block_size=48, mem_bits=4)):
         with pytest.raises(ValueError):
             O.Layout(2, 64, k_group=32, **bad)
+
+
+def test_reciprocal_quantizer_rule_equals_division():
+    """The write kernels quantize with d * (1 / scale) and fall back to the exact division when the
+    product lies within 2^-12 of a half-integer (csrc/common.cuh, quant_code_r).  In float32 arithmetic
+    that rule must give the code of the reference's divide-then-round (quant.py:39-45) for every input,
+    also for quotients crowded around the rounding ties."""
+    rng = np.random.default_rng(0)
+    n = 1_000_000
+    for levels in (3.0, 15.0, 255.0):
+        s = (np.float32(2.0) ** rng.uniform(-14, 4, n).astype(np.float32) * rng.uniform(1, 2, n).astype(np.float32))
+        s = np.maximum(s, np.float32(6.103515625e-05)).astype(np.float16).astype(np.float32)
+        k = rng.integers(0, int(levels) + 1, n).astype(np.float32)
+        off = np.where(rng.random(n) < 0.5, np.float32(0.5) + rng.uniform(-3e-4, 3e-4, n).astype(np.float32),
+                       rng.uniform(-0.2, 1.2, n).astype(np.float32))
+        d = ((k + off) * s).astype(np.float32)
+        fast = (d * (np.float32(1) / s).astype(np.float32)).astype(np.float32)
+        exact = (d / s).astype(np.float32)
+        tie = (np.abs(fast - np.floor(fast) - np.float32(0.5)) < np.float32(2.0 ** -12)) | ~(np.abs(fast) < 512)
+        got = np.clip(np.rint(np.where(tie, exact, fast)), 0, levels)
+        assert np.array_equal(got, np.clip(np.rint(exact), 0, levels))
