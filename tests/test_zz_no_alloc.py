@@ -72,31 +72,3 @@ def test_static_scratch_decode_refuses_oversized_requests():
     lens = torch.zeros(s, dtype=torch.long, device="cuda")
     rc = _call(True, store, q, table, lens, 1.0, 32, 1, out)
     assert rc == -2 and b"built-in scratch" in N.lib.echokv_last_error()
-
-
-def test_decode_events_hook_times_the_split_kernel():
-    """echokv_set_decode_events: two caller-provided CUDA events are recorded around the split kernel."""
-    import torch
-    import scenarios as S
-    from cuda_runner import run_cuda
-    from echokv_b200 import _native as N
-    from echokv_b200.kernels.decode import decode_attention
-
-    sc = next(s for s in S.decode_scenarios() if s.name == "decode_bs16_bf16")
-    res = run_cuda(sc)
-    store = res["_store"]
-    q = torch.from_numpy(sc.query).to("cuda", dtype=torch.bfloat16)
-    table = torch.from_numpy(sc.block_table).cuda()
-    lens = torch.tensor(sc.seq_lens, device="cuda")
-    want = decode_attention(store, q, table, lens, sc.scale)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(); e1.record()
-    torch.cuda.synchronize()
-    N.lib.echokv_set_decode_events(e0.cuda_event, e1.cuda_event)
-    try:
-        got = decode_attention(store, q, table, lens, sc.scale)
-        torch.cuda.synchronize()
-        assert 0.0 < e0.elapsed_time(e1) < 50.0
-    finally:
-        N.lib.echokv_set_decode_events(None, None)
-    assert torch.equal(got, want)
