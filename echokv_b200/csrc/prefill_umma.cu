@@ -1,0 +1,342 @@
+// Chunked-prefill attention over dense contexts on the 5th-generation tensor cores (tcgen05 + TMEM),
+// head size 128.  Same contract as prefill_dense_kernel in prefill.cu: queries of a chunk attend to the
+// request's whole context, bottom-right causal.
+//
+// One CTA = one (chunk, KV head, 128 rows); a row is a (query token, query head of the group) pair and
+// owns one TMEM lane, and thread r of the CTA's 128 owns row r.  Per 64-key tile:
+//   S  = Q K^T   one thread issues 8 tcgen05.mma (M 128, N 64, K 16 each): Q [128 x 128] and the K tile
+//                [64 x 128] sit in shared memory as 128-byte-swizzled K-major panels of 64 channels;
+//                the fp32 result lands in 64 TMEM columns;
+//   softmax      thread r reads its row of S with tcgen05.ld, masks, exponentiates against a running
+//                reference (moved only when a row outgrows it by more than 2^8, then the row of O in TMEM
+//                is rescaled with tcgen05.ld / tcgen05.st) and writes P as a 16-bit K-major panel;
+//   O += P V     4 tcgen05.mma (M 128, N 128, K 16): the V tile is used as it lies in memory
+//                ([key][channel], an MN-major B operand), O accumulates in 128 TMEM columns.
+// K / V tiles are double-buffered with cp.async; completion of the MMAs comes back through
+// tcgen05.commit on an mbarrier.  Every wait is bounded; a wait that gives up ends the CTA's work, frees
+// its TMEM and raises the status word.
+#include "common.cuh"
+
+using namespace echokv;
+
+namespace echokv {
+namespace umma {
+
+constexpr int UM = 128;  // rows per CTA = TMEM lanes
+constexpr int UN = 64;   // keys per tile
+constexpr int UD = 128;  // head size
+constexpr int TMEM_COLS = 256;  // S: columns [0, 64), O: columns [64, 192)
+constexpr int O_COL = 64;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr float REF_SLACK = 8.f;  // log2 units a row may exceed the softmax reference before it moves
+
+constexpr int Q_BYTES = UM * UD * 2;        // two panels of 128 rows x 128 bytes
+constexpr int KV_BYTES = UN * UD * 2;       // two panels of 64 rows x 128 bytes
+constexpr int P_BYTES = UM * UN * 2;        // one panel of 128 rows x 128 bytes
+constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024;  // K, V double-buffered; slack for 1024-byte alignment
+
+struct Args {
+  const void *q, *k, *v;
+  void* out;
+  const int32_t* chunks;  // [n, 4]: q_start, q_end, ctx, dense_start
+  int64_t q_s0, q_s1, kv_s0, kv_s1, o_s0, o_s1;
+  int gqa, out_dtype, is_bf16;
+  float scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// byte offset of 16-byte chunk c (0..7) of row r inside a 128-byte-swizzled panel (rows of 128 bytes)
+__device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+
+__device__ __forceinline__ void cp16(uint32_t dst, const void* src, bool on) {
+  const int n = on ? 16 : 0;  // zero-fill
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle: start address, leading / stride byte offsets (>> 4).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(lbo >> 4) << 16;
+  d |= (uint64_t)(sbo >> 4) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t a = smem_u32(bar);
+  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(a), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                 "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+                 "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+                 "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+                 "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+                 "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+                 "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+                 "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+                 "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+                 "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+                 "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+               : "memory");
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, bool bf16) {
+  uint32_t d;
+  if (bf16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
+__global__ void __launch_bounds__(UM, 2) prefill_umma_kernel(Args A) {
+  extern __shared__ unsigned char dyn[];
+  __shared__ __align__(8) uint64_t bar_s, bar_o;
+  __shared__ uint32_t tmem_slot;
+  const uint32_t base = (smem_u32(dyn) + 1023u) & ~1023u;  // swizzled panels want 1024-byte alignment
+  const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + 2 * KV_BYTES, p_s = v_s + 2 * KV_BYTES;
+
+  const int4 ck = reinterpret_cast<const int4*>(A.chunks)[blockIdx.z];
+  const int q0 = ck.x, nq = ck.y - ck.x, ctx = ck.z;
+  const int64_t dense0 = ck.w;
+  const int gqa = A.gqa, h = blockIdx.y;
+  const int rows = nq * gqa;
+  const int row0 = blockIdx.x * UM;
+  if (row0 >= rows) return;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const bool bf16 = A.is_bf16 != 0;
+
+  // this thread's row
+  const int row = row0 + tid;
+  const bool live = row < rows;
+  const int tok = live ? row / gqa : 0, hq = live ? h * gqa + row % gqa : 0;
+  const int lim = live ? ctx - nq + tok : -1;  // last visible key
+  // keys this CTA can see: up to the causal limit of its last row
+  const int last_tok = min(nq - 1, (row0 + UM - 1) / gqa);
+  const int n_keys = min(ctx, ctx - nq + last_tok + 1);
+  const int n_tiles = (n_keys + UN - 1) / UN;
+
+  const uint16_t* qp = reinterpret_cast<const uint16_t*>(A.q) + (int64_t)(q0 + tok) * A.q_s0 + (int64_t)hq * A.q_s1;
+  const uint16_t* kp = reinterpret_cast<const uint16_t*>(A.k) + dense0 * A.kv_s0 + (int64_t)h * A.kv_s1;
+  const uint16_t* vp = reinterpret_cast<const uint16_t*>(A.v) + dense0 * A.kv_s0 + (int64_t)h * A.kv_s1;
+
+  auto load_tile = [&](int tile, int stage) {
+    const int key0 = tile * UN;
+#pragma unroll
+    for (int j = 0; j < (UN * 16) / UM; ++j) {
+      const int idx = tid + UM * j, key = idx >> 4, c = idx & 15;
+      const bool on = key0 + key < n_keys;
+      const int64_t src = (int64_t)(on ? key0 + key : 0) * A.kv_s0 + c * 8;
+      const uint32_t off = stage * KV_BYTES + (c >> 3) * (UN * 128) + swz(key, c & 7);
+      cp16(k_s + off, kp + src, on);
+      cp16(v_s + off, vp + src, on);
+    }
+  };
+
+  // Q (this thread's row, zero past the end) and the first K / V tile
+#pragma unroll
+  for (int c = 0; c < 16; ++c) cp16(q_s + (c >> 3) * (UM * 128) + swz(tid, c & 7), qp + c * 8, live);
+  load_tile(0, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_s)));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_o)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;");
+  const uint32_t tmem = tmem_slot;
+  const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's quarter of the lanes
+
+  // instruction descriptors (kind::f16): fp32 accumulator, 16-bit A / B, N, M; the P.V one takes B MN-major
+  const uint32_t fmt = bf16 ? 1u : 0u;
+  const uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(UN >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
+  const uint32_t idesc_pv = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(UD >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
+
+  float m_ref = -INFINITY, l_run = 0.f;
+  bool ok = true;
+  for (int tile = 0; tile < n_tiles && ok; ++tile) {
+    const int stage = tile & 1;
+    if (tile + 1 < n_tiles) load_tile(tile + 1, stage ^ 1);  // its buffer was released by the wait on bar_o below
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor-core reads
+    __syncthreads();
+
+    if (tid == 0) {  // S = Q K^T
+      asm volatile("tcgen05.fence::after_thread_sync;");
+#pragma unroll
+      for (int k = 0; k < UD / 16; ++k) {
+        const uint64_t a = make_desc(q_s + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
+        const uint64_t b = make_desc(k_s + stage * KV_BYTES + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
+        mma_f16(tmem, a, b, idesc_qk, k > 0);
+      }
+      mma_commit(&bar_s);
+    }
+    if (!bar_wait(&bar_s, tile & 1)) { ok = false; }
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    asm volatile("tcgen05.fence::after_thread_sync;");
+
+    // this row's scores
+    float s[UN];
+    tmem_ld32(t_row, *reinterpret_cast<float(*)[32]>(&s[0]));
+    tmem_ld32(t_row + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+    const int key0 = tile * UN;
+    const bool edge = key0 + UN - 1 > lim;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < UN; ++j) {
+      float x = s[j] * A.scale_log2;
+      if (edge && key0 + j > lim) x = -INFINITY;
+      s[j] = x;
+      mx = fmaxf(mx, x);
+    }
+    // the reference only moves when some row of the warp outgrows it by more than REF_SLACK
+    if (__any_sync(0xffffffffu, mx > m_ref + REF_SLACK)) {
+      const float m_new = fmaxf(m_ref, mx);
+      const float corr = m_new == -INFINITY ? 1.f : ex2(m_ref - m_new);
+      m_ref = m_new;
+      l_run *= corr;
+      if (tile > 0) {  // O holds earlier tiles: rescale this row of it
+#pragma unroll
+        for (int c0 = 0; c0 < UD; c0 += 32) {
+          float o[32];
+          tmem_ld32(t_row + O_COL + c0, o);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] *= corr;
+          tmem_st32(t_row + O_COL + c0, o);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      }
+    }
+    const float ref = m_ref == -INFINITY ? 0.f : m_ref;
+    float sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < UN / 8; ++c) {
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p0 = ex2(s[8 * c + 2 * e] - ref), p1 = ex2(s[8 * c + 2 * e + 1] - ref);
+        sum += p0 + p1;
+        w[e] = pack16(p0, p1, bf16);
+      }
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_s + swz(tid, c)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+    }
+    l_run += sum;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P stores -> tensor-core reads
+    asm volatile("tcgen05.fence::before_thread_sync;");
+    __syncthreads();
+
+    if (tid == 0) {  // O += P V
+      asm volatile("tcgen05.fence::after_thread_sync;");
+#pragma unroll
+      for (int k = 0; k < UN / 16; ++k) {
+        const uint64_t a = make_desc(p_s + k * 32, 16, 1024);
+        // V as it lies in memory: rows = keys, 128 bytes = 64 channels per panel; 16 keys = two 8-key groups
+        const uint64_t b = make_desc(v_s + stage * KV_BYTES + k * 2048, UN * 128, 1024);
+        mma_f16(tmem + O_COL, a, b, idesc_pv, (tile > 0 || k > 0) ? 1u : 0u);
+      }
+      mma_commit(&bar_o);
+    }
+    // P, this stage of K / V and O are free again once the MMAs have completed
+    if (!bar_wait(&bar_o, tile & 1)) { ok = false; }
+    ok = __syncthreads_and(ok);
+    asm volatile("tcgen05.fence::after_thread_sync;");
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+  if (ok) {  // every lane takes part in the TMEM loads; rows past the end just do not store
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    const int64_t base_o = (int64_t)(q0 + tok) * A.o_s0 + (int64_t)hq * A.o_s1;
+#pragma unroll
+    for (int c0 = 0; c0 < UD; c0 += 32) {
+      float o[32];
+      tmem_ld32(t_row + O_COL + c0, o);
+      if (live) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const float x0 = o[j] * inv, x1 = o[j + 1] * inv;
+          const int d = c0 + j;
+          if (A.out_dtype == ECHOKV_DT_F32) {
+            *reinterpret_cast<float2*>(reinterpret_cast<float*>(A.out) + base_o + d) = make_float2(x0, x1);
+          } else {
+            *reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(A.out) + base_o + d) = pack16(x0, x1, A.out_dtype == ECHOKV_DT_BF16);
+          }
+        }
+      }
+    }
+  }
+  if (!ok && tid == 0 && A.status) atomicExch(A.status, 1);
+  asm volatile("tcgen05.fence::before_thread_sync;");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+}
+
+}  // namespace umma
+
+// Launches the tcgen05 kernel when the shape fits (head size 128, 16-bit inputs); otherwise leaves
+// `handled` false.
+int launch_prefill_umma(const void* q, int64_t q_s0, int64_t q_s1, const void* k, const void* v, int64_t kv_s0,
+                        int64_t kv_s1, int dtype, const int32_t* chunks, int64_t n_chunks, int max_rows, void* out,
+                        int64_t o_s0, int64_t o_s1, int out_dtype, float scale_log2, int gqa, int H, int head_size,
+                        cudaStream_t st, bool* handled) {
+  using namespace umma;
+  *handled = false;
+  if (head_size != UD || (dtype != ECHOKV_DT_F16 && dtype != ECHOKV_DT_BF16)) return ECHOKV_OK;
+  Args A;
+  A.q = q; A.k = k; A.v = v; A.out = out; A.chunks = chunks;
+  A.q_s0 = q_s0; A.q_s1 = q_s1; A.kv_s0 = kv_s0; A.kv_s1 = kv_s1; A.o_s0 = o_s0; A.o_s1 = o_s1;
+  A.gqa = gqa; A.out_dtype = out_dtype; A.is_bf16 = dtype == ECHOKV_DT_BF16; A.scale_log2 = scale_log2;
+  A.status = nullptr;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return check_launch("prefill (tcgen05 kernel)");
+    configured[dev] = true;
+  }
+  dim3 grid((max_rows + UM - 1) / UM, H, (unsigned)n_chunks);
+  prefill_umma_kernel<<<grid, UM, SMEM_BYTES, st>>>(A);
+  const int rc = check_launch("prefill (tcgen05 kernel)");
+  if (rc) return rc;
+  *handled = true;
+  return ECHOKV_OK;
+}
+
+}  // namespace echokv

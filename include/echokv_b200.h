@@ -219,6 +219,11 @@ int echokv_prefill(const void* query, int64_t q_s0, int64_t q_s1, const void* k_
 int echokv_gather_rows(const void* src, int64_t src_row_stride_bytes, const int64_t* rows, int64_t n, void* dst,
                        int64_t row_bytes, void* stream);
 
+/* Kernel selection of echokv_prefill: 0 (default) takes the tcgen05 / TMEM kernel when the shape fits
+ * (head size 128) and the mma.sync kernel otherwise; 1 always takes the mma.sync kernel.  Returns the
+ * previous setting.  No counterpart in the reference (it calls a flash-attention library there). */
+int echokv_set_prefill_path(int path);
+
 /* Canary attention-KL estimator, batched over layers -- canary_kl (canary.py:59-89).
  * query [L, nq, Hq, D] of q_dtype, kref float32 [L, W, H, D] oldest key first (ring
  * already unrolled: row (ring_pos + i) % W when ring_fill == W).  Scores the last

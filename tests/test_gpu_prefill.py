@@ -34,8 +34,22 @@ CASES = [
 ]
 
 
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma_sync"])
 @pytest.mark.parametrize("sc", CASES, ids=lambda s: s.name)
-def test_dense_path_matches_oracle_and_row_path(sc):
+def test_dense_path_matches_oracle_and_row_path(sc, kernel):
+    """Both attention kernels of the dense path (head size 128 takes the tcgen05 kernel unless told otherwise)."""
+    import torch
+    from echokv_b200 import _native as N
+    from echokv_b200.kernels.prefill import build_dense, build_rows, prefill_attention
+
+    old = N.lib.echokv_set_prefill_path(1 if kernel == "mma_sync" else 0)
+    try:
+        _dense_case(sc)
+    finally:
+        N.lib.echokv_set_prefill_path(old)
+
+
+def _dense_case(sc):
     import torch
     from echokv_b200.kernels.prefill import build_dense, build_rows, prefill_attention
 
