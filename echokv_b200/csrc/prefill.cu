@@ -309,9 +309,9 @@ namespace echokv {
 int launch_prefill_umma(const void* q, int64_t q_s0, int64_t q_s1, const void* k, const void* v, int64_t kv_s0,
                         int64_t kv_s1, int dtype, const int32_t* chunks, int64_t n_chunks, int max_rows, void* out,
                         int64_t o_s0, int64_t o_s1, int out_dtype, float scale_log2, int gqa, int H, int head_size,
-                        cudaStream_t st, bool* handled);
+                        cudaStream_t st, bool pipelined, bool* handled);
 }
-static int g_prefill_path = 0;  // 0: tcgen05 kernel when the shape fits, 1: always the mma.sync kernel
+static int g_prefill_path = 0;  // 0: pipelined tcgen05 kernel when the shape fits, 1: always the mma.sync kernel, 2: plain tcgen05 kernel
 
 extern "C" {
 
@@ -344,10 +344,11 @@ int echokv_prefill(const void* query, int64_t q_s0, int64_t q_s1, const void* k_
   A.scale_log2 = softmax_scale * 1.4426950408889634f;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int max_rows = max_chunk_len * A.gqa;
-  if (g_prefill_path == 0) {
+  if (g_prefill_path != 1) {
     bool handled = false;
     const int rc = launch_prefill_umma(query, q_s0, q_s1, k_dense, v_dense, kv_s0, kv_s1, dtype, chunks, n_chunks, max_rows, out,
-                                       o_s0, o_s1, out_dtype, A.scale_log2, A.gqa, num_kv_heads, head_size, st, &handled);
+                                       o_s0, o_s1, out_dtype, A.scale_log2, A.gqa, num_kv_heads, head_size, st, g_prefill_path == 0,
+                                       &handled);
     if (rc || handled) return rc;
   }
   if (dtype == ECHOKV_DT_F16)

@@ -81,18 +81,23 @@ __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity) {
   }
   return false;
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
                  "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
                  "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
                  "=r"(r[30]), "=r"(r[31])
                : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  tmem_ld32_nowait(taddr, r);
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// The registers of a tcgen05.ld may only be read after this.
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
                ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
@@ -212,20 +217,25 @@ __global__ void __launch_bounds__(UM, 2) prefill_umma_kernel(Args A) {
     if (!ok) break;
     asm volatile("tcgen05.fence::after_thread_sync;");
 
-    // this row's scores
+    // this row's scores: both halves in flight, then one wait
+    uint32_t raw[UN];
+    tmem_ld32_nowait(t_row, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
+    tmem_ld32_nowait(t_row + 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[32]));
+    tmem_ld_wait();
     float s[UN];
-    tmem_ld32(t_row, *reinterpret_cast<float(*)[32]>(&s[0]));
-    tmem_ld32(t_row + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
-    const int key0 = tile * UN;
-    const bool edge = key0 + UN - 1 > lim;
-    float mx = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < UN; ++j) {
-      float x = s[j] * A.scale_log2;
-      if (edge && key0 + j > lim) x = -INFINITY;
-      s[j] = x;
-      mx = fmaxf(mx, x);
+    for (int j = 0; j < UN; ++j) s[j] = __uint_as_float(raw[j]);
+    const int key0 = tile * UN;
+    if (key0 + UN - 1 > lim) {  // the tile crosses this row's causal limit
+#pragma unroll
+      for (int j = 0; j < UN; ++j)
+        if (key0 + j > lim) s[j] = -INFINITY;
     }
+    // maximum in raw units (the scale is positive), four independent chains
+    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < UN; ++j) m4[j & 3] = fmaxf(m4[j & 3], s[j]);
+    const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * A.scale_log2;
     // the reference only moves when some row of the warp outgrows it by more than REF_SLACK
     if (__any_sync(0xffffffffu, mx > m_ref + REF_SLACK)) {
       const float m_new = fmaxf(m_ref, mx);
@@ -244,19 +254,20 @@ __global__ void __launch_bounds__(UM, 2) prefill_umma_kernel(Args A) {
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
     }
-    const float ref = m_ref == -INFINITY ? 0.f : m_ref;
-    float sum = 0.f;
+    const float nref = m_ref == -INFINITY ? 0.f : -m_ref;
+    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int c = 0; c < UN / 8; ++c) {
       uint32_t w[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float p0 = ex2(s[8 * c + 2 * e] - ref), p1 = ex2(s[8 * c + 2 * e + 1] - ref);
-        sum += p0 + p1;
+        const float p0 = ex2(fmaf(s[8 * c + 2 * e], A.scale_log2, nref)), p1 = ex2(fmaf(s[8 * c + 2 * e + 1], A.scale_log2, nref));
+        sum4[e] += p0 + p1;
         w[e] = pack16(p0, p1, bf16);
       }
       asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_s + swz(tid, c)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
     }
+    const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
     l_run += sum;
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P stores -> tensor-core reads
     asm volatile("tcgen05.fence::before_thread_sync;");
@@ -307,6 +318,214 @@ __global__ void __launch_bounds__(UM, 2) prefill_umma_kernel(Args A) {
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
 }
 
+
+// The same computation with the tensor work overlapped with the softmax: the scores of tile t + 1 are
+// issued (into a second 64-column score buffer) before the softmax of tile t starts, and O += P V of tile
+// t runs while the softmax of tile t + 1 does.  One CTA per SM; K / V tiles in a four-stage ring.
+constexpr int PIPE_STAGES = 4;
+constexpr int S1_COL = 192;
+constexpr int SMEM_PIPE = Q_BYTES + 2 * PIPE_STAGES * KV_BYTES + P_BYTES + 1024;
+
+__global__ void __launch_bounds__(UM, 1) prefill_umma_pipe_kernel(Args A) {
+  extern __shared__ unsigned char dyn[];
+  __shared__ __align__(8) uint64_t bar_s[2], bar_o;
+  __shared__ uint32_t tmem_slot;
+  const uint32_t base = (smem_u32(dyn) + 1023u) & ~1023u;
+  const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + PIPE_STAGES * KV_BYTES, p_s = v_s + PIPE_STAGES * KV_BYTES;
+
+  const int4 ck = reinterpret_cast<const int4*>(A.chunks)[blockIdx.z];
+  const int q0 = ck.x, nq = ck.y - ck.x, ctx = ck.z;
+  const int64_t dense0 = ck.w;
+  const int gqa = A.gqa, h = blockIdx.y;
+  const int rows = nq * gqa;
+  const int row0 = blockIdx.x * UM;
+  if (row0 >= rows) return;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const bool bf16 = A.is_bf16 != 0;
+  const int row = row0 + tid;
+  const bool live = row < rows;
+  const int tok = live ? row / gqa : 0, hq = live ? h * gqa + row % gqa : 0;
+  const int lim = live ? ctx - nq + tok : -1;
+  const int last_tok = min(nq - 1, (row0 + UM - 1) / gqa);
+  const int n_keys = min(ctx, ctx - nq + last_tok + 1);
+  const int n_tiles = (n_keys + UN - 1) / UN;
+
+  const uint16_t* qp = reinterpret_cast<const uint16_t*>(A.q) + (int64_t)(q0 + tok) * A.q_s0 + (int64_t)hq * A.q_s1;
+  const uint16_t* kp = reinterpret_cast<const uint16_t*>(A.k) + dense0 * A.kv_s0 + (int64_t)h * A.kv_s1;
+  const uint16_t* vp = reinterpret_cast<const uint16_t*>(A.v) + dense0 * A.kv_s0 + (int64_t)h * A.kv_s1;
+  auto load_tile = [&](int tile) {
+    const int key0 = tile * UN, stage = tile % PIPE_STAGES;
+#pragma unroll
+    for (int j = 0; j < (UN * 16) / UM; ++j) {
+      const int idx = tid + UM * j, key = idx >> 4, c = idx & 15;
+      const bool on = key0 + key < n_keys;
+      const int64_t src = (int64_t)(on ? key0 + key : 0) * A.kv_s0 + c * 8;
+      const uint32_t off = stage * KV_BYTES + (c >> 3) * (UN * 128) + swz(key, c & 7);
+      cp16(k_s + off, kp + src, on);
+      cp16(v_s + off, vp + src, on);
+    }
+  };
+#pragma unroll
+  for (int c = 0; c < 16; ++c) cp16(q_s + (c >> 3) * (UM * 128) + swz(tid, c & 7), qp + c * 8, live);
+  // tiles 0 .. PIPE_STAGES - 2 in flight, one commit group each (empty groups keep the count regular)
+#pragma unroll
+  for (int t0 = 0; t0 < PIPE_STAGES - 1; ++t0) {
+    if (t0 < n_tiles) load_tile(t0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_s[0])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_s[1])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_o)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("cp.async.wait_group %0;" ::"n"(PIPE_STAGES - 2) : "memory");  // Q and tile 0 have landed
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;");
+  const uint32_t tmem = tmem_slot;
+  const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t fmt = bf16 ? 1u : 0u;
+  const uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(UN >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
+  const uint32_t idesc_pv = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(UD >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
+  auto issue_qk = [&](int tile) {  // S[tile & 1] = Q K_tile^T (one thread)
+    const int stage = tile % PIPE_STAGES;
+    const uint32_t s_col = (tile & 1) ? S1_COL : 0;
+#pragma unroll
+    for (int k = 0; k < UD / 16; ++k) {
+      const uint64_t a = make_desc(q_s + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
+      const uint64_t b = make_desc(k_s + stage * KV_BYTES + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
+      mma_f16(tmem + s_col, a, b, idesc_qk, k > 0);
+    }
+    mma_commit(&bar_s[tile & 1]);
+  };
+  if (tid == 0) issue_qk(0);
+
+  float m_ref = -INFINITY, l_run = 0.f;
+  bool ok = true;
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    // tile + 1 has landed (all but the newest copy group are complete) and is visible to the tensor cores
+    asm volatile("cp.async.wait_group %0;" ::"n"(PIPE_STAGES - 3) : "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (!bar_wait(&bar_s[tile & 1], (tile >> 1) & 1)) ok = false;  // the scores of this tile
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    asm volatile("tcgen05.fence::after_thread_sync;");
+    // the next tile's scores run on the tensor cores while this tile's softmax runs here; their buffer was
+    // last read by the softmax of tile - 1, which every thread has left
+    if (tid == 0 && tile + 1 < n_tiles) issue_qk(tile + 1);
+
+    uint32_t raw[UN];
+    const uint32_t s_col = (tile & 1) ? S1_COL : 0;
+    tmem_ld32_nowait(t_row + s_col, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
+    tmem_ld32_nowait(t_row + s_col + 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[32]));
+    tmem_ld_wait();
+    float s[UN];
+#pragma unroll
+    for (int j = 0; j < UN; ++j) s[j] = __uint_as_float(raw[j]);
+    const int key0 = tile * UN;
+    if (key0 + UN - 1 > lim) {
+#pragma unroll
+      for (int j = 0; j < UN; ++j)
+        if (key0 + j > lim) s[j] = -INFINITY;
+    }
+    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < UN; ++j) m4[j & 3] = fmaxf(m4[j & 3], s[j]);
+    const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * A.scale_log2;
+    bool o_idle = tile == 0;  // O += P V of the previous tile is known to have completed
+    if (__any_sync(0xffffffffu, mx > m_ref + REF_SLACK)) {
+      const float m_new = fmaxf(m_ref, mx);
+      const float corr = m_new == -INFINITY ? 1.f : ex2(m_ref - m_new);
+      m_ref = m_new;
+      l_run *= corr;
+      if (tile > 0) {  // rescale this row of O, once the MMAs that accumulate into it are done
+        if (!bar_wait(&bar_o, (tile - 1) & 1)) ok = false;
+        o_idle = true;
+        asm volatile("tcgen05.fence::after_thread_sync;");
+#pragma unroll
+        for (int c0 = 0; c0 < UD; c0 += 32) {
+          float o[32];
+          tmem_ld32(t_row + O_COL + c0, o);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] *= corr;
+          tmem_st32(t_row + O_COL + c0, o);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      }
+    }
+    const float nref = m_ref == -INFINITY ? 0.f : -m_ref;
+    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t w[UN / 2];
+#pragma unroll
+    for (int c = 0; c < UN / 8; ++c) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p0 = ex2(fmaf(s[8 * c + 2 * e], A.scale_log2, nref)), p1 = ex2(fmaf(s[8 * c + 2 * e + 1], A.scale_log2, nref));
+        sum4[e] += p0 + p1;
+        w[4 * c + e] = pack16(p0, p1, bf16);
+      }
+    }
+    l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+    // P, the stage tile - 1 used and O are free once the previous O += P V has completed
+    if (!o_idle && !bar_wait(&bar_o, (tile - 1) & 1)) ok = false;
+    if (tile + PIPE_STAGES - 1 < n_tiles) load_tile(tile + PIPE_STAGES - 1);  // into the stage tile - 1 used
+    asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+    for (int c = 0; c < UN / 8; ++c)
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_s + swz(tid, c)), "r"(w[4 * c]), "r"(w[4 * c + 1]), "r"(w[4 * c + 2]), "r"(w[4 * c + 3]) : "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;");
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    if (tid == 0) {  // O += P V
+      asm volatile("tcgen05.fence::after_thread_sync;");
+      const int stage = tile % PIPE_STAGES;
+#pragma unroll
+      for (int k = 0; k < UN / 16; ++k) {
+        const uint64_t a = make_desc(p_s + k * 32, 16, 1024);
+        const uint64_t b = make_desc(v_s + stage * KV_BYTES + k * 2048, UN * 128, 1024);
+        mma_f16(tmem + O_COL, a, b, idesc_pv, (tile > 0 || k > 0) ? 1u : 0u);
+      }
+      mma_commit(&bar_o);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (ok && !bar_wait(&bar_o, (n_tiles - 1) & 1)) ok = false;
+  ok = __syncthreads_and(ok);
+  asm volatile("tcgen05.fence::after_thread_sync;");
+  if (ok) {
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    const int64_t base_o = (int64_t)(q0 + tok) * A.o_s0 + (int64_t)hq * A.o_s1;
+#pragma unroll
+    for (int c0 = 0; c0 < UD; c0 += 32) {
+      float o[32];
+      tmem_ld32(t_row + O_COL + c0, o);
+      if (live) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const float x0 = o[j] * inv, x1 = o[j + 1] * inv;
+          const int d = c0 + j;
+          if (A.out_dtype == ECHOKV_DT_F32) {
+            *reinterpret_cast<float2*>(reinterpret_cast<float*>(A.out) + base_o + d) = make_float2(x0, x1);
+          } else {
+            *reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(A.out) + base_o + d) = pack16(x0, x1, A.out_dtype == ECHOKV_DT_BF16);
+          }
+        }
+      }
+    }
+  }
+  if (!ok && tid == 0 && A.status) atomicExch(A.status, 1);
+  asm volatile("tcgen05.fence::before_thread_sync;");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+}
+
 }  // namespace umma
 
 // Launches the tcgen05 kernel when the shape fits (head size 128, 16-bit inputs); otherwise leaves
@@ -314,7 +533,7 @@ __global__ void __launch_bounds__(UM, 2) prefill_umma_kernel(Args A) {
 int launch_prefill_umma(const void* q, int64_t q_s0, int64_t q_s1, const void* k, const void* v, int64_t kv_s0,
                         int64_t kv_s1, int dtype, const int32_t* chunks, int64_t n_chunks, int max_rows, void* out,
                         int64_t o_s0, int64_t o_s1, int out_dtype, float scale_log2, int gqa, int H, int head_size,
-                        cudaStream_t st, bool* handled) {
+                        cudaStream_t st, bool pipelined, bool* handled) {
   using namespace umma;
   *handled = false;
   if (head_size != UD || (dtype != ECHOKV_DT_F16 && dtype != ECHOKV_DT_BF16)) return ECHOKV_OK;
@@ -327,12 +546,14 @@ int launch_prefill_umma(const void* q, int64_t q_s0, int64_t q_s1, const void* k
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_umma_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_PIPE) != cudaSuccess)
       return check_launch("prefill (tcgen05 kernel)");
     configured[dev] = true;
   }
   dim3 grid((max_rows + UM - 1) / UM, H, (unsigned)n_chunks);
-  prefill_umma_kernel<<<grid, UM, SMEM_BYTES, st>>>(A);
+  if (pipelined) prefill_umma_pipe_kernel<<<grid, UM, SMEM_PIPE, st>>>(A);
+  else prefill_umma_kernel<<<grid, UM, SMEM_BYTES, st>>>(A);
   const int rc = check_launch("prefill (tcgen05 kernel)");
   if (rc) return rc;
   *handled = true;

@@ -220,7 +220,8 @@ int echokv_gather_rows(const void* src, int64_t src_row_stride_bytes, const int6
                        int64_t row_bytes, void* stream);
 
 /* Kernel selection of echokv_prefill: 0 (default) takes the tcgen05 / TMEM kernel when the shape fits
- * (head size 128) and the mma.sync kernel otherwise; 1 always takes the mma.sync kernel.  Returns the
+ * (head size 128) and the mma.sync kernel otherwise; 1 always takes the mma.sync kernel; 2 takes the
+ * tcgen05 kernel without the overlap of tensor work and softmax (two CTAs per SM).  Returns the
  * previous setting.  No counterpart in the reference (it calls a flash-attention library there). */
 int echokv_set_prefill_path(int path);
 
