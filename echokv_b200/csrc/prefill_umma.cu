@@ -324,29 +324,32 @@ __global__ void __launch_bounds__(UM, 2) prefill_umma_kernel(Args A) {
 // t runs while the softmax of tile t + 1 does.  One CTA per SM; K / V tiles in a four-stage ring.
 constexpr int PIPE_STAGES = 4;
 constexpr int S1_COL = 192;
-constexpr int SMEM_PIPE = Q_BYTES + 2 * PIPE_STAGES * KV_BYTES + P_BYTES + 1024;
+template <int G> constexpr int smem_pipe() { return G * (Q_BYTES + P_BYTES) + 2 * PIPE_STAGES * KV_BYTES + 1024; }
 
-__global__ void __launch_bounds__(UM, 1) prefill_umma_pipe_kernel(Args A) {
+// G groups of 128 rows share the K / V tiles of a CTA (G = 2: 256 threads, all 512 TMEM columns).
+template <int G>
+__global__ void __launch_bounds__(UM * G, 1) prefill_umma_pipe_kernel(Args A) {
   extern __shared__ unsigned char dyn[];
   __shared__ __align__(8) uint64_t bar_s[2], bar_o;
   __shared__ uint32_t tmem_slot;
   const uint32_t base = (smem_u32(dyn) + 1023u) & ~1023u;
-  const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + PIPE_STAGES * KV_BYTES, p_s = v_s + PIPE_STAGES * KV_BYTES;
+  const uint32_t q_s = base, k_s = q_s + G * Q_BYTES, v_s = k_s + PIPE_STAGES * KV_BYTES, p_s = v_s + PIPE_STAGES * KV_BYTES;
 
   const int4 ck = reinterpret_cast<const int4*>(A.chunks)[blockIdx.z];
   const int q0 = ck.x, nq = ck.y - ck.x, ctx = ck.z;
   const int64_t dense0 = ck.w;
   const int gqa = A.gqa, h = blockIdx.y;
   const int rows = nq * gqa;
-  const int row0 = blockIdx.x * UM;
+  const int row0 = blockIdx.x * UM * G;
   if (row0 >= rows) return;
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int grp = tid / UM, r128 = tid % UM;  // group of 128 rows, row inside it (= TMEM lane)
   const bool bf16 = A.is_bf16 != 0;
   const int row = row0 + tid;
   const bool live = row < rows;
   const int tok = live ? row / gqa : 0, hq = live ? h * gqa + row % gqa : 0;
   const int lim = live ? ctx - nq + tok : -1;
-  const int last_tok = min(nq - 1, (row0 + UM - 1) / gqa);
+  const int last_tok = min(nq - 1, (row0 + UM * G - 1) / gqa);
   const int n_keys = min(ctx, ctx - nq + last_tok + 1);
   const int n_tiles = (n_keys + UN - 1) / UN;
 
@@ -356,8 +359,8 @@ __global__ void __launch_bounds__(UM, 1) prefill_umma_pipe_kernel(Args A) {
   auto load_tile = [&](int tile) {
     const int key0 = tile * UN, stage = tile % PIPE_STAGES;
 #pragma unroll
-    for (int j = 0; j < (UN * 16) / UM; ++j) {
-      const int idx = tid + UM * j, key = idx >> 4, c = idx & 15;
+    for (int j = 0; j < (UN * 16) / (UM * G); ++j) {
+      const int idx = tid + UM * G * j, key = idx >> 4, c = idx & 15;
       const bool on = key0 + key < n_keys;
       const int64_t src = (int64_t)(on ? key0 + key : 0) * A.kv_s0 + c * 8;
       const uint32_t off = stage * KV_BYTES + (c >> 3) * (UN * 128) + swz(key, c & 7);
@@ -366,7 +369,7 @@ __global__ void __launch_bounds__(UM, 1) prefill_umma_pipe_kernel(Args A) {
     }
   };
 #pragma unroll
-  for (int c = 0; c < 16; ++c) cp16(q_s + (c >> 3) * (UM * 128) + swz(tid, c & 7), qp + c * 8, live);
+  for (int c = 0; c < 16; ++c) cp16(q_s + grp * Q_BYTES + (c >> 3) * (UM * 128) + swz(r128, c & 7), qp + c * 8, live);
   // tiles 0 .. PIPE_STAGES - 2 in flight, one commit group each (empty groups keep the count regular)
 #pragma unroll
   for (int t0 = 0; t0 < PIPE_STAGES - 1; ++t0) {
@@ -380,7 +383,7 @@ __global__ void __launch_bounds__(UM, 1) prefill_umma_pipe_kernel(Args A) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS * G));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
   asm volatile("cp.async.wait_group %0;" ::"n"(PIPE_STAGES - 2) : "memory");  // Q and tile 0 have landed
@@ -389,7 +392,7 @@ __global__ void __launch_bounds__(UM, 1) prefill_umma_pipe_kernel(Args A) {
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;");
   const uint32_t tmem = tmem_slot;
-  const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t t_row = tmem + ((uint32_t)((warp & 3) * 32) << 16) + grp * TMEM_COLS;  // this warp's quarter of the lanes, this group's columns
   const uint32_t fmt = bf16 ? 1u : 0u;
   const uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(UN >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
   const uint32_t idesc_pv = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(UD >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
@@ -397,11 +400,13 @@ __global__ void __launch_bounds__(UM, 1) prefill_umma_pipe_kernel(Args A) {
     const int stage = tile % PIPE_STAGES;
     const uint32_t s_col = (tile & 1) ? S1_COL : 0;
 #pragma unroll
-    for (int k = 0; k < UD / 16; ++k) {
-      const uint64_t a = make_desc(q_s + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
-      const uint64_t b = make_desc(k_s + stage * KV_BYTES + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
-      mma_f16(tmem + s_col, a, b, idesc_qk, k > 0);
-    }
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int k = 0; k < UD / 16; ++k) {
+        const uint64_t a = make_desc(q_s + g * Q_BYTES + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
+        const uint64_t b = make_desc(k_s + stage * KV_BYTES + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
+        mma_f16(tmem + g * TMEM_COLS + s_col, a, b, idesc_qk, k > 0);
+      }
     mma_commit(&bar_s[tile & 1]);
   };
   if (tid == 0) issue_qk(0);
@@ -478,7 +483,7 @@ __global__ void __launch_bounds__(UM, 1) prefill_umma_pipe_kernel(Args A) {
     asm volatile("cp.async.commit_group;" ::: "memory");
 #pragma unroll
     for (int c = 0; c < UN / 8; ++c)
-      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_s + swz(tid, c)), "r"(w[4 * c]), "r"(w[4 * c + 1]), "r"(w[4 * c + 2]), "r"(w[4 * c + 3]) : "memory");
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_s + grp * P_BYTES + swz(r128, c)), "r"(w[4 * c]), "r"(w[4 * c + 1]), "r"(w[4 * c + 2]), "r"(w[4 * c + 3]) : "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;");
     ok = __syncthreads_and(ok);
@@ -487,11 +492,13 @@ __global__ void __launch_bounds__(UM, 1) prefill_umma_pipe_kernel(Args A) {
       asm volatile("tcgen05.fence::after_thread_sync;");
       const int stage = tile % PIPE_STAGES;
 #pragma unroll
-      for (int k = 0; k < UN / 16; ++k) {
-        const uint64_t a = make_desc(p_s + k * 32, 16, 1024);
-        const uint64_t b = make_desc(v_s + stage * KV_BYTES + k * 2048, UN * 128, 1024);
-        mma_f16(tmem + O_COL, a, b, idesc_pv, (tile > 0 || k > 0) ? 1u : 0u);
-      }
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int k = 0; k < UN / 16; ++k) {
+          const uint64_t a = make_desc(p_s + g * P_BYTES + k * 32, 16, 1024);
+          const uint64_t b = make_desc(v_s + stage * KV_BYTES + k * 2048, UN * 128, 1024);
+          mma_f16(tmem + g * TMEM_COLS + O_COL, a, b, idesc_pv, (tile > 0 || k > 0) ? 1u : 0u);
+        }
       mma_commit(&bar_o);
     }
   }
@@ -523,7 +530,7 @@ __global__ void __launch_bounds__(UM, 1) prefill_umma_pipe_kernel(Args A) {
   if (!ok && tid == 0 && A.status) atomicExch(A.status, 1);
   asm volatile("tcgen05.fence::before_thread_sync;");
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS * G));
 }
 
 }  // namespace umma
@@ -547,13 +554,20 @@ int launch_prefill_umma(const void* q, int64_t q_s0, int64_t q_s1, const void* k
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
     if (cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
-        cudaFuncSetAttribute(prefill_umma_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_PIPE) != cudaSuccess)
+        cudaFuncSetAttribute(prefill_umma_pipe_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pipe<1>()) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_umma_pipe_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pipe<2>()) != cudaSuccess)
       return check_launch("prefill (tcgen05 kernel)");
     configured[dev] = true;
   }
   dim3 grid((max_rows + UM - 1) / UM, H, (unsigned)n_chunks);
-  if (pipelined) prefill_umma_pipe_kernel<<<grid, UM, SMEM_PIPE, st>>>(A);
-  else prefill_umma_kernel<<<grid, UM, SMEM_BYTES, st>>>(A);
+  if (pipelined && max_rows > UM) {  // two groups of 128 rows per CTA share the K / V tiles
+    grid.x = (max_rows + 2 * UM - 1) / (2 * UM);
+    prefill_umma_pipe_kernel<2><<<grid, 2 * UM, smem_pipe<2>(), st>>>(A);
+  } else if (pipelined) {
+    prefill_umma_pipe_kernel<1><<<grid, UM, smem_pipe<1>(), st>>>(A);
+  } else {
+    prefill_umma_kernel<<<grid, UM, SMEM_BYTES, st>>>(A);
+  }
   const int rc = check_launch("prefill (tcgen05 kernel)");
   if (rc) return rc;
   *handled = true;
