@@ -319,19 +319,29 @@ __global__ void __launch_bounds__(UM, 2) prefill_umma_kernel(Args A) {
 }
 
 
-// The same computation with the tensor work overlapped with the softmax: the scores of tile t + 1 are
-// issued (into a second 64-column score buffer) before the softmax of tile t starts, and O += P V of tile
-// t runs while the softmax of tile t + 1 does.  One CTA per SM; K / V tiles in a four-stage ring.
+// The same computation with the tensor work overlapped with the softmax and no CTA-wide barrier in the
+// loop.  G groups of 128 rows (G = 2: all 512 TMEM columns) share the K / V tiles of a CTA; one extra warp
+// only issues MMAs.  Per 64-key tile t:
+//   row threads   wait for the scores of t (bar_s), take the softmax, wait until O += P V of t - 1 is done
+//                 (bar_o), start the copies of tile t + 3 into the stage t - 1 used, write P, arrive on bar_p;
+//                 at the top of the step they report that their copies of tile t + 1 have landed (bar_kv);
+//   issuer        waits bar_kv of t + 1 and issues its scores into the other score buffer, waits bar_p and
+//                 issues O += P V of t.
+// So the scores of t + 1 and O += P V of t run on the tensor cores under the softmax of t and t + 1.
 constexpr int PIPE_STAGES = 4;
 constexpr int S1_COL = 192;
 template <int G> constexpr int smem_pipe() { return G * (Q_BYTES + P_BYTES) + 2 * PIPE_STAGES * KV_BYTES + 1024; }
 
-// G groups of 128 rows share the K / V tiles of a CTA (G = 2: 256 threads, all 512 TMEM columns).
+__device__ __forceinline__ void bar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 template <int G>
-__global__ void __launch_bounds__(UM * G, 1) prefill_umma_pipe_kernel(Args A) {
+__global__ void __launch_bounds__(UM * G + 32, 1) prefill_umma_pipe_kernel(Args A) {
   extern __shared__ unsigned char dyn[];
-  __shared__ __align__(8) uint64_t bar_s[2], bar_o;
+  __shared__ __align__(8) uint64_t bar_s[2], bar_o, bar_p, bar_kv[PIPE_STAGES];
   __shared__ uint32_t tmem_slot;
+  constexpr int NROW = UM * G;  // row threads
   const uint32_t base = (smem_u32(dyn) + 1023u) & ~1023u;
   const uint32_t q_s = base, k_s = q_s + G * Q_BYTES, v_s = k_s + PIPE_STAGES * KV_BYTES, p_s = v_s + PIPE_STAGES * KV_BYTES;
 
@@ -340,27 +350,28 @@ __global__ void __launch_bounds__(UM * G, 1) prefill_umma_pipe_kernel(Args A) {
   const int64_t dense0 = ck.w;
   const int gqa = A.gqa, h = blockIdx.y;
   const int rows = nq * gqa;
-  const int row0 = blockIdx.x * UM * G;
+  const int row0 = blockIdx.x * NROW;
   if (row0 >= rows) return;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int grp = tid / UM, r128 = tid % UM;  // group of 128 rows, row inside it (= TMEM lane)
+  const bool issuer_warp = tid >= NROW;
+  const int grp = issuer_warp ? 0 : tid / UM, r128 = tid % UM;  // group of 128 rows, row inside it (= TMEM lane)
   const bool bf16 = A.is_bf16 != 0;
   const int row = row0 + tid;
-  const bool live = row < rows;
+  const bool live = !issuer_warp && row < rows;
   const int tok = live ? row / gqa : 0, hq = live ? h * gqa + row % gqa : 0;
   const int lim = live ? ctx - nq + tok : -1;
-  const int last_tok = min(nq - 1, (row0 + UM * G - 1) / gqa);
+  const int last_tok = min(nq - 1, (row0 + NROW - 1) / gqa);
   const int n_keys = min(ctx, ctx - nq + last_tok + 1);
   const int n_tiles = (n_keys + UN - 1) / UN;
 
   const uint16_t* qp = reinterpret_cast<const uint16_t*>(A.q) + (int64_t)(q0 + tok) * A.q_s0 + (int64_t)hq * A.q_s1;
   const uint16_t* kp = reinterpret_cast<const uint16_t*>(A.k) + dense0 * A.kv_s0 + (int64_t)h * A.kv_s1;
   const uint16_t* vp = reinterpret_cast<const uint16_t*>(A.v) + dense0 * A.kv_s0 + (int64_t)h * A.kv_s1;
-  auto load_tile = [&](int tile) {
+  auto load_tile = [&](int tile) {  // row threads only
     const int key0 = tile * UN, stage = tile % PIPE_STAGES;
 #pragma unroll
-    for (int j = 0; j < (UN * 16) / (UM * G); ++j) {
-      const int idx = tid + UM * G * j, key = idx >> 4, c = idx & 15;
+    for (int j = 0; j < (UN * 16) / NROW; ++j) {
+      const int idx = tid + NROW * j, key = idx >> 4, c = idx & 15;
       const bool on = key0 + key < n_keys;
       const int64_t src = (int64_t)(on ? key0 + key : 0) * A.kv_s0 + c * 8;
       const uint32_t off = stage * KV_BYTES + (c >> 3) * (UN * 128) + swz(key, c & 7);
@@ -368,166 +379,186 @@ __global__ void __launch_bounds__(UM * G, 1) prefill_umma_pipe_kernel(Args A) {
       cp16(v_s + off, vp + src, on);
     }
   };
+  if (!issuer_warp) {
 #pragma unroll
-  for (int c = 0; c < 16; ++c) cp16(q_s + grp * Q_BYTES + (c >> 3) * (UM * 128) + swz(r128, c & 7), qp + c * 8, live);
-  // tiles 0 .. PIPE_STAGES - 2 in flight, one commit group each (empty groups keep the count regular)
+    for (int c = 0; c < 16; ++c) cp16(q_s + grp * Q_BYTES + (c >> 3) * (UM * 128) + swz(r128, c & 7), qp + c * 8, live);
+    // tiles 0 .. PIPE_STAGES - 2 in flight, one commit group each (empty groups keep the count regular)
 #pragma unroll
-  for (int t0 = 0; t0 < PIPE_STAGES - 1; ++t0) {
-    if (t0 < n_tiles) load_tile(t0);
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int t0 = 0; t0 < PIPE_STAGES - 1; ++t0) {
+      if (t0 < n_tiles) load_tile(t0);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
   }
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_s[0])));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_s[1])));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar_o)));
+    auto init = [](uint64_t* b, int n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(n)); };
+    init(&bar_s[0], 1); init(&bar_s[1], 1); init(&bar_o, 1); init(&bar_p, NROW);
+    for (int i = 0; i < PIPE_STAGES; ++i) init(&bar_kv[i], NROW);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS * G));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
-  asm volatile("cp.async.wait_group %0;" ::"n"(PIPE_STAGES - 2) : "memory");  // Q and tile 0 have landed
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;");
   const uint32_t tmem = tmem_slot;
-  const uint32_t t_row = tmem + ((uint32_t)((warp & 3) * 32) << 16) + grp * TMEM_COLS;  // this warp's quarter of the lanes, this group's columns
   const uint32_t fmt = bf16 ? 1u : 0u;
   const uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(UN >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
   const uint32_t idesc_pv = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(UD >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
-  auto issue_qk = [&](int tile) {  // S[tile & 1] = Q K_tile^T (one thread)
-    const int stage = tile % PIPE_STAGES;
-    const uint32_t s_col = (tile & 1) ? S1_COL : 0;
-#pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-      for (int k = 0; k < UD / 16; ++k) {
-        const uint64_t a = make_desc(q_s + g * Q_BYTES + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
-        const uint64_t b = make_desc(k_s + stage * KV_BYTES + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
-        mma_f16(tmem + g * TMEM_COLS + s_col, a, b, idesc_qk, k > 0);
-      }
-    mma_commit(&bar_s[tile & 1]);
-  };
-  if (tid == 0) issue_qk(0);
-
-  float m_ref = -INFINITY, l_run = 0.f;
   bool ok = true;
-  for (int tile = 0; tile < n_tiles; ++tile) {
-    // tile + 1 has landed (all but the newest copy group are complete) and is visible to the tensor cores
-    asm volatile("cp.async.wait_group %0;" ::"n"(PIPE_STAGES - 3) : "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    if (!bar_wait(&bar_s[tile & 1], (tile >> 1) & 1)) ok = false;  // the scores of this tile
-    ok = __syncthreads_and(ok);
-    if (!ok) break;
-    asm volatile("tcgen05.fence::after_thread_sync;");
-    // the next tile's scores run on the tensor cores while this tile's softmax runs here; their buffer was
-    // last read by the softmax of tile - 1, which every thread has left
-    if (tid == 0 && tile + 1 < n_tiles) issue_qk(tile + 1);
 
-    uint32_t raw[UN];
-    const uint32_t s_col = (tile & 1) ? S1_COL : 0;
-    tmem_ld32_nowait(t_row + s_col, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
-    tmem_ld32_nowait(t_row + s_col + 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[32]));
-    tmem_ld_wait();
-    float s[UN];
+  if (issuer_warp) {
+    if (tid == NROW) {
+      auto issue_qk = [&](int tile) {  // S[tile & 1] = Q K_tile^T for every group
+        const int stage = tile % PIPE_STAGES;
+        const uint32_t s_col = (tile & 1) ? S1_COL : 0;
 #pragma unroll
-    for (int j = 0; j < UN; ++j) s[j] = __uint_as_float(raw[j]);
-    const int key0 = tile * UN;
-    if (key0 + UN - 1 > lim) {
+        for (int g = 0; g < G; ++g)
 #pragma unroll
-      for (int j = 0; j < UN; ++j)
-        if (key0 + j > lim) s[j] = -INFINITY;
-    }
-    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-    for (int j = 0; j < UN; ++j) m4[j & 3] = fmaxf(m4[j & 3], s[j]);
-    const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * A.scale_log2;
-    bool o_idle = tile == 0;  // O += P V of the previous tile is known to have completed
-    if (__any_sync(0xffffffffu, mx > m_ref + REF_SLACK)) {
-      const float m_new = fmaxf(m_ref, mx);
-      const float corr = m_new == -INFINITY ? 1.f : ex2(m_ref - m_new);
-      m_ref = m_new;
-      l_run *= corr;
-      if (tile > 0) {  // rescale this row of O, once the MMAs that accumulate into it are done
-        if (!bar_wait(&bar_o, (tile - 1) & 1)) ok = false;
-        o_idle = true;
+          for (int k = 0; k < UD / 16; ++k) {
+            const uint64_t a = make_desc(q_s + g * Q_BYTES + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
+            const uint64_t b = make_desc(k_s + stage * KV_BYTES + (k >> 2) * (UN * 128) + (k & 3) * 32, 16, 1024);
+            mma_f16(tmem + g * TMEM_COLS + s_col, a, b, idesc_qk, k > 0);
+          }
+        mma_commit(&bar_s[tile & 1]);
+      };
+      if (bar_wait(&bar_kv[0], 0)) {
         asm volatile("tcgen05.fence::after_thread_sync;");
-#pragma unroll
-        for (int c0 = 0; c0 < UD; c0 += 32) {
-          float o[32];
-          tmem_ld32(t_row + O_COL + c0, o);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] *= corr;
-          tmem_st32(t_row + O_COL + c0, o);
+        issue_qk(0);
+      } else {
+        ok = false;
+      }
+      for (int tile = 0; tile < n_tiles && ok; ++tile) {
+        if (tile + 1 < n_tiles) {  // the next tile's scores: their buffer was last read before bar_p of tile - 1
+          if (!bar_wait(&bar_kv[(tile + 1) % PIPE_STAGES], ((tile + 1) / PIPE_STAGES) & 1)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;");
+          issue_qk(tile + 1);
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        if (!bar_wait(&bar_p, tile & 1)) { ok = false; break; }  // every row thread has written its P
+        asm volatile("tcgen05.fence::after_thread_sync;");
+        const int stage = tile % PIPE_STAGES;
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+          for (int k = 0; k < UN / 16; ++k) {
+            const uint64_t a = make_desc(p_s + g * P_BYTES + k * 32, 16, 1024);
+            const uint64_t b = make_desc(v_s + stage * KV_BYTES + k * 2048, UN * 128, 1024);
+            mma_f16(tmem + g * TMEM_COLS + O_COL, a, b, idesc_pv, (tile > 0 || k > 0) ? 1u : 0u);
+          }
+        mma_commit(&bar_o);
       }
     }
-    const float nref = m_ref == -INFINITY ? 0.f : -m_ref;
-    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-    uint32_t w[UN / 2];
-#pragma unroll
-    for (int c = 0; c < UN / 8; ++c) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float p0 = ex2(fmaf(s[8 * c + 2 * e], A.scale_log2, nref)), p1 = ex2(fmaf(s[8 * c + 2 * e + 1], A.scale_log2, nref));
-        sum4[e] += p0 + p1;
-        w[4 * c + e] = pack16(p0, p1, bf16);
-      }
-    }
-    l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-    // P, the stage tile - 1 used and O are free once the previous O += P V has completed
-    if (!o_idle && !bar_wait(&bar_o, (tile - 1) & 1)) ok = false;
-    if (tile + PIPE_STAGES - 1 < n_tiles) load_tile(tile + PIPE_STAGES - 1);  // into the stage tile - 1 used
-    asm volatile("cp.async.commit_group;" ::: "memory");
-#pragma unroll
-    for (int c = 0; c < UN / 8; ++c)
-      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_s + grp * P_BYTES + swz(r128, c)), "r"(w[4 * c]), "r"(w[4 * c + 1]), "r"(w[4 * c + 2]), "r"(w[4 * c + 3]) : "memory");
+  } else {
+    const uint32_t t_row = tmem + ((uint32_t)((warp & 3) * 32) << 16) + grp * TMEM_COLS;  // this warp's lanes, this group's columns
+    // Q and tile 0 have landed
+    asm volatile("cp.async.wait_group %0;" ::"n"(PIPE_STAGES - 2) : "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;");
-    ok = __syncthreads_and(ok);
-    if (!ok) break;
-    if (tid == 0) {  // O += P V
+    bar_arrive(&bar_kv[0]);
+    float m_ref = -INFINITY, l_run = 0.f;
+    for (int tile = 0; tile < n_tiles; ++tile) {
+      if (tile + 1 < n_tiles) {  // my copies of tile + 1 have landed (all but the newest copy group are complete)
+        asm volatile("cp.async.wait_group %0;" ::"n"(PIPE_STAGES - 3) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        bar_arrive(&bar_kv[(tile + 1) % PIPE_STAGES]);
+      }
+      if (!__all_sync(0xffffffffu, bar_wait(&bar_s[tile & 1], (tile >> 1) & 1))) { ok = false; break; }  // the scores of this tile
       asm volatile("tcgen05.fence::after_thread_sync;");
-      const int stage = tile % PIPE_STAGES;
+      uint32_t raw[UN];
+      const uint32_t s_col = (tile & 1) ? S1_COL : 0;
+      tmem_ld32_nowait(t_row + s_col, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
+      tmem_ld32_nowait(t_row + s_col + 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[32]));
+      tmem_ld_wait();
+      float s[UN];
 #pragma unroll
-      for (int g = 0; g < G; ++g)
+      for (int j = 0; j < UN; ++j) s[j] = __uint_as_float(raw[j]);
+      const int key0 = tile * UN;
+      if (key0 + UN - 1 > lim) {
 #pragma unroll
-        for (int k = 0; k < UN / 16; ++k) {
-          const uint64_t a = make_desc(p_s + g * P_BYTES + k * 32, 16, 1024);
-          const uint64_t b = make_desc(v_s + stage * KV_BYTES + k * 2048, UN * 128, 1024);
-          mma_f16(tmem + g * TMEM_COLS + O_COL, a, b, idesc_pv, (tile > 0 || k > 0) ? 1u : 0u);
+        for (int j = 0; j < UN; ++j)
+          if (key0 + j > lim) s[j] = -INFINITY;
+      }
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < UN; ++j) m4[j & 3] = fmaxf(m4[j & 3], s[j]);
+      const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * A.scale_log2;
+      bool o_idle = tile == 0;  // O += P V of the previous tile is known to have completed
+      if (__any_sync(0xffffffffu, mx > m_ref + REF_SLACK)) {
+        const float m_new = fmaxf(m_ref, mx);
+        const float corr = m_new == -INFINITY ? 1.f : ex2(m_ref - m_new);
+        m_ref = m_new;
+        l_run *= corr;
+        if (tile > 0) {  // rescale this row of O, once the MMAs that accumulate into it are done
+          if (!bar_wait(&bar_o, (tile - 1) & 1)) ok = false;
+          ok = __all_sync(0xffffffffu, ok);  // the TMEM accesses below are warp-wide
+          if (!ok) break;
+          o_idle = true;
+          asm volatile("tcgen05.fence::after_thread_sync;");
+#pragma unroll
+          for (int c0 = 0; c0 < UD; c0 += 32) {
+            float o[32];
+            tmem_ld32(t_row + O_COL + c0, o);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] *= corr;
+            tmem_st32(t_row + O_COL + c0, o);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
-      mma_commit(&bar_o);
+      }
+      const float nref = m_ref == -INFINITY ? 0.f : -m_ref;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t w[UN / 2];
+#pragma unroll
+      for (int c = 0; c < UN / 8; ++c) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = ex2(fmaf(s[8 * c + 2 * e], A.scale_log2, nref)), p1 = ex2(fmaf(s[8 * c + 2 * e + 1], A.scale_log2, nref));
+          sum4[e] += p0 + p1;
+          w[4 * c + e] = pack16(p0, p1, bf16);
+        }
+      }
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      // P, the stage tile - 1 used and O are free once the previous O += P V has completed
+      if (!o_idle && !bar_wait(&bar_o, (tile - 1) & 1)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (tile + PIPE_STAGES - 1 < n_tiles) load_tile(tile + PIPE_STAGES - 1);  // into the stage tile - 1 used
+      asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < UN / 8; ++c)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_s + grp * P_BYTES + swz(r128, c)), "r"(w[4 * c]), "r"(w[4 * c + 1]),
+                     "r"(w[4 * c + 2]), "r"(w[4 * c + 3]) : "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;");
+      bar_arrive(&bar_p);
     }
-  }
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
-  if (ok && !bar_wait(&bar_o, (n_tiles - 1) & 1)) ok = false;
-  ok = __syncthreads_and(ok);
-  asm volatile("tcgen05.fence::after_thread_sync;");
-  if (ok) {
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    const int64_t base_o = (int64_t)(q0 + tok) * A.o_s0 + (int64_t)hq * A.o_s1;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (ok && !bar_wait(&bar_o, (n_tiles - 1) & 1)) ok = false;
+    ok = __all_sync(0xffffffffu, ok);
+    asm volatile("tcgen05.fence::after_thread_sync;");
+    if (ok) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const int64_t base_o = (int64_t)(q0 + tok) * A.o_s0 + (int64_t)hq * A.o_s1;
 #pragma unroll
-    for (int c0 = 0; c0 < UD; c0 += 32) {
-      float o[32];
-      tmem_ld32(t_row + O_COL + c0, o);
-      if (live) {
+      for (int c0 = 0; c0 < UD; c0 += 32) {
+        float o[32];
+        tmem_ld32(t_row + O_COL + c0, o);
+        if (live) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const float x0 = o[j] * inv, x1 = o[j + 1] * inv;
-          const int d = c0 + j;
-          if (A.out_dtype == ECHOKV_DT_F32) {
-            *reinterpret_cast<float2*>(reinterpret_cast<float*>(A.out) + base_o + d) = make_float2(x0, x1);
-          } else {
-            *reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(A.out) + base_o + d) = pack16(x0, x1, A.out_dtype == ECHOKV_DT_BF16);
+          for (int j = 0; j < 32; j += 2) {
+            const float x0 = o[j] * inv, x1 = o[j + 1] * inv;
+            const int d = c0 + j;
+            if (A.out_dtype == ECHOKV_DT_F32) {
+              *reinterpret_cast<float2*>(reinterpret_cast<float*>(A.out) + base_o + d) = make_float2(x0, x1);
+            } else {
+              *reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(A.out) + base_o + d) = pack16(x0, x1, A.out_dtype == ECHOKV_DT_BF16);
+            }
           }
         }
       }
     }
   }
-  if (!ok && tid == 0 && A.status) atomicExch(A.status, 1);
+  if (!ok && (tid & 31) == 0 && A.status) atomicExch(A.status, 1);
   asm volatile("tcgen05.fence::before_thread_sync;");
   __syncthreads();
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS * G));
@@ -562,9 +593,9 @@ int launch_prefill_umma(const void* q, int64_t q_s0, int64_t q_s1, const void* k
   dim3 grid((max_rows + UM - 1) / UM, H, (unsigned)n_chunks);
   if (pipelined && max_rows > UM) {  // two groups of 128 rows per CTA share the K / V tiles
     grid.x = (max_rows + 2 * UM - 1) / (2 * UM);
-    prefill_umma_pipe_kernel<2><<<grid, 2 * UM, smem_pipe<2>(), st>>>(A);
+    prefill_umma_pipe_kernel<2><<<grid, 2 * UM + 32, smem_pipe<2>(), st>>>(A);
   } else if (pipelined) {
-    prefill_umma_pipe_kernel<1><<<grid, UM, smem_pipe<1>(), st>>>(A);
+    prefill_umma_pipe_kernel<1><<<grid, UM + 32, smem_pipe<1>(), st>>>(A);
   } else {
     prefill_umma_kernel<<<grid, UM, SMEM_BYTES, st>>>(A);
   }
