@@ -79,8 +79,8 @@ _SIGS = {
     "echokv_decode_static": [_LP, _PP, _RP, _P, _I64, _I64, _I32, _P, _P, _I64, _P, _P, _P, _I64, _I64, _I32,
                              _F, _I32, _I32, _I64, _I32, _P],
     "echokv_dequant_dense": [_LP, _PP, _RP, _P, _I64, _P, _I64, _P, _P, _I64, _I64, _I32, _P],
-    "echokv_prefill": [_P, _I64, _I64, _P, _P, _I64, _I64, _I32, _P, _I64, _I32, _P, _I64, _I64, _I32, _F, _I32, _I32,
-                       _I32, _P],
+    "echokv_prefill": [_P, _I64, _I64, _P, _P, _I64, _I64, _I64, _I32, _P, _I64, _I32, _P, _I64, _I64, _I32, _F, _I32,
+                       _I32, _I32, _P],
     "echokv_set_decode_events": [_P, _P],
     "echokv_gather_rows": [_P, _I64, _P, _I64, _P, _I64, _P],
     "echokv_canary_kl": [_P, _I32, _I64, _I64, _I64, _P, _I64, _I64, _I64, _I32, _I32, _I32, _I32, _I32, _I32, _I32,
@@ -93,11 +93,13 @@ for _name, _args in _SIGS.items():
 
 lib.echokv_set_decode_path.argtypes = [C.c_int]
 lib.echokv_set_decode_path.restype = C.c_int
+lib.echokv_kernel_status.argtypes = [C.c_int]
+lib.echokv_kernel_status.restype = C.c_int
 
 if os.environ.get("ECHOKV_B200_DECODE_PATH"):  # experiments: see echokv_set_decode_path
     lib.echokv_set_decode_path(int(os.environ["ECHOKV_B200_DECODE_PATH"], 0))
 
-EXPORTS = sorted(list(_SIGS) + ["echokv_set_decode_path", "echokv_set_prefill_path", "echokv_decode_static_scratch_bytes", "echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
+EXPORTS = sorted(list(_SIGS) + ["echokv_set_decode_path", "echokv_kernel_status", "echokv_set_prefill_path", "echokv_decode_static_scratch_bytes", "echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
                                 "echokv_demote_scratch_bytes"])
 
 

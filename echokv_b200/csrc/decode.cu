@@ -6,6 +6,8 @@ using namespace echokv;
 namespace echokv {
 int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
                       int64_t num_seqs, int max_tier, int* counter, int* status, cudaStream_t st, bool* handled);
+int decode_status_take(bool clear);
+int prefill_status_take(bool clear);
 
 // out[q_rows[seq], head] = splits merged in split order (kernels/decode.py:226-262).  One CTA per
 // (sequence, query head): the log-sum-exp weights of the used splits are computed once into shared
@@ -209,6 +211,12 @@ int echokv_decode_static(const echokv_layout* layout, const echokv_pages* pages,
   return echokv_decode(layout, pages, residual, query, q_s0, q_s1, q_dtype, q_rows, block_table, bt_s0, bt_rows, lens,
                        device_ptr[dev], (int64_t)ECHOKV_STATIC_SCRATCH_BYTES, out, o_s0, o_s1, out_dtype, softmax_scale,
                        num_splits, blocks_per_split, num_seqs, num_q_heads, stream);
+}
+
+int echokv_kernel_status(int clear) {
+  const int d = decode_status_take(clear != 0), p = prefill_status_take(clear != 0);
+  if (d < 0 || p < 0) return set_error(ECHOKV_E_CUDA, "kernel_status: cannot read the status words"), -1;
+  return (d == 1 ? 1 : 0) | (d == 2 ? 2 : 0) | (p ? 4 : 0);
 }
 
 }  // extern "C"

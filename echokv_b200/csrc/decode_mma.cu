@@ -1117,6 +1117,19 @@ __global__ void __launch_bounds__((H + 1) * 32, H == 8 ? 2 : (H == 4 ? 4 : (H ==
 static int g_decode_path = 0;  // 0: pick by shape, 1: always the generic kernel
 static cudaEvent_t g_ev_before = nullptr, g_ev_after = nullptr;  // optional timing hook around the split kernel
 
+// Raised by decode_mma_kernel: 1 = a bounded wait ran out, 2 = a block of a tier wider than the stages.
+__device__ int g_decode_status;
+
+int decode_status_take(bool clear) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)) != cudaSuccess) return -1;  // synchronizes
+  if (v && clear) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int));
+  }
+  return v;
+}
+
 // Chooses the tensor-core kernel when the shape fits; otherwise leaves `handled` false.
 int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
                       int64_t num_seqs, int max_tier, int* counter, int* status, cudaStream_t st, bool* handled) {
@@ -1142,12 +1155,12 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   P.o_km = P.o_ks + H * D * 2;
   P.o_hdr = P.o_km + H * D * 2;
   P.stage_bytes = (P.o_hdr + (int)sizeof(StageHeader) + 127) / 128 * 128;
-  P.status = status;
   P.counter = counter;
   P.q_vec16 = (A.q_dt != ECHOKV_DT_F32) && (reinterpret_cast<uintptr_t>(A.q) % 16 == 0) && A.q_s0 % 8 == 0 && A.q_s1 % 8 == 0;
   P.debug = (g_decode_path >> 4) & 15;
   const int fixed = HDR_BYTES + UNIT * (int)sizeof(TilePlan) + REMAP_BYTES + H * q_head_bytes(A.gqa + 1);
   static int max_smem = -1, num_sms = 0;
+  static int* status_word = nullptr;
   if (max_smem < 0) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1157,8 +1170,10 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
     if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status_word), g_decode_status);
     if (e != cudaSuccess) { max_smem = -1; return set_error(ECHOKV_E_CUDA, "decode: cannot raise shared memory: %s", cudaGetErrorString(e)); }
   }
+  P.status = status ? status : status_word;
   // CTAs per SM: bounded by warps (16 consumer warps per SM is the target) and shared memory
   // (each SM has ~228 KB, 1 KB of it reserved per CTA)
   int per_sm = 16 / H;

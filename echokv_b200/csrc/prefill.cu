@@ -307,11 +307,13 @@ int launch(const PrefillArgs& A, int64_t n_chunks, int max_rows, int H, cudaStre
 
 namespace echokv {
 int launch_prefill_umma(const void* q, int64_t q_s0, int64_t q_s1, const void* k, const void* v, int64_t kv_s0,
-                        int64_t kv_s1, int dtype, const int32_t* chunks, int64_t n_chunks, int max_rows, void* out,
-                        int64_t o_s0, int64_t o_s1, int out_dtype, float scale_log2, int gqa, int H, int head_size,
-                        cudaStream_t st, bool pipelined, bool* handled);
+                        int64_t kv_s1, int64_t total_rows, int dtype, const int32_t* chunks, int64_t n_chunks, int max_rows,
+                        void* out, int64_t o_s0, int64_t o_s1, int out_dtype, float scale_log2, int gqa, int H, int head_size,
+                        cudaStream_t st, int mode, bool* handled);
 }
-static int g_prefill_path = 0;  // 0: pipelined tcgen05 kernel when the shape fits, 1: always the mma.sync kernel, 2: plain tcgen05 kernel
+// 0: pipelined tcgen05 kernel when the shape fits (tiles by tensor-map copies), 1: always the mma.sync kernel,
+// 2: plain tcgen05 kernel, 3: pipelined tcgen05 kernel with the tiles copied by the row threads
+static int g_prefill_path = 0;
 
 extern "C" {
 
@@ -322,8 +324,8 @@ int echokv_set_prefill_path(int path) {
 }
 
 int echokv_prefill(const void* query, int64_t q_s0, int64_t q_s1, const void* k_dense, const void* v_dense,
-                   int64_t kv_s0, int64_t kv_s1, int32_t dtype, const int32_t* chunks, int64_t n_chunks,
-                   int32_t max_chunk_len, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
+                   int64_t kv_s0, int64_t kv_s1, int64_t total_ctx, int32_t dtype, const int32_t* chunks,
+                   int64_t n_chunks, int32_t max_chunk_len, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
                    float softmax_scale, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_size, void* stream) {
   if (n_chunks == 0 || max_chunk_len <= 0) return ECHOKV_OK;
   if (!query || !k_dense || !v_dense || !chunks || !out) return set_error(ECHOKV_E_ARGUMENT, "prefill: null pointer");
@@ -346,9 +348,9 @@ int echokv_prefill(const void* query, int64_t q_s0, int64_t q_s1, const void* k_
   int max_rows = max_chunk_len * A.gqa;
   if (g_prefill_path != 1) {
     bool handled = false;
-    const int rc = launch_prefill_umma(query, q_s0, q_s1, k_dense, v_dense, kv_s0, kv_s1, dtype, chunks, n_chunks, max_rows, out,
-                                       o_s0, o_s1, out_dtype, A.scale_log2, A.gqa, num_kv_heads, head_size, st, g_prefill_path == 0,
-                                       &handled);
+    const int rc = launch_prefill_umma(query, q_s0, q_s1, k_dense, v_dense, kv_s0, kv_s1, total_ctx, dtype, chunks, n_chunks,
+                                       max_rows, out, o_s0, o_s1, out_dtype, A.scale_log2, A.gqa, num_kv_heads, head_size, st,
+                                       g_prefill_path, &handled);
     if (rc || handled) return rc;
   }
   if (dtype == ECHOKV_DT_F16)

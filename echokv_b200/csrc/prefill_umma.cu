@@ -15,6 +15,7 @@
 // K / V tiles are double-buffered with cp.async; completion of the MMAs comes back through
 // tcgen05.commit on an mbarrier.  Every wait is bounded; a wait that gives up ends the CTA's work, frees
 // its TMEM and raises the status word.
+#include <cuda.h>  // CUtensorMap and its enums; the encoder is looked up at run time, nothing links against the driver
 #include "common.cuh"
 
 using namespace echokv;
@@ -336,10 +337,21 @@ __device__ __forceinline__ void bar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-template <int G>
-__global__ void __launch_bounds__(UM * G + 32, 1) prefill_umma_pipe_kernel(Args A) {
+struct alignas(64) Maps {
+  CUtensorMap k, v;  // dense K / V as (channel, head, row) tensors, boxes of 64 channels x 64 rows, 128-byte swizzle
+};
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+
+// TMA = true: one more warp streams the K / V tiles with tensor-map copies (a stage is free once the commit
+// after the O += P V that read it has arrived on its bar_free); TMA = false: the row threads copy them.
+template <int G, bool TMA>
+__global__ void __launch_bounds__(UM * G + (TMA ? 64 : 32), 1) prefill_umma_pipe_kernel(Args A, const __grid_constant__ Maps M) {
   extern __shared__ unsigned char dyn[];
-  __shared__ __align__(8) uint64_t bar_s[2], bar_o, bar_p, bar_kv[PIPE_STAGES];
+  __shared__ __align__(8) uint64_t bar_s[2], bar_o, bar_p, bar_kv[PIPE_STAGES], bar_free[PIPE_STAGES];
   __shared__ uint32_t tmem_slot;
   constexpr int NROW = UM * G;  // row threads
   const uint32_t base = (smem_u32(dyn) + 1023u) & ~1023u;
@@ -353,11 +365,13 @@ __global__ void __launch_bounds__(UM * G + 32, 1) prefill_umma_pipe_kernel(Args 
   const int row0 = blockIdx.x * NROW;
   if (row0 >= rows) return;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const bool issuer_warp = tid >= NROW;
-  const int grp = issuer_warp ? 0 : tid / UM, r128 = tid % UM;  // group of 128 rows, row inside it (= TMEM lane)
+  const bool issuer_warp = tid >= NROW && tid < NROW + 32;
+  const bool producer_warp = tid >= NROW + 32;
+  const bool row_thread = tid < NROW;
+  const int grp = !row_thread ? 0 : tid / UM, r128 = tid % UM;  // group of 128 rows, row inside it (= TMEM lane)
   const bool bf16 = A.is_bf16 != 0;
   const int row = row0 + tid;
-  const bool live = !issuer_warp && row < rows;
+  const bool live = row_thread && row < rows;
   const int tok = live ? row / gqa : 0, hq = live ? h * gqa + row % gqa : 0;
   const int lim = live ? ctx - nq + tok : -1;
   const int last_tok = min(nq - 1, (row0 + NROW - 1) / gqa);
@@ -379,20 +393,26 @@ __global__ void __launch_bounds__(UM * G + 32, 1) prefill_umma_pipe_kernel(Args 
       cp16(v_s + off, vp + src, on);
     }
   };
-  if (!issuer_warp) {
+  if (row_thread) {
 #pragma unroll
     for (int c = 0; c < 16; ++c) cp16(q_s + grp * Q_BYTES + (c >> 3) * (UM * 128) + swz(r128, c & 7), qp + c * 8, live);
-    // tiles 0 .. PIPE_STAGES - 2 in flight, one commit group each (empty groups keep the count regular)
-#pragma unroll
-    for (int t0 = 0; t0 < PIPE_STAGES - 1; ++t0) {
-      if (t0 < n_tiles) load_tile(t0);
+    if constexpr (TMA) {  // Q is visible to the tensor cores after the barrier below
       asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    } else {
+      // tiles 0 .. PIPE_STAGES - 2 in flight, one commit group each (empty groups keep the count regular)
+#pragma unroll
+      for (int t0 = 0; t0 < PIPE_STAGES - 1; ++t0) {
+        if (t0 < n_tiles) load_tile(t0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      }
     }
   }
   if (tid == 0) {
     auto init = [](uint64_t* b, int n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(n)); };
     init(&bar_s[0], 1); init(&bar_s[1], 1); init(&bar_o, 1); init(&bar_p, NROW);
-    for (int i = 0; i < PIPE_STAGES; ++i) init(&bar_kv[i], NROW);
+    for (int i = 0; i < PIPE_STAGES; ++i) { init(&bar_kv[i], TMA ? 1 : NROW); init(&bar_free[i], 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -447,17 +467,39 @@ __global__ void __launch_bounds__(UM * G + 32, 1) prefill_umma_pipe_kernel(Args 
             mma_f16(tmem + g * TMEM_COLS + O_COL, a, b, idesc_pv, (tile > 0 || k > 0) ? 1u : 0u);
           }
         mma_commit(&bar_o);
+        if constexpr (TMA) mma_commit(&bar_free[stage]);
+      }
+    }
+  } else if (producer_warp) {
+    if constexpr (TMA) {
+      if (tid == NROW + 32) {
+        auto load = [&](int tile) {
+          const int stage = tile % PIPE_STAGES;
+          const int z = (int)dense0 + tile * UN;
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&bar_kv[stage])), "r"(2 * KV_BYTES) : "memory");
+#pragma unroll
+          for (int p = 0; p < 2; ++p) {  // the two panels of 64 channels
+            tma_load_3d(k_s + stage * KV_BYTES + p * (UN * 128), &M.k, 64 * p, h, z, &bar_kv[stage]);
+            tma_load_3d(v_s + stage * KV_BYTES + p * (UN * 128), &M.v, 64 * p, h, z, &bar_kv[stage]);
+          }
+        };
+        for (int tile = 0; tile < n_tiles && tile < PIPE_STAGES; ++tile) load(tile);
+        for (int tile = PIPE_STAGES; tile < n_tiles; ++tile) {  // the stage of tile - PIPE_STAGES, once its O += P V is done
+          if (!bar_wait(&bar_free[tile % PIPE_STAGES], ((tile / PIPE_STAGES) - 1) & 1)) { ok = false; break; }
+          load(tile);
+        }
       }
     }
   } else {
     const uint32_t t_row = tmem + ((uint32_t)((warp & 3) * 32) << 16) + grp * TMEM_COLS;  // this warp's lanes, this group's columns
-    // Q and tile 0 have landed
-    asm volatile("cp.async.wait_group %0;" ::"n"(PIPE_STAGES - 2) : "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    bar_arrive(&bar_kv[0]);
+    if constexpr (!TMA) {  // Q and tile 0 have landed
+      asm volatile("cp.async.wait_group %0;" ::"n"(PIPE_STAGES - 2) : "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      bar_arrive(&bar_kv[0]);
+    }
     float m_ref = -INFINITY, l_run = 0.f;
     for (int tile = 0; tile < n_tiles; ++tile) {
-      if (tile + 1 < n_tiles) {  // my copies of tile + 1 have landed (all but the newest copy group are complete)
+      if (!TMA && tile + 1 < n_tiles) {  // my copies of tile + 1 have landed (all but the newest copy group are complete)
         asm volatile("cp.async.wait_group %0;" ::"n"(PIPE_STAGES - 3) : "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         bar_arrive(&bar_kv[(tile + 1) % PIPE_STAGES]);
@@ -522,8 +564,10 @@ __global__ void __launch_bounds__(UM * G + 32, 1) prefill_umma_pipe_kernel(Args 
       if (!o_idle && !bar_wait(&bar_o, (tile - 1) & 1)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (tile + PIPE_STAGES - 1 < n_tiles) load_tile(tile + PIPE_STAGES - 1);  // into the stage tile - 1 used
-      asm volatile("cp.async.commit_group;" ::: "memory");
+      if constexpr (!TMA) {
+        if (tile + PIPE_STAGES - 1 < n_tiles) load_tile(tile + PIPE_STAGES - 1);  // into the stage tile - 1 used
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      }
 #pragma unroll
       for (int c = 0; c < UN / 8; ++c)
         asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_s + grp * P_BYTES + swz(r128, c)), "r"(w[4 * c]), "r"(w[4 * c + 1]),
@@ -568,10 +612,59 @@ __global__ void __launch_bounds__(UM * G + 32, 1) prefill_umma_pipe_kernel(Args 
 
 // Launches the tcgen05 kernel when the shape fits (head size 128, 16-bit inputs); otherwise leaves
 // `handled` false.
+// Raised (1) by a kernel of this file whose bounded wait on an mbarrier ran out; its output is then undefined.
+__device__ int g_prefill_status;
+
+int prefill_status_take(bool clear) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_prefill_status, sizeof(int)) != cudaSuccess) return -1;  // synchronizes
+  if (v && clear) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_prefill_status, &zero, sizeof(int));
+  }
+  return v;
+}
+
+namespace {
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled tensor_map_encoder() {
+  static EncodeTiled fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &res) != cudaSuccess ||
+        res != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiled>(p);
+  }();
+  return fn;
+}
+
+// (channel, head, row) view of a dense [rows, H, 128] tensor; boxes of 64 channels x 1 head x 64 rows land as a
+// 128-byte-swizzled panel.  Rows past `rows` read as zeros.
+bool encode_kv_map(CUtensorMap* map, const void* base, int64_t rows, int H, int64_t s_row, int64_t s_head, bool bf16) {
+  EncodeTiled enc = tensor_map_encoder();
+  if (!enc) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)umma::UD, (cuuint64_t)H, (cuuint64_t)rows};
+  const cuuint64_t strides[2] = {(cuuint64_t)s_head * 2, (cuuint64_t)s_row * 2};
+  const cuuint32_t box[3] = {64, 1, (cuuint32_t)umma::UN};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  return enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims,
+             strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+// mode 0: pipelined, K / V tiles by tensor-map copies when `total_rows` is known and the strides allow it;
+// mode 2: the plain kernel; mode 3: pipelined, tiles copied by the row threads.
 int launch_prefill_umma(const void* q, int64_t q_s0, int64_t q_s1, const void* k, const void* v, int64_t kv_s0,
-                        int64_t kv_s1, int dtype, const int32_t* chunks, int64_t n_chunks, int max_rows, void* out,
-                        int64_t o_s0, int64_t o_s1, int out_dtype, float scale_log2, int gqa, int H, int head_size,
-                        cudaStream_t st, bool pipelined, bool* handled) {
+                        int64_t kv_s1, int64_t total_rows, int dtype, const int32_t* chunks, int64_t n_chunks, int max_rows,
+                        void* out, int64_t o_s0, int64_t o_s1, int out_dtype, float scale_log2, int gqa, int H, int head_size,
+                        cudaStream_t st, int mode, bool* handled) {
   using namespace umma;
   *handled = false;
   if (head_size != UD || (dtype != ECHOKV_DT_F16 && dtype != ECHOKV_DT_BF16)) return ECHOKV_OK;
@@ -579,25 +672,38 @@ int launch_prefill_umma(const void* q, int64_t q_s0, int64_t q_s1, const void* k
   A.q = q; A.k = k; A.v = v; A.out = out; A.chunks = chunks;
   A.q_s0 = q_s0; A.q_s1 = q_s1; A.kv_s0 = kv_s0; A.kv_s1 = kv_s1; A.o_s0 = o_s0; A.o_s1 = o_s1;
   A.gqa = gqa; A.out_dtype = out_dtype; A.is_bf16 = dtype == ECHOKV_DT_BF16; A.scale_log2 = scale_log2;
-  A.status = nullptr;
   static bool configured[64] = {};
+  static int* status_word[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && !configured[dev]) {
+  if (dev >= 64) return ECHOKV_OK;
+  if (!configured[dev]) {
     if (cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
-        cudaFuncSetAttribute(prefill_umma_pipe_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pipe<1>()) != cudaSuccess ||
-        cudaFuncSetAttribute(prefill_umma_pipe_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pipe<2>()) != cudaSuccess)
+        cudaFuncSetAttribute(prefill_umma_pipe_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pipe<1>()) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_umma_pipe_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pipe<2>()) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_umma_pipe_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pipe<1>()) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_umma_pipe_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pipe<2>()) != cudaSuccess ||
+        cudaGetSymbolAddress(reinterpret_cast<void**>(&status_word[dev]), g_prefill_status) != cudaSuccess)
       return check_launch("prefill (tcgen05 kernel)");
     configured[dev] = true;
   }
+  A.status = status_word[dev];
   dim3 grid((max_rows + UM - 1) / UM, H, (unsigned)n_chunks);
-  if (pipelined && max_rows > UM) {  // two groups of 128 rows per CTA share the K / V tiles
-    grid.x = (max_rows + 2 * UM - 1) / (2 * UM);
-    prefill_umma_pipe_kernel<2><<<grid, 2 * UM + 32, smem_pipe<2>(), st>>>(A);
-  } else if (pipelined) {
-    prefill_umma_pipe_kernel<1><<<grid, UM + 32, smem_pipe<1>(), st>>>(A);
-  } else {
+  if (mode == 2) {
     prefill_umma_kernel<<<grid, UM, SMEM_BYTES, st>>>(A);
+  } else {
+    Maps M;
+    memset(&M, 0, sizeof(M));
+    // tensor-map copies: strides in multiples of 16 bytes, rows addressed by a 32-bit coordinate
+    const bool tma = mode == 0 && total_rows > 0 && total_rows < (1ll << 31) && (kv_s0 % 8) == 0 && (kv_s1 % 8) == 0 &&
+                     encode_kv_map(&M.k, k, total_rows, H, kv_s0, kv_s1, A.is_bf16) &&
+                     encode_kv_map(&M.v, v, total_rows, H, kv_s0, kv_s1, A.is_bf16);
+    const bool two = max_rows > UM;  // two groups of 128 rows per CTA share the K / V tiles
+    if (two) grid.x = (max_rows + 2 * UM - 1) / (2 * UM);
+    if (two && tma) prefill_umma_pipe_kernel<2, true><<<grid, 2 * UM + 64, smem_pipe<2>(), st>>>(A, M);
+    else if (two) prefill_umma_pipe_kernel<2, false><<<grid, 2 * UM + 32, smem_pipe<2>(), st>>>(A, M);
+    else if (tma) prefill_umma_pipe_kernel<1, true><<<grid, UM + 64, smem_pipe<1>(), st>>>(A, M);
+    else prefill_umma_pipe_kernel<1, false><<<grid, UM + 32, smem_pipe<1>(), st>>>(A, M);
   }
   const int rc = check_launch("prefill (tcgen05 kernel)");
   if (rc) return rc;

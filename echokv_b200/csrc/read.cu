@@ -90,6 +90,102 @@ dequant_dense_kernel(LayoutDev L, ResidualDev R, const uint8_t* __restrict__ pag
   }
 }
 
+// The same for 16-bit outputs whose rows allow 16-byte stores and blocks of at most 64 tokens: one thread per
+// (token, 8 channels) loads the 8 codes of each side as one word and the K stats as two 16-byte vectors, and
+// stores 16 bytes of K and of V.  The arithmetic is dequant8's: code * scale + min in fp32, two roundings.
+template <typename T> __device__ __forceinline__ uint32_t pack2_rn(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2_rn<__half>(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2_rn<__nv_bfloat16>(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__device__ __forceinline__ void load_codes8(const uint8_t* p, int bits, uint32_t (&q)[8]) {
+  if (bits == 8) {
+    const uint2 w = *reinterpret_cast<const uint2*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { q[i] = (w.x >> (8 * i)) & 0xFFu; q[4 + i] = (w.y >> (8 * i)) & 0xFFu; }
+  } else if (bits == 4) {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = (w >> (4 * i)) & 0xFu;
+  } else {
+    const uint32_t w = *reinterpret_cast<const uint16_t*>(p);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = (w >> (2 * i)) & 0x3u;
+  }
+}
+
+constexpr int DENSE_MAX_BS = 64;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+dequant_dense_vec_kernel(LayoutDev L, ResidualDev R, const uint8_t* __restrict__ pages, const int32_t* __restrict__ work,
+                         const int32_t* __restrict__ bt, int64_t bt_s0, T* __restrict__ k_out, T* __restrict__ v_out,
+                         int64_t o_s0, int64_t o_s1) {
+  __shared__ int64_t s_row[DENSE_MAX_BS];
+  const int4 w = reinterpret_cast<const int4*>(work)[blockIdx.x];
+  const int req = w.x, bi = w.y, ctx = w.w;
+  const int64_t row0 = w.z;
+  const int64_t blk = bt[(int64_t)req * bt_s0 + bi];
+  const int nvalid = min(L.BS, ctx - bi * L.BS);
+  const uint8_t* page = pages + blk * L.PS;
+  int bits = page[0];
+  if (bits == 0) bits = 2;  // an unopened block reads as INT2, like the attention kernels
+  if ((int)threadIdx.x < nvalid) s_row[threadIdx.x] = row_offset(pages, L, blk, threadIdx.x, bits);
+  const int64_t slot = R.block_res[blk];
+  const int open_grp = slot >= 0 ? (int)R.res_group[slot] : -1;
+  __syncthreads();
+  const int cpt = (L.H * L.D) / 8, cph = L.D / 8;
+  const int side_bytes = (L.H * L.D * bits) / 8;
+  const __half* vs_p = reinterpret_cast<const __half*>(page + L.o_vs);
+  const __half* vm_p = reinterpret_cast<const __half*>(page + L.o_vm);
+#pragma unroll 4
+  for (int idx = threadIdx.x; idx < nvalid * cpt; idx += 256) {
+    const int t = idx / cpt, c = idx - t * cpt;
+    const int h = c / cph, d0 = (c - h * cph) * 8;
+    const uint8_t* krow = pages + s_row[t] + (c * bits);  // 8 channels * bits / 8 bytes per chunk of 8
+    uint32_t qk[8], qv[8];
+    load_codes8(krow + side_bytes, bits, qv);
+    const int64_t ve = ((int64_t)t * L.H + h) * L.NG + d0 / L.VG;
+    const float vs = __half2float(vs_p[ve]), vm = __half2float(vm_p[ve]);
+    const int grp = t / L.KG;
+    float k[8];
+    if (grp == open_grp) {
+      const int64_t o = slot * R.s_slot + (int64_t)(t - grp * L.KG) * R.s_pos + h * R.s_head + d0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) k[i] = ld_dt(R.base, R.dtype, o + i);
+    } else {
+      load_codes8(krow, bits, qk);
+      const int64_t ke = ((int64_t)grp * L.H + h) * L.D + d0;
+      const uint4 s8 = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(page + L.o_ks) + ke);
+      const uint4 m8 = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(page + L.o_km) + ke);
+      const __half2* sh = reinterpret_cast<const __half2*>(&s8);
+      const __half2* mh = reinterpret_cast<const __half2*>(&m8);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 sc = __half22float2(sh[i]), mn = __half22float2(mh[i]);
+        k[2 * i] = __fadd_rn(__fmul_rn((float)qk[2 * i], sc.x), mn.x);
+        k[2 * i + 1] = __fadd_rn(__fmul_rn((float)qk[2 * i + 1], sc.y), mn.y);
+      }
+    }
+    uint4 ko, vo;
+    uint32_t* kw = reinterpret_cast<uint32_t*>(&ko);
+    uint32_t* vw = reinterpret_cast<uint32_t*>(&vo);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      kw[i] = pack2_rn<T>(k[2 * i], k[2 * i + 1]);
+      vw[i] = pack2_rn<T>(__fadd_rn(__fmul_rn((float)qv[2 * i], vs), vm), __fadd_rn(__fmul_rn((float)qv[2 * i + 1], vs), vm));
+    }
+    const int64_t o = (row0 + t) * o_s0 + h * o_s1 + d0;
+    *reinterpret_cast<uint4*>(k_out + o) = ko;
+    *reinterpret_cast<uint4*>(v_out + o) = vo;
+  }
+}
+
 // Demotion, phase 2: requantize a block's dequantized contents (scratch: K then V, float
 // [n, BS, H, D]) to INT2 into chunk 0 of its own page (tiered_cache.py:322-340).
 __global__ void __launch_bounds__(256)
@@ -204,6 +300,19 @@ int echokv_dequant_dense(const echokv_layout* layout, const echokv_pages* pages,
 #define LAUNCH(T)                                                                                              \
   dequant_dense_kernel<T><<<(unsigned)n_work, 256, 0, st>>>(L, R, (const uint8_t*)pages->base, work, block_table, \
                                                            bt_s0, (T*)k_out, (T*)v_out, out_s0, out_s1)
+  // 16-byte loads and stores need the stat arrays, the rows of the outputs and 8-channel chunks aligned
+  const bool vec = out_dtype != ECHOKV_DT_F32 && L.BS <= DENSE_MAX_BS && L.D % 8 == 0 && L.VG % 8 == 0 &&
+                   ((L.o_ks | L.o_km | L.PS | L.o_data | L.CB) % 16) == 0 && (out_s0 % 8) == 0 && (out_s1 % 8) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(k_out) | reinterpret_cast<uintptr_t>(v_out) |
+                     reinterpret_cast<uintptr_t>(pages->base) | reinterpret_cast<uintptr_t>(work)) % 16) == 0;
+#define LAUNCH_VEC(T)                                                                                              \
+  dequant_dense_vec_kernel<T><<<(unsigned)n_work, 256, 0, st>>>(L, R, (const uint8_t*)pages->base, work, block_table, \
+                                                               bt_s0, (T*)k_out, (T*)v_out, out_s0, out_s1)
+  if (vec) {
+    if (out_dtype == ECHOKV_DT_F16) LAUNCH_VEC(__half); else LAUNCH_VEC(__nv_bfloat16);
+    return check_launch("dequant_dense");
+  }
+#undef LAUNCH_VEC
   switch (out_dtype) {
     case ECHOKV_DT_F32: LAUNCH(float); break;
     case ECHOKV_DT_F16: LAUNCH(__half); break;

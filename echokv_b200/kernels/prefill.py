@@ -88,7 +88,7 @@ def dense_attention(query: torch.Tensor, k: torch.Tensor, v: torch.Tensor, chunk
         raise ValueError("the head dimension must be contiguous")
     N.check(N.lib.echokv_prefill(
         query.data_ptr(), query.stride(0), query.stride(1), k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1),
-        N.dtype_code(query.dtype), chunks.data_ptr(), chunks.shape[0], max_chunk, out.data_ptr(), out.stride(0),
+        k.shape[0], N.dtype_code(query.dtype), chunks.data_ptr(), chunks.shape[0], max_chunk, out.data_ptr(), out.stride(0),
         out.stride(1), N.dtype_code(out.dtype), softmax_scale, query.shape[1], k.shape[1], query.shape[2],
         N.stream_ptr(query.device)))
 

@@ -207,10 +207,13 @@ int echokv_dequant_dense(const echokv_layout* layout, const echokv_pages* pages,
  * there, :145-153; oracle :210-236).  k_dense / v_dense [total_ctx, H, D] are what
  * echokv_dequant_dense wrote, in the query's dtype (float16 or bfloat16).  `chunks` int32
  * [n_chunks, 4] (16-byte aligned): q_start, q_end, ctx, dense row of the context's first key.
- * Query i of a chunk of nq sees keys 0 .. ctx - nq + i.  query/out [T, Hq, D]; head_size 64 or 128. */
+ * Query i of a chunk of nq sees keys 0 .. ctx - nq + i.  query/out [T, Hq, D]; head_size 64 or 128.
+ * `total_ctx` is the number of rows of k_dense / v_dense; every one of them must hold finite values
+ * (key tiles are fetched whole, rows past a context's end are masked, not skipped).  0 = unknown:
+ * the kernels then never touch a row outside the chunks' contexts. */
 int echokv_prefill(const void* query, int64_t q_s0, int64_t q_s1, const void* k_dense, const void* v_dense,
-                   int64_t kv_s0, int64_t kv_s1, int32_t dtype, const int32_t* chunks, int64_t n_chunks,
-                   int32_t max_chunk_len, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
+                   int64_t kv_s0, int64_t kv_s1, int64_t total_ctx, int32_t dtype, const int32_t* chunks,
+                   int64_t n_chunks, int32_t max_chunk_len, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
                    float softmax_scale, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_size, void* stream);
 
 /* dst row i = src row rows[i] for n rows of row_bytes bytes (rows 16-byte aligned, a multiple of 16
@@ -221,9 +224,19 @@ int echokv_gather_rows(const void* src, int64_t src_row_stride_bytes, const int6
 
 /* Kernel selection of echokv_prefill: 0 (default) takes the tcgen05 / TMEM kernel when the shape fits
  * (head size 128) and the mma.sync kernel otherwise; 1 always takes the mma.sync kernel; 2 takes the
- * tcgen05 kernel without the overlap of tensor work and softmax (two CTAs per SM).  Returns the
- * previous setting.  No counterpart in the reference (it calls a flash-attention library there). */
+ * tcgen05 kernel without the overlap of tensor work and softmax (two CTAs per SM); 3 takes the
+ * overlapped tcgen05 kernel with the key / value tiles copied by its row threads instead of tensor-map
+ * copies (what 0 does when total_ctx is unknown).  Returns the previous setting.  No counterpart in the
+ * reference (it calls a flash-attention library there). */
 int echokv_set_prefill_path(int path);
+
+/* Every wait inside the kernels (on an mbarrier or a lock) gives up after a fixed number of polls and
+ * raises a status word on the device instead of hanging; the output of that launch is then undefined.
+ * Synchronizes the device and returns the words of the current device: bit 0 = a wait of the decode
+ * kernel ran out, bit 1 = the decode kernel met a block tier it was not built for, bit 2 = a wait of
+ * the prefill kernel ran out; negative on a CUDA error.  `clear` != 0 resets them.  No counterpart in
+ * the reference. */
+int echokv_kernel_status(int clear);
 
 /* Canary attention-KL estimator, batched over layers -- canary_kl (canary.py:59-89).
  * query [L, nq, Hq, D] of q_dtype, kref float32 [L, W, H, D] oldest key first (ring

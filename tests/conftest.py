@@ -25,3 +25,13 @@ def load_golden(name: str) -> dict:
 @pytest.fixture(scope="session")
 def golden():
     return load_golden
+
+
+@pytest.fixture(autouse=True)
+def _kernel_status_stays_clear(request):
+    """After every GPU test: no kernel gave up on a bounded wait (the status words of the library are 0)."""
+    yield
+    if request.node.get_closest_marker("gpu") is None:
+        return
+    from echokv_b200 import _native as N
+    assert N.lib.echokv_kernel_status(1) == 0

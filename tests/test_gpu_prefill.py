@@ -34,7 +34,7 @@ CASES = [
 ]
 
 
-@pytest.mark.parametrize("kernel", ["tcgen05", "mma_sync", "tcgen05_plain"])
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma_sync", "tcgen05_plain", "tcgen05_row_copies"])
 @pytest.mark.parametrize("sc", CASES, ids=lambda s: s.name)
 def test_dense_path_matches_oracle_and_row_path(sc, kernel):
     """Both attention kernels of the dense path (head size 128 takes the tcgen05 kernel unless told otherwise)."""
@@ -42,7 +42,7 @@ def test_dense_path_matches_oracle_and_row_path(sc, kernel):
     from echokv_b200 import _native as N
     from echokv_b200.kernels.prefill import build_dense, build_rows, prefill_attention
 
-    old = N.lib.echokv_set_prefill_path({"tcgen05": 0, "mma_sync": 1, "tcgen05_plain": 2}[kernel])
+    old = N.lib.echokv_set_prefill_path({"tcgen05": 0, "mma_sync": 1, "tcgen05_plain": 2, "tcgen05_row_copies": 3}[kernel])
     try:
         _dense_case(sc)
     finally:
@@ -73,7 +73,7 @@ def _dense_case(sc):
     assert np.abs(same.float().cpu().numpy()[live] - got[live]).max() <= 2e-2
 
 
-@pytest.mark.parametrize("sc", CASES[:2], ids=lambda s: s.name)
+@pytest.mark.parametrize("sc", CASES, ids=lambda s: s.name)
 def test_dense_dequant_equals_gather(sc):
     """kernels/prefill.py:90-115 against tiered_cache.py:451-478: the same values, token by token."""
     import torch
