@@ -69,6 +69,11 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a, uint64_t b,
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// A operand in tensor memory (row i of A = lane i, two 16-bit elements of K per 32-bit column)
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -109,6 +114,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
                  "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
                  "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
                  "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st32_raw(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+                 "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]),
+                 "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
+                 "r"(v[30]), "r"(v[31])
                : "memory");
 }
 __device__ __forceinline__ float ex2(float x) {
@@ -331,6 +344,7 @@ __global__ void __launch_bounds__(UM, 2) prefill_umma_kernel(Args A) {
 // So the scores of t + 1 and O += P V of t run on the tensor cores under the softmax of t and t + 1.
 constexpr int PIPE_STAGES = 4;
 constexpr int S1_COL = 192;
+constexpr bool P_IN_TMEM = true;  // P of a tile overwrites the first 32 columns of its scores and is the A operand from there
 template <int G> constexpr int smem_pipe() { return G * (Q_BYTES + P_BYTES) + 2 * PIPE_STAGES * KV_BYTES + 1024; }
 
 __device__ __forceinline__ void bar_arrive(uint64_t* bar) {
@@ -462,9 +476,14 @@ __global__ void __launch_bounds__(UM * G + (TMA ? 64 : 32), 1) prefill_umma_pipe
         for (int g = 0; g < G; ++g)
 #pragma unroll
           for (int k = 0; k < UN / 16; ++k) {
-            const uint64_t a = make_desc(p_s + g * P_BYTES + k * 32, 16, 1024);
             const uint64_t b = make_desc(v_s + stage * KV_BYTES + k * 2048, UN * 128, 1024);
-            mma_f16(tmem + g * TMEM_COLS + O_COL, a, b, idesc_pv, (tile > 0 || k > 0) ? 1u : 0u);
+            if constexpr (P_IN_TMEM) {  // 16 keys = 8 columns of P
+              mma_f16_ts(tmem + g * TMEM_COLS + O_COL, tmem + g * TMEM_COLS + ((tile & 1) ? S1_COL : 0) + k * 8, b, idesc_pv,
+                         (tile > 0 || k > 0) ? 1u : 0u);
+            } else {
+              const uint64_t a = make_desc(p_s + g * P_BYTES + k * 32, 16, 1024);
+              mma_f16(tmem + g * TMEM_COLS + O_COL, a, b, idesc_pv, (tile > 0 || k > 0) ? 1u : 0u);
+            }
           }
         mma_commit(&bar_o);
         if constexpr (TMA) mma_commit(&bar_free[stage]);
@@ -560,19 +579,28 @@ __global__ void __launch_bounds__(UM * G + (TMA ? 64 : 32), 1) prefill_umma_pipe
         }
       }
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      // P, the stage tile - 1 used and O are free once the previous O += P V has completed
-      if (!o_idle && !bar_wait(&bar_o, (tile - 1) & 1)) ok = false;
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      // The P buffer in shared memory and the stage tile - 1 used are free once the previous O += P V has
+      // completed.  P in tensor memory needs no wait: it goes where this tile's scores were, and the scores of
+      // tile + 1 that will overwrite it are issued after the O += P V that reads it.
+      if constexpr (!(P_IN_TMEM && TMA)) {
+        if (!o_idle && !bar_wait(&bar_o, (tile - 1) & 1)) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
       if constexpr (!TMA) {
         if (tile + PIPE_STAGES - 1 < n_tiles) load_tile(tile + PIPE_STAGES - 1);  // into the stage tile - 1 used
         asm volatile("cp.async.commit_group;" ::: "memory");
       }
+      if constexpr (P_IN_TMEM) {
+        tmem_st32_raw(t_row + s_col, w);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      } else {
 #pragma unroll
-      for (int c = 0; c < UN / 8; ++c)
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_s + grp * P_BYTES + swz(r128, c)), "r"(w[4 * c]), "r"(w[4 * c + 1]),
-                     "r"(w[4 * c + 2]), "r"(w[4 * c + 3]) : "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (int c = 0; c < UN / 8; ++c)
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_s + grp * P_BYTES + swz(r128, c)), "r"(w[4 * c]), "r"(w[4 * c + 1]),
+                       "r"(w[4 * c + 2]), "r"(w[4 * c + 3]) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
       asm volatile("tcgen05.fence::before_thread_sync;");
       bar_arrive(&bar_p);
     }
