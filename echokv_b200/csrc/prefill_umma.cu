@@ -342,10 +342,10 @@ __global__ void __launch_bounds__(UM, 2) prefill_umma_kernel(Args A) {
 //   issuer        waits bar_kv of t + 1 and issues its scores into the other score buffer, waits bar_p and
 //                 issues O += P V of t.
 // So the scores of t + 1 and O += P V of t run on the tensor cores under the softmax of t and t + 1.
-constexpr int PIPE_STAGES = 4;
-constexpr int S1_COL = 192;
 constexpr bool P_IN_TMEM = true;  // P of a tile overwrites the first 32 columns of its scores and is the A operand from there
-template <int G> constexpr int smem_pipe() { return G * (Q_BYTES + P_BYTES) + 2 * PIPE_STAGES * KV_BYTES + 1024; }
+constexpr int PIPE_STAGES = P_IN_TMEM ? 5 : 4;  // what fits beside Q for two groups (and P, when it is staged in shared memory)
+constexpr int S1_COL = 192;
+template <int G> constexpr int smem_pipe() { return G * (Q_BYTES + (P_IN_TMEM ? 0 : P_BYTES)) + 2 * PIPE_STAGES * KV_BYTES + 1024; }
 
 __device__ __forceinline__ void bar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -539,10 +539,14 @@ __global__ void __launch_bounds__(UM * G + (TMA ? 64 : 32), 1) prefill_umma_pipe
         for (int j = 0; j < UN; ++j)
           if (key0 + j > lim) s[j] = -INFINITY;
       }
-      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      float m16[16];  // a tree: 16 independent chains of 3, then 4 levels
 #pragma unroll
-      for (int j = 0; j < UN; ++j) m4[j & 3] = fmaxf(m4[j & 3], s[j]);
-      const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * A.scale_log2;
+      for (int j = 0; j < 16; ++j) m16[j] = fmaxf(fmaxf(s[j], s[j + 16]), fmaxf(s[j + 32], s[j + 48]));
+#pragma unroll
+      for (int w = 8; w >= 1; w >>= 1)
+#pragma unroll
+        for (int j = 0; j < w; ++j) m16[j] = fmaxf(m16[j], m16[j + w]);
+      const float mx = m16[0] * A.scale_log2;
       bool o_idle = tile == 0;  // O += P V of the previous tile is known to have completed
       if (__any_sync(0xffffffffu, mx > m_ref + REF_SLACK)) {
         const float m_new = fmaxf(m_ref, mx);
