@@ -640,6 +640,243 @@ __global__ void __launch_bounds__(UM * G + (TMA ? 64 : 32), 1) prefill_umma_pipe
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS * G));
 }
 
+// 128-key tiles, two groups of 128 rows that alternate.  Each group owns 256 TMEM columns: its scores S (128
+// columns, fp32) and its O (128 columns).  P of a tile overwrites the first 64 columns of S and is the A operand
+// of O += P V from there, so a group's next scores can only be issued after that MMA: while one group takes its
+// softmax, the tensor cores run the other group's O += P V and next Q K^T.  K and V tiles travel in separate
+// two-stage rings (a K stage is free as soon as both groups' scores of its tile are issued and done, long
+// before the V stage of the same tile).  M 128 x N 128 score MMAs read 8 KB of shared memory per 64-cycle
+// instruction, inside what shared memory delivers; the N 64 ones of the kernel above need 6 KB per 32 cycles.
+constexpr int WN = 128;                    // keys per tile
+constexpr int WKV_BYTES = WN * UD * 2;     // one K or V tile: two panels of 128 rows x 128 bytes
+constexpr int W_STAGES = 2;
+constexpr int W_SCOL = 0, W_OCOL = 128, W_GCOLS = 256;
+constexpr int smem_wide() { return 2 * Q_BYTES + 2 * W_STAGES * WKV_BYTES + 1024; }
+
+__device__ __forceinline__ void tmem_st16_raw(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+                 "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16_raw(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                 "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(2 * UM + 64, 1) prefill_umma_wide_kernel(Args A, const __grid_constant__ Maps M) {
+  extern __shared__ unsigned char dyn[];
+  __shared__ __align__(8) uint64_t bar_s[2], bar_p[2], bar_o[2], bar_k[W_STAGES], bar_v[W_STAGES], bar_kfree[W_STAGES],
+      bar_vfree[W_STAGES];
+  __shared__ uint32_t tmem_slot;
+  constexpr int NROW = 2 * UM;
+  const uint32_t base = (smem_u32(dyn) + 1023u) & ~1023u;
+  const uint32_t q_s = base, k_s = q_s + 2 * Q_BYTES, v_s = k_s + W_STAGES * WKV_BYTES;
+
+  const int4 ck = reinterpret_cast<const int4*>(A.chunks)[blockIdx.z];
+  const int q0 = ck.x, nq = ck.y - ck.x, ctx = ck.z;
+  const int dense0 = ck.w;
+  const int gqa = A.gqa, h = blockIdx.y;
+  const int rows = nq * gqa;
+  const int row0 = blockIdx.x * NROW;
+  if (row0 >= rows) return;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const bool row_thread = tid < NROW;
+  const int grp = row_thread ? tid / UM : 0, r128 = tid % UM;
+  const bool bf16 = A.is_bf16 != 0;
+  const int row = row0 + tid;
+  const bool live = row_thread && row < rows;
+  const int tok = live ? row / gqa : 0, hq = live ? h * gqa + row % gqa : 0;
+  const int lim = live ? ctx - nq + tok : -1;
+  const int last_tok = min(nq - 1, (row0 + NROW - 1) / gqa);
+  const int n_keys = min(ctx, ctx - nq + last_tok + 1);
+  const int n_tiles = (n_keys + WN - 1) / WN;
+
+  if (row_thread) {
+    const uint16_t* qp = reinterpret_cast<const uint16_t*>(A.q) + (int64_t)(q0 + tok) * A.q_s0 + (int64_t)hq * A.q_s1;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) cp16(q_s + grp * Q_BYTES + (c >> 3) * (UM * 128) + swz(r128, c & 7), qp + c * 8, live);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (tid == 0) {
+    auto init = [](uint64_t* b, int n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(n)); };
+    for (int g = 0; g < 2; ++g) { init(&bar_s[g], 1); init(&bar_p[g], UM); init(&bar_o[g], 1); }
+    for (int i = 0; i < W_STAGES; ++i) { init(&bar_k[i], 1); init(&bar_v[i], 1); init(&bar_kfree[i], 1); init(&bar_vfree[i], 1); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(2 * W_GCOLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;");
+  const uint32_t tmem = tmem_slot;
+  const uint32_t fmt = bf16 ? 1u : 0u;
+  const uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(WN >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
+  const uint32_t idesc_pv = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(UD >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
+  bool ok = true;
+
+  if (tid == NROW) {  // the MMA issuer
+    auto issue_qk = [&](int g, int tile) {  // S_g = Q_g K_tile^T
+      const uint32_t kb = k_s + (tile % W_STAGES) * WKV_BYTES;
+#pragma unroll
+      for (int k = 0; k < UD / 16; ++k) {
+        const uint64_t a = make_desc(q_s + g * Q_BYTES + (k >> 2) * (UM * 128) + (k & 3) * 32, 16, 1024);
+        const uint64_t b = make_desc(kb + (k >> 2) * (WN * 128) + (k & 3) * 32, 16, 1024);
+        mma_f16(tmem + g * W_GCOLS + W_SCOL, a, b, idesc_qk, k > 0);
+      }
+      mma_commit(&bar_s[g]);
+    };
+    if (bar_wait(&bar_k[0], 0)) {
+      asm volatile("tcgen05.fence::after_thread_sync;");
+      issue_qk(0, 0);
+      issue_qk(1, 0);
+      mma_commit(&bar_kfree[0]);
+    } else {
+      ok = false;
+    }
+    for (int tile = 0; tile < n_tiles && ok; ++tile) {
+      const int stage = tile % W_STAGES, nstage = (tile + 1) % W_STAGES;
+      const bool more = tile + 1 < n_tiles;
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        if (!bar_wait(&bar_p[g], tile & 1)) { ok = false; break; }  // the group's P is in tensor memory
+        if (g == 0 && !bar_wait(&bar_v[stage], (tile / W_STAGES) & 1)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;");
+#pragma unroll
+        for (int k = 0; k < WN / 16; ++k) {  // 16 keys = 8 columns of P; V as it lies in memory (MN-major B)
+          const uint64_t b = make_desc(v_s + stage * WKV_BYTES + k * 2048, WN * 128, 1024);
+          mma_f16_ts(tmem + g * W_GCOLS + W_OCOL, tmem + g * W_GCOLS + W_SCOL + k * 8, b, idesc_pv, (tile > 0 || k > 0) ? 1u : 0u);
+        }
+        mma_commit(&bar_o[g]);
+        if (g == 1) mma_commit(&bar_vfree[stage]);
+        if (more) {  // the group's next scores go over its P, after the MMA that reads it
+          if (g == 0 && !bar_wait(&bar_k[nstage], ((tile + 1) / W_STAGES) & 1)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;");
+          issue_qk(g, tile + 1);
+          if (g == 1) mma_commit(&bar_kfree[nstage]);
+        }
+      }
+    }
+  } else if (tid == NROW + 32) {  // the tile producer
+    auto load = [&](const CUtensorMap* map, uint32_t dst, uint64_t* bar, int tile) {
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(WKV_BYTES) : "memory");
+      tma_load_3d(dst, map, 0, h, dense0 + tile * WN, bar);
+      tma_load_3d(dst + WN * 128, map, 64, h, dense0 + tile * WN, bar);
+    };
+    for (int tile = 0; tile < n_tiles; ++tile) {
+      const int stage = tile % W_STAGES;
+      const uint32_t par = ((tile / W_STAGES) - 1) & 1;
+      if (tile >= W_STAGES && !bar_wait(&bar_kfree[stage], par)) { ok = false; break; }
+      load(&M.k, k_s + stage * WKV_BYTES, &bar_k[stage], tile);
+      if (tile >= W_STAGES && !bar_wait(&bar_vfree[stage], par)) { ok = false; break; }
+      load(&M.v, v_s + stage * WKV_BYTES, &bar_v[stage], tile);
+    }
+  } else if (row_thread) {
+    const uint32_t t_row = tmem + ((uint32_t)((warp & 3) * 32) << 16) + grp * W_GCOLS;  // this warp's lanes, this group's columns
+    float m_ref = -INFINITY, l_run = 0.f;
+    for (int tile = 0; tile < n_tiles; ++tile) {
+      if (!__all_sync(0xffffffffu, bar_wait(&bar_s[grp], tile & 1))) { ok = false; break; }  // the scores of this tile
+      asm volatile("tcgen05.fence::after_thread_sync;");
+      uint32_t raw[WN];
+#pragma unroll
+      for (int c = 0; c < WN / 32; ++c) tmem_ld32_nowait(t_row + W_SCOL + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&raw[32 * c]));
+      tmem_ld_wait();
+      const int key0 = tile * WN;
+      if (key0 + WN - 1 > lim) {  // bottom-right causal mask, and the keys past the context
+#pragma unroll
+        for (int j = 0; j < WN; ++j)
+          if (key0 + j > lim) raw[j] = 0xff800000u;  // -inf
+      }
+      float m16[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float a = fmaxf(fmaxf(__uint_as_float(raw[j]), __uint_as_float(raw[j + 16])), fmaxf(__uint_as_float(raw[j + 32]), __uint_as_float(raw[j + 48])));
+        const float b = fmaxf(fmaxf(__uint_as_float(raw[j + 64]), __uint_as_float(raw[j + 80])), fmaxf(__uint_as_float(raw[j + 96]), __uint_as_float(raw[j + 112])));
+        m16[j] = fmaxf(a, b);
+      }
+#pragma unroll
+      for (int w = 8; w >= 1; w >>= 1)
+#pragma unroll
+        for (int j = 0; j < w; ++j) m16[j] = fmaxf(m16[j], m16[j + w]);
+      const float mx = m16[0] * A.scale_log2;
+      // the reference only moves when some row of the warp outgrows it by more than REF_SLACK
+      if (__any_sync(0xffffffffu, mx > m_ref + REF_SLACK)) {
+        const float m_new = fmaxf(m_ref, mx);
+        const float corr = m_new == -INFINITY ? 1.f : ex2(m_ref - m_new);
+        m_ref = m_new;
+        l_run *= corr;
+        if (tile > 0) {  // rescale this row of O, once the MMAs that accumulate into it are done
+          if (!__all_sync(0xffffffffu, bar_wait(&bar_o[grp], (tile - 1) & 1))) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;");
+#pragma unroll 1
+          for (int c0 = 0; c0 < UD; c0 += 16) {  // 16 columns at a time: the tile's scores stay in registers
+            uint32_t o[16];
+            tmem_ld16_raw(t_row + W_OCOL + c0, o);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+            tmem_st16_raw(t_row + W_OCOL + c0, o);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+      const float nref = m_ref == -INFINITY ? 0.f : -m_ref;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < WN / 32; ++c) {  // 32 keys -> 16 columns of P, over scores already in registers
+        uint32_t w[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float p0 = ex2(fmaf(__uint_as_float(raw[32 * c + 2 * e]), A.scale_log2, nref));
+          const float p1 = ex2(fmaf(__uint_as_float(raw[32 * c + 2 * e + 1]), A.scale_log2, nref));
+          sum4[e & 3] += p0 + p1;
+          w[e] = pack16(p0, p1, bf16);
+        }
+        tmem_st16_raw(t_row + W_SCOL + 16 * c, w);
+      }
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;");
+      bar_arrive(&bar_p[grp]);
+    }
+    if (ok && !bar_wait(&bar_o[grp], (n_tiles - 1) & 1)) ok = false;
+    ok = __all_sync(0xffffffffu, ok);
+    asm volatile("tcgen05.fence::after_thread_sync;");
+    if (ok) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const int64_t base_o = (int64_t)(q0 + tok) * A.o_s0 + (int64_t)hq * A.o_s1;
+#pragma unroll
+      for (int c0 = 0; c0 < UD; c0 += 32) {
+        float o[32];
+        tmem_ld32(t_row + W_OCOL + c0, o);
+        if (live) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float x0 = o[j] * inv, x1 = o[j + 1] * inv;
+            const int d = c0 + j;
+            if (A.out_dtype == ECHOKV_DT_F32) {
+              *reinterpret_cast<float2*>(reinterpret_cast<float*>(A.out) + base_o + d) = make_float2(x0, x1);
+            } else {
+              *reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(A.out) + base_o + d) = pack16(x0, x1, A.out_dtype == ECHOKV_DT_BF16);
+            }
+          }
+        }
+      }
+    }
+  }
+  if (!ok && (tid & 31) == 0 && A.status) atomicExch(A.status, 1);
+  asm volatile("tcgen05.fence::before_thread_sync;");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * W_GCOLS));
+}
+
 }  // namespace umma
 
 // Launches the tcgen05 kernel when the shape fits (head size 128, 16-bit inputs); otherwise leaves
@@ -675,14 +912,14 @@ EncodeTiled tensor_map_encoder() {
   return fn;
 }
 
-// (channel, head, row) view of a dense [rows, H, 128] tensor; boxes of 64 channels x 1 head x 64 rows land as a
-// 128-byte-swizzled panel.  Rows past `rows` read as zeros.
-bool encode_kv_map(CUtensorMap* map, const void* base, int64_t rows, int H, int64_t s_row, int64_t s_head, bool bf16) {
+// (channel, head, row) view of a dense [rows, H, 128] tensor; boxes of 64 channels x 1 head x `box_rows` rows land
+// as a 128-byte-swizzled panel.  Rows past `rows` read as zeros.
+bool encode_kv_map(CUtensorMap* map, const void* base, int64_t rows, int H, int64_t s_row, int64_t s_head, bool bf16, int box_rows) {
   EncodeTiled enc = tensor_map_encoder();
   if (!enc) return false;
   const cuuint64_t dims[3] = {(cuuint64_t)umma::UD, (cuuint64_t)H, (cuuint64_t)rows};
   const cuuint64_t strides[2] = {(cuuint64_t)s_head * 2, (cuuint64_t)s_row * 2};
-  const cuuint32_t box[3] = {64, 1, (cuuint32_t)umma::UN};
+  const cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
   const cuuint32_t elem[3] = {1, 1, 1};
   return enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims,
              strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -691,8 +928,9 @@ bool encode_kv_map(CUtensorMap* map, const void* base, int64_t rows, int H, int6
 
 }  // namespace
 
-// mode 0: pipelined, K / V tiles by tensor-map copies when `total_rows` is known and the strides allow it;
-// mode 2: the plain kernel; mode 3: pipelined, tiles copied by the row threads.
+// mode 0: pipelined; K / V tiles by tensor-map copies when `total_rows` is known and the strides allow it, and then
+// 128-key tiles for chunks of more than 128 rows; mode 4: the same with 64-key tiles throughout; mode 2: the plain
+// kernel; mode 3: pipelined, 64-key tiles copied by the row threads.
 int launch_prefill_umma(const void* q, int64_t q_s0, int64_t q_s1, const void* k, const void* v, int64_t kv_s0,
                         int64_t kv_s1, int64_t total_rows, int dtype, const int32_t* chunks, int64_t n_chunks, int max_rows,
                         void* out, int64_t o_s0, int64_t o_s1, int out_dtype, float scale_log2, int gqa, int H, int head_size,
@@ -715,6 +953,7 @@ int launch_prefill_umma(const void* q, int64_t q_s0, int64_t q_s1, const void* k
         cudaFuncSetAttribute(prefill_umma_pipe_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pipe<2>()) != cudaSuccess ||
         cudaFuncSetAttribute(prefill_umma_pipe_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pipe<1>()) != cudaSuccess ||
         cudaFuncSetAttribute(prefill_umma_pipe_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pipe<2>()) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_umma_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_wide()) != cudaSuccess ||
         cudaGetSymbolAddress(reinterpret_cast<void**>(&status_word[dev]), g_prefill_status) != cudaSuccess)
       return check_launch("prefill (tcgen05 kernel)");
     configured[dev] = true;
@@ -727,12 +966,15 @@ int launch_prefill_umma(const void* q, int64_t q_s0, int64_t q_s1, const void* k
     Maps M;
     memset(&M, 0, sizeof(M));
     // tensor-map copies: strides in multiples of 16 bytes, rows addressed by a 32-bit coordinate
-    const bool tma = mode == 0 && total_rows > 0 && total_rows < (1ll << 31) && (kv_s0 % 8) == 0 && (kv_s1 % 8) == 0 &&
-                     encode_kv_map(&M.k, k, total_rows, H, kv_s0, kv_s1, A.is_bf16) &&
-                     encode_kv_map(&M.v, v, total_rows, H, kv_s0, kv_s1, A.is_bf16);
     const bool two = max_rows > UM;  // two groups of 128 rows per CTA share the K / V tiles
+    const bool wide = two && mode == 0;  // 128-key tiles
+    const bool tma = (mode == 0 || mode == 4) && total_rows > 0 && total_rows < (1ll << 31) && (kv_s0 % 8) == 0 && (kv_s1 % 8) == 0 &&
+                     encode_kv_map(&M.k, k, total_rows, H, kv_s0, kv_s1, A.is_bf16, wide ? WN : UN) &&
+                     encode_kv_map(&M.v, v, total_rows, H, kv_s0, kv_s1, A.is_bf16, wide ? WN : UN);
     if (two) grid.x = (max_rows + 2 * UM - 1) / (2 * UM);
-    if (two && tma) prefill_umma_pipe_kernel<2, true><<<grid, 2 * UM + 64, smem_pipe<2>(), st>>>(A, M);
+    if (wide && tma) prefill_umma_wide_kernel<<<grid, 2 * UM + 64, smem_wide(), st>>>(A, M);
+    else if (wide) prefill_umma_pipe_kernel<2, false><<<grid, 2 * UM + 32, smem_pipe<2>(), st>>>(A, M);
+    else if (two && tma) prefill_umma_pipe_kernel<2, true><<<grid, 2 * UM + 64, smem_pipe<2>(), st>>>(A, M);
     else if (two) prefill_umma_pipe_kernel<2, false><<<grid, 2 * UM + 32, smem_pipe<2>(), st>>>(A, M);
     else if (tma) prefill_umma_pipe_kernel<1, true><<<grid, UM + 64, smem_pipe<1>(), st>>>(A, M);
     else prefill_umma_pipe_kernel<1, false><<<grid, UM + 32, smem_pipe<1>(), st>>>(A, M);

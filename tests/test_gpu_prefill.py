@@ -34,7 +34,7 @@ CASES = [
 ]
 
 
-@pytest.mark.parametrize("kernel", ["tcgen05", "mma_sync", "tcgen05_plain", "tcgen05_row_copies"])
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma_sync", "tcgen05_plain", "tcgen05_row_copies", "tcgen05_64key_tiles"])
 @pytest.mark.parametrize("sc", CASES, ids=lambda s: s.name)
 def test_dense_path_matches_oracle_and_row_path(sc, kernel):
     """Both attention kernels of the dense path (head size 128 takes the tcgen05 kernel unless told otherwise)."""
@@ -42,7 +42,7 @@ def test_dense_path_matches_oracle_and_row_path(sc, kernel):
     from echokv_b200 import _native as N
     from echokv_b200.kernels.prefill import build_dense, build_rows, prefill_attention
 
-    old = N.lib.echokv_set_prefill_path({"tcgen05": 0, "mma_sync": 1, "tcgen05_plain": 2, "tcgen05_row_copies": 3}[kernel])
+    old = N.lib.echokv_set_prefill_path({"tcgen05": 0, "mma_sync": 1, "tcgen05_plain": 2, "tcgen05_row_copies": 3, "tcgen05_64key_tiles": 4}[kernel])
     try:
         _dense_case(sc)
     finally:
