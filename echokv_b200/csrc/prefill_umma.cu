@@ -29,6 +29,16 @@ constexpr int UD = 128;  // head size
 constexpr int TMEM_COLS = 256;  // S: columns [0, 64), O: columns [64, 192)
 constexpr int O_COL = 64;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+#ifdef ECHOKV_PROFILE
+// profile builds only: cycles that row thread 0 of every group spends per phase of the tile loop
+__device__ unsigned long long g_pphase[8];
+#define PF_T(x) const long long x = clock64()
+#define PF_ADD(k, a, b) pf[k] += (b) - (a)
+#else
+#define PF_T(x)
+#define PF_ADD(k, a, b)
+#endif
 constexpr float REF_SLACK = 8.f;  // log2 units a row may exceed the softmax reference before it moves
 
 constexpr int Q_BYTES = UM * UD * 2;        // two panels of 128 rows x 128 bytes
@@ -782,13 +792,19 @@ __global__ void __launch_bounds__(2 * UM + 64, 1) prefill_umma_wide_kernel(Args 
   } else if (row_thread) {
     const uint32_t t_row = tmem + ((uint32_t)((warp & 3) * 32) << 16) + grp * W_GCOLS;  // this warp's lanes, this group's columns
     float m_ref = -INFINITY, l_run = 0.f;
+#ifdef ECHOKV_PROFILE
+    long long pf[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#endif
     for (int tile = 0; tile < n_tiles; ++tile) {
+      PF_T(c0);
       if (!__all_sync(0xffffffffu, bar_wait(&bar_s[grp], tile & 1))) { ok = false; break; }  // the scores of this tile
       asm volatile("tcgen05.fence::after_thread_sync;");
+      PF_T(c1);
       uint32_t raw[WN];
 #pragma unroll
       for (int c = 0; c < WN / 32; ++c) tmem_ld32_nowait(t_row + W_SCOL + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&raw[32 * c]));
       tmem_ld_wait();
+      PF_T(c2);
       const int key0 = tile * WN;
       if (key0 + WN - 1 > lim) {  // bottom-right causal mask, and the keys past the context
 #pragma unroll
@@ -808,7 +824,9 @@ __global__ void __launch_bounds__(2 * UM + 64, 1) prefill_umma_wide_kernel(Args 
         for (int j = 0; j < w; ++j) m16[j] = fmaxf(m16[j], m16[j + w]);
       const float mx = m16[0] * A.scale_log2;
       // the reference only moves when some row of the warp outgrows it by more than REF_SLACK
-      if (__any_sync(0xffffffffu, mx > m_ref + REF_SLACK)) {
+      const bool moves = __any_sync(0xffffffffu, mx > m_ref + REF_SLACK);
+      PF_T(c3);
+      if (moves) {
         const float m_new = fmaxf(m_ref, mx);
         const float corr = m_new == -INFINITY ? 1.f : ex2(m_ref - m_new);
         m_ref = m_new;
@@ -828,6 +846,7 @@ __global__ void __launch_bounds__(2 * UM + 64, 1) prefill_umma_wide_kernel(Args 
         }
       }
       const float nref = m_ref == -INFINITY ? 0.f : -m_ref;
+      PF_T(c4);
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < WN / 32; ++c) {  // 32 keys -> 16 columns of P, over scores already in registers
@@ -842,10 +861,20 @@ __global__ void __launch_bounds__(2 * UM + 64, 1) prefill_umma_wide_kernel(Args 
         tmem_st16_raw(t_row + W_SCOL + 16 * c, w);
       }
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      PF_T(c5);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;");
       bar_arrive(&bar_p[grp]);
+      PF_T(c6);
+      PF_ADD(0, c0, c1); PF_ADD(1, c1, c2); PF_ADD(2, c2, c3); PF_ADD(3, c3, c4); PF_ADD(4, c4, c5); PF_ADD(5, c5, c6);
+#ifdef ECHOKV_PROFILE
+      pf[7] += 1;
+#endif
     }
+#ifdef ECHOKV_PROFILE
+    if (r128 == 0)
+      for (int i = 0; i < 8; ++i) atomicAdd(&g_pphase[i], (unsigned long long)pf[i]);
+#endif
     if (ok && !bar_wait(&bar_o[grp], (n_tiles - 1) & 1)) ok = false;
     ok = __all_sync(0xffffffffu, ok);
     asm volatile("tcgen05.fence::after_thread_sync;");
@@ -883,6 +912,17 @@ __global__ void __launch_bounds__(2 * UM + 64, 1) prefill_umma_wide_kernel(Args 
 // `handled` false.
 // Raised (1) by a kernel of this file whose bounded wait on an mbarrier ran out; its output is then undefined.
 __device__ int g_prefill_status;
+
+#ifdef ECHOKV_PROFILE
+extern "C" int echokv_debug_prefill_phase(unsigned long long* dst, int clear) {
+  const int rc = (int)cudaMemcpyFromSymbol(dst, umma::g_pphase, sizeof(unsigned long long) * 8);
+  if (clear) {
+    const unsigned long long z[8] = {};
+    cudaMemcpyToSymbol(umma::g_pphase, z, sizeof(z));
+  }
+  return rc;
+}
+#endif
 
 int prefill_status_take(bool clear) {
   int v = 0;
