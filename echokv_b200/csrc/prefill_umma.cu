@@ -847,20 +847,23 @@ __global__ void __launch_bounds__(2 * UM + 64, 1) prefill_umma_wide_kernel(Args 
       }
       const float nref = m_ref == -INFINITY ? 0.f : -m_ref;
       PF_T(c4);
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      // two elements per instruction (packed fp32 FMA / ADD) for the scaling and the row sum
+      const float2 sc2 = make_float2(A.scale_log2, A.scale_log2), nr2 = make_float2(nref, nref);
+      float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
       for (int c = 0; c < WN / 32; ++c) {  // 32 keys -> 16 columns of P, over scores already in registers
         uint32_t w[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float p0 = ex2(fmaf(__uint_as_float(raw[32 * c + 2 * e]), A.scale_log2, nref));
-          const float p1 = ex2(fmaf(__uint_as_float(raw[32 * c + 2 * e + 1]), A.scale_log2, nref));
-          sum4[e & 3] += p0 + p1;
-          w[e] = pack16(p0, p1, bf16);
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw[32 * c + 2 * e]), __uint_as_float(raw[32 * c + 2 * e + 1])), sc2, nr2);
+          const float2 pp = make_float2(ex2(x.x), ex2(x.y));
+          sum2[e & 3] = __fadd2_rn(sum2[e & 3], pp);
+          w[e] = pack16(pp.x, pp.y, bf16);
         }
         tmem_st16_raw(t_row + W_SCOL + 16 * c, w);
       }
-      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      const float2 s01 = __fadd2_rn(sum2[0], sum2[1]), s23 = __fadd2_rn(sum2[2], sum2[3]);
+      l_run += (s01.x + s01.y) + (s23.x + s23.y);
       PF_T(c5);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;");
