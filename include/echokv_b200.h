@@ -226,7 +226,8 @@ int echokv_gather_rows(const void* src, int64_t src_row_stride_bytes, const int6
  * (head size 128) and the mma.sync kernel otherwise; 1 always takes the mma.sync kernel; 2 takes the
  * tcgen05 kernel without the overlap of tensor work and softmax (two CTAs per SM); 3 takes the
  * overlapped tcgen05 kernel with the key / value tiles copied by its row threads instead of tensor-map
- * copies (what 0 does when total_ctx is unknown).  Returns the previous setting.  No counterpart in the
+ * copies (what 0 does when total_ctx is unknown); 4 keeps 64-key tiles where 0 would take the
+ * 128-key-tile kernel (chunks of more than 128 rows).  Returns the previous setting.  No counterpart in the
  * reference (it calls a flash-attention library there). */
 int echokv_set_prefill_path(int path);
 
