@@ -31,6 +31,8 @@ CASES = [
                       chunks=[333, 5]),
     S.build_attention("dense_f16_gqa1", 8, 128, 16, 8, [129, 1000], [2, 8, 4, 4], seed=93, kg=16, dtype="f16", gqa=1,
                       chunks=[129, 400]),
+    S.build_attention("dense_bf16_h3", 3, 128, 16, 8, [150, 45], [4, 8], seed=94, kg=16, dtype="bf16", gqa=2,
+                      chunks=[90, 45]),
 ]
 
 
