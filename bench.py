@@ -551,6 +551,7 @@ def run_b200(a) -> None:
             "canary": {"interval": a.canary_interval, "fires": canary["fires"],
                        "last": None if canary["pending"] is None else [round(x, 6) for x in canary["pending"][0].tolist()]},
             "clocks": clocks,
+            "kernel_status": int(N.lib.echokv_kernel_status(0)),  # 0: no kernel gave up on a bounded wait
             "prefill": prefill,
             "stock_bf16_decode": stock,
             "write": {"gbs": write_bytes / write_ms / 1e6, "ms_total": write_ms, "what": "bulk quantize-on-write of the context"},
