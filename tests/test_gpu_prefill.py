@@ -105,3 +105,42 @@ def test_dense_rejects_what_it_cannot_run():
         dense_attention(q, kv, kv, chunks, 4, torch.zeros_like(q), 0.1)
     with pytest.raises(ValueError):
         dense_attention(q.half(), kv.half(), kv.bfloat16(), chunks, 4, torch.zeros_like(q), 0.1)
+
+
+@pytest.mark.parametrize("path", [0, 4, 3, 2, 1], ids=["tcgen05", "64key_tiles", "row_copies", "plain", "mma_sync"])
+def test_dense_attention_long_context_matches_sdpa(path):
+    """Contexts of dozens of key tiles (the K / V rings wrap many times) whose scores grow along the context, so the
+    softmax reference moves and rows of O are rescaled; against torch's fp32 attention, tolerance 2e-2 (bf16)."""
+    import torch
+    import torch.nn.functional as F
+    from echokv_b200 import _native as N
+    from echokv_b200.kernels.prefill import dense_attention
+
+    torch.manual_seed(5)
+    Hq, H, D, dt = 8, 2, 128, torch.bfloat16
+    shapes = [(300, 3000), (77, 2500), (130, 130)]  # (chunk length, context)
+    T, total = sum(nq for nq, _ in shapes), sum(ctx for _, ctx in shapes)
+    q = torch.randn(T, Hq, D, device="cuda", dtype=dt)
+    k = torch.randn(total, H, D, device="cuda", dtype=dt)
+    v = torch.randn(total, H, D, device="cuda", dtype=dt)
+    rows, at_q, at_k = [], 0, 0
+    for nq, ctx in shapes:
+        ramp = torch.linspace(0.2, 3.0, ctx, device="cuda")[:, None, None]  # later keys score higher
+        k[at_k:at_k + ctx] = (k[at_k:at_k + ctx].float() * ramp).to(dt)
+        rows.append([at_q, at_q + nq, ctx, at_k])
+        at_q, at_k = at_q + nq, at_k + ctx
+    chunks = torch.tensor(rows, dtype=torch.int32, device="cuda")
+    out = torch.zeros(T, Hq, D, device="cuda", dtype=torch.float32)
+    old = N.lib.echokv_set_prefill_path(path)
+    try:
+        dense_attention(q, k, v, chunks, max(nq for nq, _ in shapes), out, D ** -0.5)
+    finally:
+        N.lib.echokv_set_prefill_path(old)
+    for qs, qe, ctx, ks in rows:
+        nq = qe - qs
+        qf = q[qs:qe].transpose(0, 1).float()
+        kf = k[ks:ks + ctx].transpose(0, 1).repeat_interleave(Hq // H, 0).float()
+        vf = v[ks:ks + ctx].transpose(0, 1).repeat_interleave(Hq // H, 0).float()
+        mask = torch.arange(ctx, device="cuda")[None, :] <= (ctx - nq + torch.arange(nq, device="cuda"))[:, None]
+        want = F.scaled_dot_product_attention(qf, kf, vf, attn_mask=mask, scale=D ** -0.5).transpose(0, 1)
+        assert (out[qs:qe] - want).abs().max().item() <= 2e-2
