@@ -186,8 +186,10 @@ int echokv_decode_static(const echokv_layout* layout, const echokv_pages* pages,
                          void* stream) {
   if (num_seqs <= 0) return ECHOKV_OK;
   if (!layout) return set_error(ECHOKV_E_ARGUMENT, "decode_static: layout is null");
+  if (num_q_heads <= 0 || layout->head_size <= 0 || num_splits <= 0)
+    return set_error(ECHOKV_E_ARGUMENT, "decode_static: num_q_heads, head_size and num_splits must be positive");
   const int64_t need = echokv_decode_scratch_bytes(num_seqs, num_q_heads, layout->head_size, num_splits);
-  if (need <= 0 || need > (int64_t)ECHOKV_STATIC_SCRATCH_BYTES)
+  if (need > (int64_t)ECHOKV_STATIC_SCRATCH_BYTES)
     return set_error(ECHOKV_E_UNSUPPORTED,
                      "decode_static: %lld sequences x %d query heads x %d splits need %lld bytes of split partials, "
                      "the built-in scratch holds %lld; use echokv_decode with caller-provided scratch",

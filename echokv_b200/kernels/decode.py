@@ -11,21 +11,34 @@ import torch
 from echokv_b200 import _native as N
 
 BLOCKS_PER_SPLIT = 16
+MAX_DECODE_SPLITS = 32  # upper bound of the split grid (backend.py:67-69 of the reference caps its fixed grid alike)
 
 
 class _Scratch:
-    """Per-device split-partials buffer, grown on demand and reused (a stable address lets a
-    captured CUDA graph replay it)."""
+    """Per-device split-partials buffer.
+
+    The buffer grows on demand until a call arrives while its stream is being captured: from then on
+    a CUDA graph may hold the buffer's address, so it is never replaced or freed.  A later eager call
+    that needs more bytes than the pinned buffer holds (more sequences than the captured sizes, or the
+    row path of a long prefill) gets a temporary of its own for that call instead.
+    """
 
     def __init__(self) -> None:
         self.buf: dict[torch.device, torch.Tensor] = {}
+        self.pinned: set[torch.device] = set()
 
     def get(self, device, nbytes: int) -> torch.Tensor:
         cur = self.buf.get(device)
-        if cur is None or cur.numel() < nbytes:
-            if torch.cuda.is_current_stream_capturing():
-                raise RuntimeError("decode scratch must be sized before CUDA-graph capture (run one eager step first)")
-            cur = self.buf[device] = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        capturing = torch.cuda.is_current_stream_capturing()
+        if cur is not None and cur.numel() >= nbytes:
+            if capturing:
+                self.pinned.add(device)
+            return cur
+        if capturing:
+            raise RuntimeError("decode scratch must be sized before CUDA-graph capture (run one eager step first)")
+        if device in self.pinned:
+            return torch.empty(nbytes, dtype=torch.uint8, device=device)  # this call only; the pinned buffer stays
+        cur = self.buf[device] = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         return cur
 
 
@@ -70,7 +83,7 @@ def decode_attention(store, query: torch.Tensor, block_table: torch.Tensor, seq_
     if num_splits is None:
         width = block_table.shape[1]
         max_blocks = width if max_len is None else min(width, -(-max_len // L.block_size))
-        num_splits = max(1, -(-max_blocks // blocks_per_split))
+        num_splits = max(1, min(-(-max_blocks // blocks_per_split), MAX_DECODE_SPLITS))
     if s == 0:
         return out
     nbytes = N.lib.echokv_decode_scratch_bytes(s, hq, L.head_size, num_splits)

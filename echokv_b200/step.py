@@ -23,12 +23,10 @@ import torch
 from echokv_b200.canary import canary_kl_ring, tp_mean
 from echokv_b200.controller import LayerController
 from echokv_b200.quant import SUPPORTED_BITS
-from echokv_b200.kernels.decode import BLOCKS_PER_SPLIT, decode_attention
+from echokv_b200.kernels.decode import BLOCKS_PER_SPLIT, MAX_DECODE_SPLITS, decode_attention
 from echokv_b200.kernels.write import gather_rows
 from echokv_b200.tiered_cache import TieredKVCache, TieredLayout
 from echokv_b200.write_plan import SharedState, WriteMeta
-
-MAX_DECODE_SPLITS = 32  # upper bound of the fixed split grid (backend.py:67-69 of the reference)
 
 
 class Staging:

@@ -189,3 +189,38 @@ def test_decode_events_hook_times_the_split_kernel():
     finally:
         N.lib.echokv_set_decode_events(None, None)
     assert torch.equal(got, want)
+
+
+def test_captured_graph_keeps_its_scratch_when_a_larger_eager_call_follows():
+    """A CUDA graph holds the address of the split-partials buffer it was captured with.  A later eager call
+    that needs more scratch (more sequences or splits than the captured grid) must not take that buffer
+    away from under the graph: the replay still gives the eager result bit for bit."""
+    import torch
+    from echokv_b200.kernels import decode as KD
+    from echokv_b200.kernels.decode import decode_attention
+
+    sc = DEC[1]
+    store, q, table, lens, _ = _store_and_inputs(sc)
+    dev = q.device
+    want = decode_attention(store, q, table, lens, sc.scale, 1, num_splits=4)
+    out = torch.zeros_like(want)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        decode_attention(store, q, table, lens, sc.scale, 1, num_splits=4, out=out)  # warm on the side stream
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        decode_attention(store, q, table, lens, sc.scale, 1, num_splits=4, out=out)
+    held = KD._scratch.buf[dev]
+    # an eager call whose partials cannot fit the held buffer: many sequences x the widest split grid
+    reps = max(1, held.numel() // (q.shape[1] * 32 * (q.shape[2] + 2) * 4 * len(sc.seq_lens))) + 1
+    big_q, big_t, big_l = q.repeat(reps, 1, 1), table.repeat(reps, 1), lens.repeat(reps)
+    big = decode_attention(store, big_q, big_t, big_l, sc.scale, 1, num_splits=32)
+    assert KD._scratch.buf[dev] is held and held.data_ptr() == KD._scratch.buf[dev].data_ptr()
+    junk = torch.full((held.numel() // 4,), 3.0e38, device=dev)  # whatever the allocator hands out next is not the held buffer
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    assert torch.isfinite(big).all() and junk.numel() > 0

@@ -135,3 +135,22 @@ def test_product_has_no_cpu_path():
         TieredKVCache(L, torch.zeros(4, 64 * TieredLayout.per_token_bytes(2, 64, 4), dtype=torch.uint8))
     with pytest.raises(RuntimeError):
         to_device(torch.zeros(1), "cpu")
+
+
+def test_product_controller_follows_the_reference_trace(golden):
+    """echokv_b200.controller.LayerController on the reference's recorded trace (controller.py:45-68 of the
+    reference: EMA per tier, lowest tier under tau, optional sqrt scaling of tau with the context length)."""
+    from echokv_b200.controller import ControllerParams, LayerController
+
+    z = golden("canary_controller")
+    for mode in ("none", "sqrt"):
+        c = LayerController(ControllerParams(tau0=0.01, l0=4096, tau_scaling=mode, alpha=0.3, init_bits=8))
+        trace = []
+        for d, ctx in zip(z["ctl_obs"], z["ctl_ctx"]):
+            c.observe(dict(zip((2, 4, 8), d.tolist())), float(ctx))
+            trace.append(c.bits)
+        assert trace == z[f"ctl_bits_{mode}"].tolist()
+        assert c.fires == len(trace)
+    pinned = LayerController(ControllerParams(fixed_bits=4))
+    pinned.observe({2: 0.0, 4: 0.0, 8: 0.0}, 4096.0)
+    assert pinned.bits == 4 and pinned.transitions == 0

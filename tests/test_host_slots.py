@@ -137,3 +137,30 @@ def test_null_block_redirect_is_mirrored():
     t.redirect_writes_to_null_block = True
     t.append_block_ids(0, ([7, 8],), True)
     assert t._echokv_np[0][0, :2].tolist() == [0, 0]
+
+
+def test_plugin_entry_point_is_declared(tmp_path, monkeypatch):
+    """pyproject.toml declares `echokv = echokv_b200.plugin:register` in the `vllm.general_plugins` group
+    (pyproject.toml:12-13 of the reference): build the package metadata and find it the way vLLM does."""
+    import importlib.metadata as md
+    import os
+    from pathlib import Path
+
+    import setuptools.build_meta as backend
+
+    root = Path(__file__).resolve().parent.parent
+    monkeypatch.chdir(root)
+    before = set(os.listdir(root))
+    try:
+        info = backend.prepare_metadata_for_build_wheel(str(tmp_path))
+    finally:
+        import shutil
+        for name in set(os.listdir(root)) - before:  # setuptools leaves an egg-info folder beside the sources
+            shutil.rmtree(root / name, ignore_errors=True)
+    dist = md.PathDistribution(tmp_path / info)
+    assert dist.metadata["Name"] == "echokv-b200"
+    eps = [e for e in dist.entry_points if e.group == "vllm.general_plugins"]
+    assert [(e.name, e.value) for e in eps] == [("echokv", "echokv_b200.plugin:register")]
+    register = eps[0].load()
+    monkeypatch.delenv("ECHOKV_ENABLE", raising=False)
+    register()  # without ECHOKV_ENABLE=1 the call touches nothing (plugin.py:17-28 of the reference)

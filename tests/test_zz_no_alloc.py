@@ -4,8 +4,10 @@ Some hosts of this library may not allocate device memory at the point where the
 a plugin living inside another framework's frozen memory pool, or a C program with no CUDA
 allocator -- so ``echokv_decode_static`` keeps the split partials in an 8 MiB array that is part
 of the library.  This test calls it through the C ABI twice in a row (the array is shared by all
-calls and keeps the previous call's contents) and compares with the ordinary entry point within
-the decode tolerance used everywhere else (max-abs 5e-3); oversized requests must be refused.
+calls and keeps the previous call's contents) and compares with the ordinary entry point: both run
+the same kernels on the same inputs, so the outputs must be identical bit for bit (which is inside
+the decode tolerance used everywhere else, max-abs 5e-3); the second call must leave the amount of
+device memory in use unchanged; oversized or malformed requests must be refused.
 It is collected last so that a failure here cannot hide any other test.
 """
 
@@ -51,10 +53,15 @@ def test_static_scratch_decode_matches_regular_entry_point():
             want = torch.zeros(q.shape, device="cuda", dtype=torch.float32)
             got = torch.zeros_like(want)
             N.check(_call(False, store, q, table, lens, sc.scale, num_splits, bps, want, scratch))
+            torch.cuda.synchronize()
+            free0, used0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
             N.check(_call(True, store, q, table, lens, sc.scale, num_splits, bps, got))
             torch.cuda.synchronize()
+            if rep:  # the first call on a device may load the module and looks up the array's address
+                assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_allocated() == used0
             assert torch.isfinite(got).all()
             assert float((got - want).abs().max()) <= 5e-3, (sc.name, rep)
+            assert torch.equal(got, want), (sc.name, rep)
 
 
 def test_static_scratch_decode_refuses_oversized_requests():
@@ -72,3 +79,7 @@ def test_static_scratch_decode_refuses_oversized_requests():
     lens = torch.zeros(s, dtype=torch.long, device="cuda")
     rc = _call(True, store, q, table, lens, 1.0, 32, 1, out)
     assert rc == -2 and b"built-in scratch" in N.lib.echokv_last_error()
+    rc = N.lib.echokv_decode_static(store.c_layout, store.c_pages, store.c_res, q.data_ptr(), q.stride(0), q.stride(1), 0, None,
+                                    table.data_ptr(), table.stride(0), None, lens.data_ptr(), out.data_ptr(), out.stride(0),
+                                    out.stride(1), 0, 1.0, 4, 1, 2, 0, N.stream_ptr(q.device))
+    assert rc == -3  # no query heads: an argument error, not a size refusal
