@@ -96,9 +96,6 @@ lib.echokv_set_decode_path.restype = C.c_int
 lib.echokv_kernel_status.argtypes = [C.c_int]
 lib.echokv_kernel_status.restype = C.c_int
 
-if os.environ.get("ECHOKV_B200_DECODE_PATH"):  # experiments: see echokv_set_decode_path
-    lib.echokv_set_decode_path(int(os.environ["ECHOKV_B200_DECODE_PATH"], 0))
-
 EXPORTS = sorted(list(_SIGS) + ["echokv_set_decode_path", "echokv_kernel_status", "echokv_set_prefill_path", "echokv_decode_static_scratch_bytes", "echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
                                 "echokv_demote_scratch_bytes"])
 

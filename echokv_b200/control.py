@@ -94,8 +94,6 @@ def set_tier_vector(model: torch.nn.Module, bits) -> int:
             raise ValueError(f"unsupported tier {b}")
     for impl, b in zip(impls, wanted):
         impl.controller.bits = b
-        if impl.store is not None:
-            impl.store.max_tier = 0  # a pinned-tier promise made to the decode kernel no longer holds
     return len(impls)
 
 

@@ -5,7 +5,7 @@ using namespace echokv;
 
 namespace echokv {
 int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
-                      int64_t num_seqs, int max_tier, int* counter, int* status, cudaStream_t st, bool* handled);
+                      int64_t num_seqs, int* counter, int* status, cudaStream_t st, bool* handled);
 int decode_status_take(bool clear);
 int prefill_status_take(bool clear);
 
@@ -148,7 +148,7 @@ int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const 
   bool handled = false;
   int* counter = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(scratch) +
                                         echokv_decode_scratch_bytes(num_seqs, num_q_heads, L.D, num_splits) - 256);
-  rc = launch_decode_mma(L, R, pg, A, num_seqs, pages->max_tier, counter, nullptr, st, &handled);
+  rc = launch_decode_mma(L, R, pg, A, num_seqs, counter, nullptr, st, &handled);
   if (rc) return rc;
   if (!handled) {
     dim3 grid((unsigned)num_seqs, (unsigned)L.H, (unsigned)num_splits);

@@ -166,8 +166,6 @@ class GroupRunner:
         for i, pages in enumerate(caches):
             res = residuals[i] if residuals else torch.zeros(residual_slots + 1, g, h, d, dtype=model_dtype, device=dev)
             self.stores.append(TieredKVCache(layout, pages, residual=res, shared=self.shared))
-            if controllers[i].params.fixed_bits is not None:  # a pinned layer can never hold a higher tier
-                self.stores[-1].max_tier = controllers[i].params.fixed_bits
             self.krefs.append(krefs[i] if krefs else self._kref_all[i])
             self.stashes.append(stashes[i] if stashes else self._stash_all[i])
         self.canary_max_q = canary_max_q

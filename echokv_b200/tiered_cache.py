@@ -226,9 +226,9 @@ class TieredKVCache:
 
     @property
     def max_tier(self) -> int:
-        """Upper bound (2/4/8) the caller guarantees for the tier of every block of this layer, or 0.
-        The decode kernel sizes its shared-memory stages by it; a block above the bound is read as
-        empty, so only set it when the layer's tier cannot rise (e.g. a pinned tier)."""
+        """Upper bound (2/4/8) the caller knows for the tier of every block of this layer, or 0.
+        Informational: the kernels do not depend on it (the decode kernel's shared-memory stages have
+        one size for every tier, so a layer may change tier under a captured graph)."""
         return self._c_pages.max_tier
 
     @max_tier.setter

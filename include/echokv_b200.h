@@ -69,8 +69,9 @@ typedef struct echokv_pages {
   void* base;
   int64_t page_stride_bytes;
   int64_t num_blocks;
-  int32_t max_tier; /* upper bound of the tier of any block in this pool (2/4/8), 0 = unknown;
-                       lets the decode kernel size its shared-memory stages for narrower rows */
+  int32_t max_tier; /* optional: upper bound of the tier of any block in this pool (2/4/8), 0 = unknown.
+                       Informational only: no kernel depends on it (the decode kernel's shared-memory
+                       stages have one size for every tier) */
   int32_t reserved;
 } echokv_pages;
 
@@ -182,8 +183,8 @@ int echokv_decode_static(const echokv_layout* layout, const echokv_pages* pages,
                          int64_t num_seqs, int32_t num_q_heads, void* stream);
 
 /* Kernel selection of echokv_decode: 0 (default) picks the tensor-core kernel when the shape fits
- * (head_size 128, v_group 32, 1/2/4/8 KV heads, <= 8 query heads per KV head) and the generic
- * CUDA-core kernel otherwise; 1 always takes the generic kernel.  Returns the previous setting.
+ * (head_size 128, v_group 32, 1/2/4/8 KV heads, <= 8 query heads per KV head, block_size and k_group
+ * multiples of 16) and the generic CUDA-core kernel otherwise; 1 always takes the generic kernel.  Returns the previous setting.
  * No counterpart in the reference (its Triton autotuner plays this role, kernels/decode.py:265-280). */
 int echokv_set_decode_path(int path);
 
@@ -234,8 +235,7 @@ int echokv_set_prefill_path(int path);
 /* Every wait inside the kernels (on an mbarrier or a lock) gives up after a fixed number of polls and
  * raises a status word on the device instead of hanging; the output of that launch is then undefined.
  * Synchronizes the device and returns the words of the current device: bit 0 = a wait of the decode
- * kernel ran out, bit 1 = the decode kernel met a block tier it was not built for, bit 2 = a wait of
- * the prefill kernel ran out; negative on a CUDA error.  `clear` != 0 resets them.  No counterpart in
+ * kernel ran out, bit 1 = reserved (always 0), bit 2 = a wait of the prefill kernel ran out; negative on a CUDA error.  `clear` != 0 resets them.  No counterpart in
  * the reference. */
 int echokv_kernel_status(int clear);
 
