@@ -93,10 +93,12 @@ for _name, _args in _SIGS.items():
 
 lib.echokv_set_decode_path.argtypes = [C.c_int]
 lib.echokv_set_decode_path.restype = C.c_int
+lib.echokv_set_decode_wait_limit.argtypes = [C.c_int64, C.c_int]
+lib.echokv_set_decode_wait_limit.restype = C.c_int
 lib.echokv_kernel_status.argtypes = [C.c_int]
 lib.echokv_kernel_status.restype = C.c_int
 
-EXPORTS = sorted(list(_SIGS) + ["echokv_set_decode_path", "echokv_kernel_status", "echokv_set_prefill_path", "echokv_decode_static_scratch_bytes", "echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
+EXPORTS = sorted(list(_SIGS) + ["echokv_set_decode_path", "echokv_set_decode_wait_limit", "echokv_kernel_status", "echokv_set_prefill_path", "echokv_decode_static_scratch_bytes", "echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
                                 "echokv_demote_scratch_bytes"])
 
 

@@ -60,6 +60,16 @@ class EchoKVAttentionBackend(AttentionBackend):
         return replace(spec, num_head_slots=1, state_content_bytes=nbytes)
 
     @staticmethod
+    def get_kv_cache_shape(num_blocks: int, block_size: int, num_kv_heads: int, head_size: int,
+                           cache_dtype_str: str = "auto"):
+        """Shape (in elements of the model dtype) of a layer's slice of the pool on vLLM releases without
+        ``customize_spec``: one opaque run of bytes per token, ``vllm_compat.slot_bytes`` per KV head."""
+        from echokv_b200.vllm_compat import slot_bytes
+
+        elt = torch.empty((), dtype=_model_dtype()).element_size()
+        return (num_blocks, 1, block_size, num_kv_heads * slot_bytes(num_kv_heads, head_size) // elt)
+
+    @staticmethod
     def get_supported_kernel_block_sizes(kv_cache_spec=None):
         return [MultipleOf(_block_multiple())]
 

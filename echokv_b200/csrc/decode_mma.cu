@@ -54,7 +54,7 @@ __device__ unsigned long long g_cta[1024 * 4];  // per CTA: start ns, end ns, SM
 constexpr int D = 128;          // head size of this kernel
 constexpr int NG = 4;           // V groups per head (v_group 32)
 constexpr int TILE = 16;        // tokens per tile
-constexpr unsigned long long WAIT_NS = 2000000000ull;  // a wait gives up after this long
+constexpr unsigned long long WAIT_NS = 2000000000ull;  // a wait gives up after this long (echokv_set_decode_wait_limit changes it)
 
 // What the producer tells the consumers about a staged group (stored at `o_hdr` of its first stage).
 constexpr int F_RES = 1, F_FIRST = 2, F_LAST = 4;  // K from the residual buffer / first / last group of a work item
@@ -68,9 +68,9 @@ struct alignas(16) StageHeader {
 struct alignas(16) TilePlan {
   StageHeader hdr;
   const unsigned char* stats[4];    // V scale, V min, K scale, K min of the tile (one run from stats[0] when contiguous)
-  const unsigned char* row_src[TILE];
+  const unsigned char* run[4];      // the tile's token rows lie in up to four runs (one per chunk it touches) of `TILE >> run_shift` rows
 };
-constexpr int UNIT = 32;         // tiles planned at a time (one per producer lane)
+constexpr int UNIT = 16;         // tiles planned at a time (one per producer lane)
 constexpr int MAX_NS = 8;        // stage ring slots at most
 constexpr int HDR_BYTES = 256;   // 2 * MAX_NS mbarriers + the remap lock
 static_assert(sizeof(StageHeader) == 32 && sizeof(TilePlan) % 16 == 0, "16-byte copies of headers");
@@ -92,9 +92,12 @@ struct Params {
   const uint8_t* pages;
   DecodeArgs A;
   int NS, num_seqs;
+  int team_bytes;                          // shared memory of one team of a CTA
   int* status;                             // device status word (0 ok), may be null
   int* counter;                            // next unclaimed work item (zero at launch)
   int q_vec16;                             // 16-bit queries whose rows can be read with 16-byte loads
+  unsigned long long wait_ns;              // a wait on a barrier or the remap lock gives up after this long
+  int idle_producer;                       // test hook: the producer warps stage nothing, so every consumer wait runs out
 };
 
 // ---- PTX helpers ---------------------------------------------------------------------------
@@ -124,15 +127,17 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Returns false if the barrier did not flip within WAIT_NS.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Returns false if the barrier did not flip within `limit_ns`.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned long long limit_ns) {
   if (mbar_try(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (;;) {
 #pragma unroll 1
-    for (int it = 0; it < 256; ++it)
+    for (int it = 0; it < 256; ++it) {
+      __nanosleep(40);  // leave the issue slots to the warps that have work
       if (mbar_try(bar, parity)) return true;
-    if (global_ns() - t0 > WAIT_NS) return false;
+    }
+    if (global_ns() - t0 > limit_ns) return false;
   }
 }
 __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -296,10 +301,11 @@ __device__ __forceinline__ float acc_unit(int half) {
   else return 1.f;
 }
 
-// Shared-memory copy of a warp's queries: [8 query rows + a zero row][D] fp16, pre-multiplied by
-// softmax_scale * log2(e), rows padded by 16 bytes so that ldmatrix over the query rows is conflict free.
+// Shared-memory copy of a team's queries: [H][gqa query rows][D] fp16 and one zero row that every absent query
+// column of the MMAs reads, pre-multiplied by softmax_scale * log2(e), rows padded by 16 bytes so that ldmatrix
+// over the query rows is conflict free.
 constexpr int QN_ROW = D * 2 + 16;
-__host__ __device__ constexpr int q_head_bytes(int rows) { return rows * QN_ROW; }
+__host__ __device__ constexpr int q_copy_bytes(int H, int gqa) { return (H * gqa + 1) * QN_ROW; }
 constexpr int REMAP_ROW = D + 4;                      // floats per query head in the canonical layout
 constexpr int REMAP_BYTES = 8 * REMAP_ROW * 4;
 
@@ -307,9 +313,7 @@ struct WarpState {
   float acc[8][4];  // O^T tiles: [m-tile][c0..c3], channel order depends on `bits`
   float bl[4];      // [0],[1]: sum_t p * v_min for V group r (lanes r < NG); [2],[3]: sum_t p
   float m0, m1;     // running max (log2 domain) of query heads 2j and 2j+1
-  uint32_t qf[16];  // this lane's B fragments of the query for the 8 k-steps of Q.K^T, in tier `qbits`' channel order
   int bits;         // tier whose channel order `acc` is in (0: none yet)
-  int qbits;        // tier `qf` was built for (0: none yet)
 };
 
 template <int BITS>
@@ -363,126 +367,123 @@ __device__ __forceinline__ uint32_t code_row(const Lane& ln, bool v_side) {
     return pr * slot_bytes(H) + odd * (64u * H) + ln.h * 32u + piece + (v_side ? 32u * H : 0u);
 }
 
-// (Re)build the register copy of the query for tier BITS from the shared copy: lane (r, j) holds column r
-// of every B fragment, i.e. query head r at the two channel pairs the tier's unpacking puts into k slots
-// 2j, 2j+1 and 2j+8, 2j+9 of each k-step, times the 2^-pos of the codes' bit positions.
-template <int BITS>
-__device__ __forceinline__ void build_qf(WarpState& w, const Lane& ln) {
-  const uint32_t base = ln.qn_lane;
-  if constexpr (BITS == 8) {  // k-step p: channels 16p + 4j + {0,1} and {2,3}
+// ---- Q.K^T over the codes of NT tiles, with the k_min term riding along -----------------------------------
+// Per piece of channels the lane loads its slice of the query once (natural channel order, shared memory), and
+// per tile multiplies it by the K group's scales (q' = q * k_scale, fp16), pairs the products the way the tier's
+// unpacking pairs the codes, and runs the MMA k-steps:  c += codes * q'  in code units (2^-24).
+// The query slice is pre-divided by the 2^pos of the code position each channel sits at (INT4: upper nibbles,
+// INT2: crumbs at bits 2, 4, 6).
+//
+// The constant term of the scores, sum_d q[g, d] * k_min[d], is the same for every token of a K group; one chain
+// of 8 more k-steps gives it for two tiles at once: the A fragment's rows 0..7 are the first tile's k_min row
+// (ldmatrix with all eight row addresses equal), rows 8..15 the second tile's; the B fragments are the natural
+// query (ldmatrix over the 8 query rows).  c2[0], c2[1]: first tile, query heads 2j, 2j+1; c2[2], c2[3]: second.
+// The chains (one or two per tile, and this one) are interleaved so that no MMA waits for the one before it.
+template <int BITS, int H, int NT>
+__device__ __forceinline__ void qk_scores(const Lane& ln, const uint32_t (&sbk)[NT], float (&c)[NT][4], float (&c2)[4]) {
+  uint32_t krow[NT], ks[NT];
 #pragma unroll
-    for (int p = 0; p < 8; ++p) {
-      uint2 q;
-      asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(q.x), "=r"(q.y) : "r"(base + p * 32 + ln.j * 8));
-      w.qf[2 * p] = q.x;
-      w.qf[2 * p + 1] = q.y;
-    }
-  } else if constexpr (BITS == 4) {  // piece p (32 channels): lane's channels 32p + 8j + 0..7, pairs (0,4) (1,5) (2,6) (3,7)
-#pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      uint32_t q[4];
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]) : "r"(base + p * 64 + ln.j * 16));
-      w.qf[4 * p + 0] = prmt(q[0], q[2], 0x5410u);
-      w.qf[4 * p + 1] = hmul2u(prmt(q[0], q[2], 0x7632u), 0x2c002c00u);  // upper nibbles: 2^-4
-      w.qf[4 * p + 2] = prmt(q[1], q[3], 0x5410u);
-      w.qf[4 * p + 3] = hmul2u(prmt(q[1], q[3], 0x7632u), 0x2c002c00u);
-    }
-  } else {  // piece p (64 channels): lane's channels 64p + 16j + 0..15, pairs (i, i + 8), position 2 * (i % 4)
-#pragma unroll
-    for (int p = 0; p < 2; ++p) {
-      uint32_t q[8];
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]) : "r"(base + p * 128 + ln.j * 32));
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7]) : "r"(base + p * 128 + ln.j * 32 + 16));
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const uint32_t pair = (i & 1) ? prmt(q[i >> 1], q[(i >> 1) + 4], 0x7632u) : prmt(q[i >> 1], q[(i >> 1) + 4], 0x5410u);
-        const uint32_t f = (i & 3) == 0 ? 0x3c003c00u : (i & 3) == 1 ? 0x34003400u : (i & 3) == 2 ? 0x2c002c00u : 0x24002400u;
-        w.qf[8 * p + i] = (i & 3) == 0 ? pair : hmul2u(pair, f);  // 1, 2^-2, 2^-4, 2^-6
-      }
-    }
+  for (int t = 0; t < NT; ++t) {
+    krow[t] = sbk[t] + code_row<BITS, H>(ln, false);
+    ks[t] = sbk[t] + o_ks(H) + ln.h * (D * 2);
   }
-  w.qbits = BITS;
-}
-
-// ---- Q.K^T over the codes of one tile: c += codes * (q * k_scale), in code units (2^-24) ---------------
-template <int BITS, int H>
-__device__ __forceinline__ void qk_codes(const WarpState& w, const Lane& ln, uint32_t sb, float (&c)[4]) {
-  const uint32_t krow = sb + code_row<BITS, H>(ln, false);
-  const uint32_t ks = sb + o_ks(H) + ln.h * (D * 2);
+  const uint32_t km_ld = ((ln.lane & 8) ? sbk[NT - 1] : sbk[0]) + ln.km_ld;
+  uint32_t Bn[4];
+  auto km_step = [&](auto kc) {  // k-step `k` of the k_min chain
+    constexpr int k = decltype(kc)::value;
+    uint32_t Am[4];
+    if constexpr ((k & 1) == 0) ldsm_x4<(k / 2) * 64>(Bn, ln.qn_ld);
+    ldsm_x4<k * 32>(Am, km_ld);
+    mma16816(c2, Am[0], Am[1], Am[2], Am[3], Bn[2 * (k & 1)], Bn[2 * (k & 1) + 1]);
+  };
   if constexpr (BITS == 8) {
-    const uint32_t sp = ks + ln.j * 8;  // this lane's 4 channels of every 16-channel piece
+    const uint32_t qp = ln.qn_lane + ln.j * 8;  // this lane's 4 channels of every 16-channel piece
     static_for<4>([&](auto ic) {  // pieces 2i, 2i+1 (16 channels each)
       constexpr int i = decltype(ic)::value;
-      uint32_t R[4];
-      ldsm_x4<i * 32>(R, krow);
+      uint32_t R[NT][4];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) ldsm_x4<i * 32>(R[t], krow[t]);
       static_for<2>([&](auto ec) {
         constexpr int e = decltype(ec)::value, p = 2 * i + e;
-        const uint2 s = lds64<32 * p>(sp);
-        uint32_t a[2], b[2];
-        sub8(R[2 * e], a);
-        sub8(R[2 * e + 1], b);
-        mma16816(c, a[0], b[0], a[1], b[1], hmul2u(w.qf[2 * p], s.x), hmul2u(w.qf[2 * p + 1], s.y));
+        const uint2 q = lds64<32 * p>(qp);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          const uint2 sc = lds64<32 * p>(ks[t] + ln.j * 8);
+          uint32_t a[2], b[2];
+          sub8(R[t][2 * e], a);
+          sub8(R[t][2 * e + 1], b);
+          mma16816(c[t], a[0], b[0], a[1], b[1], hmul2u(q.x, sc.x), hmul2u(q.y, sc.y));
+        }
+        km_step(std::integral_constant<int, p>{});
       });
     });
   } else if constexpr (BITS == 4) {
-    const uint32_t sp = ks + ln.j * 16;  // this lane's 8 channels of every 32-channel piece
+    const uint32_t qp = ln.qn_lane + ln.j * 16;  // this lane's 8 channels of every 32-channel piece
     static_for<2>([&](auto ic) {  // pieces 2i, 2i+1 (32 channels each)
       constexpr int i = decltype(ic)::value;
-      uint32_t R[4];
-      ldsm_x4<i * 32>(R, krow);
+      uint32_t R[NT][4];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) ldsm_x4<i * 32>(R[t], krow[t]);
       static_for<2>([&](auto ec) {
         constexpr int e = decltype(ec)::value, p = 2 * i + e;
-        uint32_t S[4];
-        lds128<64 * p>(S, sp);
-        uint32_t a[4], b[4];
-        sub4(R[2 * e], a);
-        sub4(R[2 * e + 1], b);
-        mma16816(c, a[0], b[0], a[1], b[1], hmul2u(w.qf[4 * p], prmt(S[0], S[2], 0x5410u)),
-                 hmul2u(w.qf[4 * p + 1], prmt(S[0], S[2], 0x7632u)));
-        mma16816(c, a[2], b[2], a[3], b[3], hmul2u(w.qf[4 * p + 2], prmt(S[1], S[3], 0x5410u)),
-                 hmul2u(w.qf[4 * p + 3], prmt(S[1], S[3], 0x7632u)));
+        uint32_t Q[4];
+        lds128<64 * p>(Q, qp);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) Q[k] = hmul2u(Q[k], 0x2c003c00u);  // odd channels sit in upper nibbles (pos 4): 2^-4
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          uint32_t S[4], Z[4];
+          lds128<64 * p>(S, ks[t] + ln.j * 16);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) Z[k] = hmul2u(Q[k], S[k]);
+          uint32_t a[4], b[4];
+          sub4(R[t][2 * e], a);
+          sub4(R[t][2 * e + 1], b);
+          mma16816(c[t], a[0], b[0], a[1], b[1], prmt(Z[0], Z[2], 0x5410u), prmt(Z[0], Z[2], 0x7632u));  // channels 0,4 | 1,5
+          if (t == 0) km_step(std::integral_constant<int, 2 * p>{});
+          mma16816(c[t], a[2], b[2], a[3], b[3], prmt(Z[1], Z[3], 0x5410u), prmt(Z[1], Z[3], 0x7632u));  // channels 2,6 | 3,7
+        }
+        km_step(std::integral_constant<int, 2 * p + 1>{});
       });
     });
   } else {
-    const uint32_t sp = ks + ln.j * 32;  // this lane's 16 channels of every 64-channel piece
-    uint32_t R[4];
-    ldsm_x4<0>(R, krow);  // pieces 0, 1 (64 channels each)
+    const uint32_t qp = ln.qn_lane + ln.j * 32;  // this lane's 16 channels of every 64-channel piece
+    uint32_t R[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) ldsm_x4<0>(R[t], krow[t]);  // pieces 0, 1 (64 channels each)
     static_for<2>([&](auto pc) {
       constexpr int p = decltype(pc)::value;
-      uint32_t S[8];
+      uint32_t Q[8];
       {
         uint32_t t4[4];
-        lds128<128 * p>(t4, sp);      S[0] = t4[0]; S[1] = t4[1]; S[2] = t4[2]; S[3] = t4[3];
-        lds128<128 * p + 16>(t4, sp); S[4] = t4[0]; S[5] = t4[1]; S[6] = t4[2]; S[7] = t4[3];
-      }
-      uint32_t a[8], b[8];
-      sub2(R[2 * p], a);
-      sub2(R[2 * p + 1], b);
+        lds128<128 * p>(t4, qp);
+        Q[0] = t4[0]; Q[1] = hmul2u(t4[1], 0x24002c00u); Q[2] = t4[2]; Q[3] = hmul2u(t4[3], 0x24002c00u);
+        lds128<128 * p + 16>(t4, qp);
+        Q[4] = t4[0]; Q[5] = hmul2u(t4[1], 0x24002c00u); Q[6] = t4[2]; Q[7] = hmul2u(t4[3], 0x24002c00u);
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        mma16816(c, a[2 * k], b[2 * k], a[2 * k + 1], b[2 * k + 1],
-                 hmul2u(w.qf[8 * p + 2 * k], prmt(S[k], S[k + 4], 0x5410u)),
-                 hmul2u(w.qf[8 * p + 2 * k + 1], prmt(S[k], S[k + 4], 0x7632u)));
+        for (int k = 0; k < 8; k += 2) Q[k] = hmul2u(Q[k], 0x34003c00u);  // crumbs at pos 0, 2: 1, 2^-2; at pos 4, 6: 2^-4, 2^-6
+      }
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        uint32_t S[8], Z[8];
+        {
+          uint32_t t4[4];
+          lds128<128 * p>(t4, ks[t] + ln.j * 32);      S[0] = t4[0]; S[1] = t4[1]; S[2] = t4[2]; S[3] = t4[3];
+          lds128<128 * p + 16>(t4, ks[t] + ln.j * 32); S[4] = t4[0]; S[5] = t4[1]; S[6] = t4[2]; S[7] = t4[3];
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) Z[k] = hmul2u(Q[k], S[k]);
+        uint32_t a[8], b[8];
+        sub2(R[t][2 * p], a);
+        sub2(R[t][2 * p + 1], b);
+        static_for<4>([&](auto kc) {
+          constexpr int k = decltype(kc)::value;
+          mma16816(c[t], a[2 * k], b[2 * k], a[2 * k + 1], b[2 * k + 1], prmt(Z[k], Z[k + 4], 0x5410u), prmt(Z[k], Z[k + 4], 0x7632u));
+          if (t == 0) km_step(std::integral_constant<int, 4 * p + k>{});
+        });
+      }
     });
   }
-}
-
-// Constant term of the scores, sum_d q[g, d] * k_min[d], for up to two tiles in one chain of 8 MMA
-// k-steps: the A fragment's rows 0..7 are the first tile's k_min row (ldmatrix with all eight row
-// addresses equal), rows 8..15 the second tile's; the B fragments are the natural-order query
-// (ldmatrix over the 8 query rows).  c2[0], c2[1]: first tile, query heads 2j, 2j+1; c2[2], c2[3]: second tile.
-template <int H>
-__device__ __forceinline__ void km_term(const Lane& ln, uint32_t sb0, uint32_t sb1, float (&c2)[4]) {
-  const uint32_t a_ld = ((ln.lane & 8) ? sb1 : sb0) + ln.km_ld;
-  static_for<4>([&](auto k2c) {
-    constexpr int k2 = decltype(k2c)::value;
-    uint32_t B[4], A0[4], A1[4];
-    ldsm_x4<k2 * 64>(B, ln.qn_ld);
-    ldsm_x4<k2 * 64>(A0, a_ld);
-    ldsm_x4<k2 * 64 + 32>(A1, a_ld);
-    mma16816(c2, A0[0], A0[1], A0[2], A0[3], B[0], B[1]);
-    mma16816(c2, A1[0], A1[1], A1[2], A1[3], B[2], B[3]);
-  });
 }
 
 // K of the tile comes from the residual buffer (the block's open group): fp16(k) straight into the
@@ -619,14 +620,13 @@ __device__ __forceinline__ int bias_row(int G, int h) { return H >= 2 ? G + 4 * 
 
 // Bring the warp's state to tier BITS: the register copy of the query and the accumulators' channel order.
 template <int BITS>
-__device__ __forceinline__ void enter_tier(WarpState& w, const Lane& ln, float* remap, int* lock, bool& ok) {
-  if (w.qbits != BITS) build_qf<BITS>(w, ln);
+__device__ __forceinline__ void enter_tier(WarpState& w, const Lane& ln, float* remap, int* lock, unsigned long long limit_ns, bool& ok) {
   if (w.bits != BITS) {
     if (w.bits != 0) {  // re-map the accumulators to this tier's channel order (rare: tier changes inside a work item)
       if (ln.lane == 0) {
         const unsigned long long t0 = global_ns();
         while (atomicCAS(lock, 0, 1) != 0) {
-          if (global_ns() - t0 > WAIT_NS) { ok = false; break; }
+          if (global_ns() - t0 > limit_ns) { ok = false; break; }
         }
       }
       __syncwarp();
@@ -648,7 +648,7 @@ __device__ __forceinline__ void process_group(const Params& P, const Lane& ln, c
                                               int n_valid, bool in_res, long long res_slot, int pos0, WarpState& w,
                                               float* remap, int* lock, bool& ok) {
   PROF_T(f0);
-  enter_tier<BITS>(w, ln, remap, lock, ok);
+  enter_tier<BITS>(w, ln, remap, lock, P.wait_ns, ok);
   float c[NT][4];
 #pragma unroll
   for (int t = 0; t < NT; ++t) c[t][0] = c[t][1] = c[t][2] = c[t][3] = 0.f;
@@ -656,16 +656,13 @@ __device__ __forceinline__ void process_group(const Params& P, const Lane& ln, c
     const float4 s4 = qk_residual(P.R, res_slot, pos0, n_valid, ln.qn_lane, ln.h, ln.lane);
     c[0][0] = s4.x; c[0][1] = s4.y; c[0][2] = s4.z; c[0][3] = s4.w;
   } else {
+    // scores in code units; the k_min chain rides along
     float c2[4] = {0.f, 0.f, 0.f, 0.f};
-    km_term<H>(ln, sbk[0], sbk[NT - 1], c2);
-#pragma unroll
-    for (int t = 0; t < NT; ++t) qk_codes<BITS, H>(w, ln, sbk[t], c[t]);
+    qk_scores<BITS, H, NT>(ln, sbk, c, c2);
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
-      c[t][0] = fmaf(c[t][0], CODE_UNSCALE, c2[2 * t]);
-      c[t][1] = fmaf(c[t][1], CODE_UNSCALE, c2[2 * t + 1]);
-      c[t][2] = fmaf(c[t][2], CODE_UNSCALE, c2[2 * t]);
-      c[t][3] = fmaf(c[t][3], CODE_UNSCALE, c2[2 * t + 1]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) c[t][k] = fmaf(c[t][k], CODE_UNSCALE, c2[2 * (NT == 1 ? 0 : t) + (k & 1)]);
     }
   }
   if (NT == 1 && n_valid < TILE) {  // a partial tile (the sequence's last): tokens past the end do not count
@@ -739,6 +736,10 @@ __device__ __forceinline__ BlockMeta load_meta(const Params& P, int64_t bt_row, 
   return m;
 }
 
+// The split's partial result: accumulators (in true units, V min contributions added) to acc[seq, head, split, :],
+// running maximum and denominator to ml.  A lane's accumulator rows are neighbouring channels (INT4: 4 per V group,
+// INT2: 8 per half of the head, INT8: 2 per 16-channel tile), so they leave as 16- or 8-byte stores that the
+// eight lanes of a query head put side by side.
 template <int BITS, int H>
 __device__ __forceinline__ void write_partial(const Params& P, const WarpState& w, int seq, int split, int h, int lane) {
   const int r = lane >> 2, j = lane & 3;
@@ -746,38 +747,70 @@ __device__ __forceinline__ void write_partial(const Params& P, const WarpState& 
   const int g0 = 2 * j, g1 = 2 * j + 1;
   const int64_t o0 = (((int64_t)seq * A.Hq + h * A.gqa + g0) * A.num_splits + split);
   const int64_t o1 = o0 + A.num_splits;
+  float* dst0 = A.acc + o0 * D;
+  float* dst1 = A.acc + o1 * D;
+  const bool on0 = g0 < A.gqa, on1 = g1 < A.gqa;
+  // V min contribution of V group G: held by lane (r = bias_row(G), j)
+  float bias0[NG], bias1[NG];
 #pragma unroll
-  for (int mt = 0; mt < 8; ++mt) {
-    // V min contribution of the channels' group: held by lane (r = G, j)
-    int G;
-    if constexpr (BITS == 8) G = mt >> 1;
-    else if constexpr (BITS == 4) G = mt >> 1;
-    else G = 2 * (mt >> 2) + (r >= 4 ? 1 : 0);
-    const float bias0 = __shfl_sync(0xffffffffu, w.bl[0], bias_row<H>(G, h) * 4 + j);
-    const float bias1 = __shfl_sync(0xffffffffu, w.bl[1], bias_row<H>(G, h) * 4 + j);
-    const int c0 = acc_channel<BITS>(mt, r, 0), c1 = acc_channel<BITS>(mt, r, 1);
-    if (g0 < A.gqa) {
-      A.acc[o0 * D + c0] = fmaf(w.acc[mt][0], acc_unit<BITS>(0), bias0);
-      A.acc[o0 * D + c1] = fmaf(w.acc[mt][2], acc_unit<BITS>(1), bias0);
+  for (int G = 0; G < NG; ++G) {
+    bias0[G] = __shfl_sync(0xffffffffu, w.bl[0], bias_row<H>(G, h) * 4 + j);
+    bias1[G] = __shfl_sync(0xffffffffu, w.bl[1], bias_row<H>(G, h) * 4 + j);
+  }
+  if constexpr (BITS == 4) {  // m-tiles 2G, 2G+1: channels 32G + 4r + {0,1} and {2,3}
+#pragma unroll
+    for (int G = 0; G < NG; ++G) {
+      const float u0 = acc_unit<4>(0), u1 = acc_unit<4>(1);
+      const int ch = 32 * G + 4 * r;
+      if (on0) *reinterpret_cast<float4*>(dst0 + ch) = make_float4(
+          fmaf(w.acc[2 * G][0], u0, bias0[G]), fmaf(w.acc[2 * G][2], u1, bias0[G]),
+          fmaf(w.acc[2 * G + 1][0], u0, bias0[G]), fmaf(w.acc[2 * G + 1][2], u1, bias0[G]));
+      if (on1) *reinterpret_cast<float4*>(dst1 + ch) = make_float4(
+          fmaf(w.acc[2 * G][1], u0, bias1[G]), fmaf(w.acc[2 * G][3], u1, bias1[G]),
+          fmaf(w.acc[2 * G + 1][1], u0, bias1[G]), fmaf(w.acc[2 * G + 1][3], u1, bias1[G]));
     }
-    if (g1 < A.gqa) {
-      A.acc[o1 * D + c0] = fmaf(w.acc[mt][1], acc_unit<BITS>(0), bias1);
-      A.acc[o1 * D + c1] = fmaf(w.acc[mt][3], acc_unit<BITS>(1), bias1);
+  } else if constexpr (BITS == 2) {  // m-tiles 4q .. 4q+3: channels 64q + 8r + {0..7}, all in V group 2q + (r >= 4)
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const float b0 = r >= 4 ? bias0[2 * q + 1] : bias0[2 * q], b1 = r >= 4 ? bias1[2 * q + 1] : bias1[2 * q];
+      const int ch = 64 * q + 8 * r;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int m = 4 * q + 2 * e;
+        if (on0) *reinterpret_cast<float4*>(dst0 + ch + 4 * e) = make_float4(w.acc[m][0] + b0, w.acc[m][2] + b0, w.acc[m + 1][0] + b0, w.acc[m + 1][2] + b0);
+        if (on1) *reinterpret_cast<float4*>(dst1 + ch + 4 * e) = make_float4(w.acc[m][1] + b1, w.acc[m][3] + b1, w.acc[m + 1][1] + b1, w.acc[m + 1][3] + b1);
+      }
+    }
+  } else {  // m-tile mt: channels 16 mt + 2r + {0, 1}, V group mt / 2
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+      const float u = acc_unit<8>(0);
+      const int ch = 16 * mt + 2 * r;
+      if (on0) *reinterpret_cast<float2*>(dst0 + ch) = make_float2(fmaf(w.acc[mt][0], u, bias0[mt >> 1]), fmaf(w.acc[mt][2], u, bias0[mt >> 1]));
+      if (on1) *reinterpret_cast<float2*>(dst1 + ch) = make_float2(fmaf(w.acc[mt][1], u, bias1[mt >> 1]), fmaf(w.acc[mt][3], u, bias1[mt >> 1]));
     }
   }
   if (r == 0) {
-    if (g0 < A.gqa) { A.ml[o0 * 2] = w.m0; A.ml[o0 * 2 + 1] = w.bl[2]; }
-    if (g1 < A.gqa) { A.ml[o1 * 2] = w.m1; A.ml[o1 * 2 + 1] = w.bl[3]; }
+    if (on0) *reinterpret_cast<float2*>(A.ml + o0 * 2) = make_float2(w.m0, w.bl[2]);
+    if (on1) *reinterpret_cast<float2*>(A.ml + o1 * 2) = make_float2(w.m1, w.bl[3]);
   }
 }
 __device__ __forceinline__ int ring_next(int st, int NS) { return st + 1 == NS ? 0 : st + 1; }
 
+// Teams per CTA: a CTA is V independent teams of H consumer warps + 1 producer warp, each with its own barriers,
+// plans, query copy and stage ring in its slice of the CTA's shared memory.  One CTA per SM: registers are handed
+// out per CTA for an even number of warps, so 18 warps in one CTA get 112 registers each where two CTAs of 9
+// warps (allocated as 10) would get 96.
+template <int H> struct Teams { static constexpr int V = H == 8 ? 2 : (H == 4 ? 3 : (H == 2 ? 5 : 8)); };
+
 template <int H>
-__global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) decode_mma_kernel(const Params P) {
-  extern __shared__ __align__(128) unsigned char smem[];
+__global__ void __launch_bounds__((H + 1) * 32 * Teams<H>::V, 1) decode_mma_kernel(const Params P) {
+  extern __shared__ __align__(128) unsigned char smem_all[];
+  constexpr int TEAM_THREADS = (H + 1) * 32;
   const LayoutDev& L = P.L;
   const DecodeArgs& A = P.A;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int team = threadIdx.x / TEAM_THREADS, tid = threadIdx.x - team * TEAM_THREADS;
+  const int warp = tid >> 5, lane = tid & 31;
   const int NS = P.NS;
   const int n_items = P.num_seqs * A.num_splits;
   constexpr int SB = stage_bytes(H);
@@ -786,18 +819,18 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
   const long long cta_c0 = clock64();
 #endif
 
-  // shared memory: [barriers | lock][tile plans][remap][query copy per head][stage ring]
+  // shared memory of a team: [barriers | lock][tile plans][remap][query copy per head][stage ring]
+  unsigned char* smem = smem_all + (size_t)team * P.team_bytes;
   uint64_t* sfull = reinterpret_cast<uint64_t*>(smem);   // stage ring: header written, copies landed
   uint64_t* sempty = sfull + MAX_NS;                     // stage ring: every consumer warp is done with the stage
   int* lock = reinterpret_cast<int*>(sempty + MAX_NS);
   TilePlan* plan = reinterpret_cast<TilePlan*>(smem + HDR_BYTES);
   float* remap = reinterpret_cast<float*>(smem + HDR_BYTES + UNIT * sizeof(TilePlan));
   unsigned char* qs = reinterpret_cast<unsigned char*>(remap) + REMAP_BYTES;
-  const int q_rows = A.gqa + 1;
-  unsigned char* ring = qs + H * q_head_bytes(q_rows);
+  unsigned char* ring = qs + (q_copy_bytes(H, A.gqa) + 127) / 128 * 128;
   const uint32_t ring_u = smem_u32(ring), full_u = smem_u32(sfull), empty_u = smem_u32(sempty);
 
-  if (threadIdx.x == 0) {
+  if (tid == 0) {
     for (int s = 0; s < MAX_NS; ++s) { mbar_init(sfull + s, 1); mbar_init(sempty + s, H * 32); }
     *lock = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -805,10 +838,10 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
   {  // zero the ring once: rows of a partial tile that are never copied must read as finite numbers
     const int n16 = (NS * SB) / 16;
     uint4* z = reinterpret_cast<uint4*>(ring);
-    for (int i = threadIdx.x; i < n16; i += (H + 1) * 32) z[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < n16; i += TEAM_THREADS) z[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
-    if (threadIdx.x < NS)  // the row of ones the [v_min | ones] operand reads: no copy ever lands on it
-      *reinterpret_cast<uint4*>(ring + (size_t)threadIdx.x * SB + o_ones(H)) = make_uint4(0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u);
+    if (tid < NS)  // the row of ones the [v_min | ones] operand reads: no copy ever lands on it
+      *reinterpret_cast<uint4*>(ring + (size_t)tid * SB + o_ones(H)) = make_uint4(0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the bulk copies write the same bytes later
   }
   __syncthreads();
@@ -841,13 +874,15 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
     // Fill one stage: wait until the consumers have released it, write the header, start the copies.
     // `rows`: 0 = no token rows (header only), 1 = whole [K | V] rows in pairs, 2 = K sides, 3 = V sides (INT8).
     auto fill = [&](const TilePlan& d, int flags_extra, int rows) -> bool {
-      if (!mbar_wait(empty_u + st * 8, (pph >> st) & 1)) return false;
+      if (!mbar_wait(empty_u + st * 8, (pph >> st) & 1, P.wait_ns)) return false;
       pph ^= 1u << st;
       const int4 h0 = *reinterpret_cast<const int4*>(&d.hdr);   // bits, n_valid, flags, pos0
       const uint32_t bar = full_u + st * 8, st_u = ring_u + (uint32_t)st * SB;
       const int nv = h0.y;
       const uint32_t side = 16u * H * h0.x;                     // bytes of one side (K or V) of a token row: H * D * bits / 8
       const uint32_t k_stats = 2u * H * D * 2, v_stats = 2u * TILE * H * NG * 2;
+      const int rt = min((2 * L.BS) / h0.x, TILE);              // token rows per run (see TilePlan)
+      auto row_src = [&](int t) { return d.run[t / rt] + (uint32_t)(t % rt) * 2u * side; };
       if (lane == 0) {
         int4* hd = reinterpret_cast<int4*>(ring + (size_t)st * SB + o_hdr(H));
         hd[0] = make_int4(h0.x, h0.y, h0.z | flags_extra, h0.w);
@@ -858,10 +893,10 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
       __syncwarp();
       if (rows == 1) {
         // lane p < 8 copies tokens 2p and 2p + 1 in one piece (neighbours in their chunk: a chunk holds an even number of tokens)
-        if (lane < 8) { if (2 * lane < nv) bulk_copy(st_u + lane * slot_bytes(H), d.row_src[2 * lane], (2 * lane + 1 < nv ? 4u : 2u) * side, bar); }
+        if (lane < 8) { if (2 * lane < nv) bulk_copy(st_u + lane * slot_bytes(H), row_src(2 * lane), (2 * lane + 1 < nv ? 4u : 2u) * side, bar); }
       } else {
         // lane t < 16 copies one side of token t to its half of slot t / 2
-        if (lane < TILE && lane < nv) bulk_copy(st_u + (lane >> 1) * slot_bytes(H) + (lane & 1) * side, d.row_src[lane] + (rows == 3 ? side : 0u), side, bar);
+        if (lane < TILE && lane < nv) bulk_copy(st_u + (lane >> 1) * slot_bytes(H) + (lane & 1) * side, row_src(lane) + (rows == 3 ? side : 0u), side, bar);
       }
       if (contig) {
         if (lane == 16 && rows != 2) bulk_copy(st_u + o_vs(H), d.stats[0], v_stats, bar);
@@ -875,7 +910,7 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
       st = ring_next(st, NS);
       return true;
     };
-    bool more = advance();
+    bool more = P.idle_producer ? false : advance();
     BlockMeta nxt = more ? load_meta(P, bt_row, lane < U ? base + lane : b_end, b_end) : BlockMeta{};
     while (more && ok) {
       const BlockMeta cur = nxt;
@@ -909,17 +944,12 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
           const bool in_res = ks_slot >= 0 && grp == kgrp;
           const unsigned char* page = P.pages + (int64_t)kblk * L.PS;
           TilePlan& d = plan[lane];
-          int jc = t0 / tpc, in_chunk = t0 - jc * tpc;      // chunk of the tile's first token, position inside it
-          const unsigned char* chunk = nullptr;
-          for (int t = 0; t < TILE; ++t) {
-            if (t == 0 || in_chunk == tpc) {
-              if (t) { ++jc; in_chunk = 0; }
-              int64_t pg = kblk, cs = 0;
-              if (jc > 0) { const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3); pg = id / L.KC; cs = id - pg * L.KC; }
-              chunk = P.pages + pg * L.PS + L.o_data + cs * L.CB;
-            }
-            d.row_src[t] = chunk + (int64_t)in_chunk * row_bytes;
-            ++in_chunk;
+          const int rt = min(tpc, TILE);                    // token rows per run: the tile's part of one chunk
+          for (int rr = 0; rr < TILE / rt; ++rr) {
+            const int tok = t0 + rr * rt, jc = tok / tpc;     // chunk of the run's first token
+            int64_t pg = kblk, cs = 0;
+            if (jc > 0) { const int id = jc == 1 ? c1 : (jc == 2 ? c2 : c3); pg = id / L.KC; cs = id - pg * L.KC; }
+            d.run[rr] = P.pages + pg * L.PS + L.o_data + cs * L.CB + (int64_t)(tok - jc * tpc) * row_bytes;
           }
           const int nv = min(TILE, blk_tok - t0);
           d.hdr.bits = bits; d.hdr.n_valid = nv;
@@ -949,8 +979,8 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
       __syncwarp();  // every lane is done reading the plans before the next unit overwrites them
       ok = !__any_sync(0xffffffffu, !ok);
     }
-    if (ok) {  // no more work: tell the consumers
-      if (mbar_wait(empty_u + st * 8, (pph >> st) & 1)) {
+    if (ok && !P.idle_producer) {  // no more work: tell the consumers
+      if (mbar_wait(empty_u + st * 8, (pph >> st) & 1, P.wait_ns)) {
         if (lane == 0) {
           reinterpret_cast<int4*>(ring + (size_t)st * SB + o_hdr(H))[0] = make_int4(2, -1, 0, 0);
           mbar_arrive(full_u + st * 8);
@@ -964,19 +994,20 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
       // time before the CTA's shared memory goes away.
       for (int s = 0; s < NS; ++s) {
         const uint32_t uses = fills > (uint32_t)s ? (fills - s + NS - 1) / NS : 0;
-        if (uses > 0) mbar_wait(full_u + s * 8, (uses - 1) & 1);
+        if (uses > 0) mbar_wait(full_u + s * 8, (uses - 1) & 1, P.wait_ns);
       }
     }
   } else {
     // ===================== consumers: warp h owns KV head h =====================
     Lane ln;
     ln.h = warp; ln.lane = lane; ln.r = lane >> 2; ln.j = lane & 3;
-    unsigned char* qn = qs + ln.h * q_head_bytes(q_rows);
-    {  // query columns >= gqa of the MMAs read the shared zero row
-      const int my_row = ln.r < A.gqa ? ln.r : A.gqa, ld_row = (lane & 7) < A.gqa ? (lane & 7) : A.gqa;
-      ln.qn_lane = smem_u32(qn + my_row * QN_ROW);
-      ln.qn_ld = smem_u32(qn + ld_row * QN_ROW + (lane >> 3) * 16);
-      for (int i = lane; i < D / 2; i += 32) *reinterpret_cast<uint32_t*>(qn + A.gqa * QN_ROW + i * 4) = 0u;
+    unsigned char* qn = qs + ln.h * A.gqa * QN_ROW;
+    {  // query columns >= gqa of the MMAs read the team's zero row (every warp writes the same zeros)
+      unsigned char* zero = qs + H * A.gqa * QN_ROW;
+      ln.qn_lane = smem_u32(ln.r < A.gqa ? qn + ln.r * QN_ROW : zero);
+      ln.qn_ld = smem_u32(((lane & 7) < A.gqa ? qn + (lane & 7) * QN_ROW : zero) + (lane >> 3) * 16);
+      for (int i = lane; i < D / 2; i += 32) *reinterpret_cast<uint32_t*>(zero + i * 4) = 0u;
+      __syncwarp();
     }
     ln.vs_row = o_vs(H) + (uint32_t)(2 * ln.r * H + ln.h) * NG * 2;  // token 2r; token 2r + 1 (MMA row r + 8) is one token further
     // [v_min | ones] operand, read transposed: matrices 0 / 2 = v_min of the even / odd tokens (k order: tokens 0,2,..,14
@@ -988,7 +1019,7 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
     int c_st = 0;                  // stage being consumed
     uint32_t cph = 0;              // per stage: parity of the `full` phase to wait for
     WarpState w;
-    w.bits = 0; w.qbits = 0;
+    w.bits = 0;
     w.m0 = w.m1 = -INFINITY;
 #pragma unroll
     for (int mt = 0; mt < 8; ++mt) { w.acc[mt][0] = w.acc[mt][1] = w.acc[mt][2] = w.acc[mt][3] = 0.f; }
@@ -999,7 +1030,7 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
     long long res_slot = -1;
     // Wait for the stage at the head of the ring and read its header; false when a wait ran out.
     auto fetch = [&]() -> bool {
-      if (!mbar_wait(full_u + c_st * 8, (cph >> c_st) & 1)) return false;  // header written, copies landed
+      if (!mbar_wait(full_u + c_st * 8, (cph >> c_st) & 1, P.wait_ns)) return false;  // header written, copies landed
       uint32_t hd[4], ex[4];
       const uint32_t ha = ring_u + (uint32_t)c_st * SB + o_hdr(H);
       lds128<0>(hd, ha);
@@ -1055,7 +1086,6 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
       w.bl[0] = w.bl[1] = w.bl[2] = w.bl[3] = 0.f;
       w.m0 = w.m1 = -INFINITY;
       w.bits = 0;
-      w.qbits = 0;
     };
     // Kinds of groups; each kind is worked off in a loop of its own for as long as groups of that kind follow one
     // another (one tier per layer is the common case), so that the loop body holds a single code path.
@@ -1076,7 +1106,7 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
         const uint32_t sb0 = ring_u + (uint32_t)c_st * SB;
         const int st1 = ring_next(c_st, NS);
         const uint32_t sb1 = ring_u + (uint32_t)st1 * SB;
-        if (TWO && !mbar_wait(full_u + st1 * 8, (cph >> st1) & 1)) { ok = false; break; }
+        if (TWO && !mbar_wait(full_u + st1 * 8, (cph >> st1) & 1, P.wait_ns)) { ok = false; break; }
         PROF_T(r1);
         PROF_PHASE(4, r0, r1);  // item start + wait for the second stage
         const bool last = (flags & F_LAST) != 0;
@@ -1128,11 +1158,12 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
   }
   if (!ok && lane == 0 && P.status) atomicExch(P.status, 1);
 #ifdef ECHOKV_PROFILE
-  if (threadIdx.x == 0 && blockIdx.x < 1024) {
+  if (tid == 0 && blockIdx.x * Teams<H>::V + team < 1024) {
+    const int slot = blockIdx.x * Teams<H>::V + team;
     unsigned int smid;
     asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    g_cta[blockIdx.x * 4 + 0] = cta_t0; g_cta[blockIdx.x * 4 + 1] = global_ns();
-    g_cta[blockIdx.x * 4 + 2] = smid; g_cta[blockIdx.x * 4 + 3] = (unsigned long long)(clock64() - cta_c0);
+    g_cta[slot * 4 + 0] = cta_t0; g_cta[slot * 4 + 1] = global_ns();
+    g_cta[slot * 4 + 2] = smid; g_cta[slot * 4 + 3] = (unsigned long long)(clock64() - cta_c0);
   }
 #endif
 }
@@ -1140,6 +1171,8 @@ __global__ void __launch_bounds__((H + 1) * 32) __maxnreg__(H == 8 ? 112 : 128) 
 }  // namespace mma
 
 static int g_decode_path = 0;  // 0: pick by shape, 1: always the generic kernel
+static unsigned long long g_wait_ns = mma::WAIT_NS;  // see echokv_set_decode_wait_limit
+static int g_idle_producer = 0;
 static cudaEvent_t g_ev_before = nullptr, g_ev_after = nullptr;  // optional timing hook around the split kernel
 
 // Raised by decode_mma_kernel: 1 = a bounded wait ran out.
@@ -1204,33 +1237,29 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   P.counter = counter;
   P.q_vec16 = (A.q_dt != ECHOKV_DT_F32) && (reinterpret_cast<uintptr_t>(A.q) % 16 == 0) && A.q_s0 % 8 == 0 && A.q_s1 % 8 == 0;
   P.status = status ? status : dv->status_word;
-  const int fixed = HDR_BYTES + UNIT * (int)sizeof(TilePlan) + REMAP_BYTES + H * q_head_bytes(A.gqa + 1);
+  P.wait_ns = g_wait_ns;
+  P.idle_producer = g_idle_producer;
+  const int fixed = HDR_BYTES + UNIT * (int)sizeof(TilePlan) + REMAP_BYTES + (q_copy_bytes(H, A.gqa) + 127) / 128 * 128;
   const int sbytes = stage_bytes(H);
-  // CTAs per SM: bounded by warps (16 consumer warps per SM is the target) and shared memory
-  // (each SM has ~228 KB, 1 KB of it reserved per CTA)
-  int per_sm = 16 / H;
-  if (per_sm < 2) per_sm = 2;
-  if (per_sm > 8) per_sm = 8;
-  int ns = 0;
-  for (; per_sm >= 1; --per_sm) {
-    const int budget = (dv->max_smem + 1024) / per_sm - 1024;
-    ns = (budget - fixed) / sbytes;
-    if (ns > MAX_NS) ns = MAX_NS;
-    if (ns >= 4) break;  // a group of two stages in work and one in flight at the least
-  }
-  if (per_sm < 1 || ns < 4) return ECHOKV_OK;
+  // One CTA per SM holding V teams; every team gets an equal slice of the SM's shared memory.
+  const int V = H == 8 ? Teams<8>::V : H == 4 ? Teams<4>::V : H == 2 ? Teams<2>::V : Teams<1>::V;
+  const int budget = (dv->max_smem / V) / 128 * 128;
+  int ns = (budget - fixed) / sbytes;
+  if (ns > MAX_NS) ns = MAX_NS;
+  if (ns < 4) return ECHOKV_OK;  // a group of two stages in work and one in flight at the least
   P.NS = ns;
-  const int smem_bytes = fixed + ns * sbytes;
-  int64_t grid = (int64_t)dv->num_sms * per_sm;
+  P.team_bytes = (fixed + ns * sbytes + 127) / 128 * 128;
+  const int smem_bytes = P.team_bytes * V;
   const int64_t n_items = num_seqs * (int64_t)A.num_splits;
-  if (grid > n_items) grid = n_items;
+  int64_t grid = dv->num_sms;
+  if (grid * V > n_items) grid = (n_items + V - 1) / V;
   if (cudaMemsetAsync(counter, 0, sizeof(int), st) != cudaSuccess) return check_launch("decode (work counter)");
   if (g_ev_before) cudaEventRecord(g_ev_before, st);
   switch (H) {
-    case 1: decode_mma_kernel<1><<<(unsigned)grid, 2 * 32, smem_bytes, st>>>(P); break;
-    case 2: decode_mma_kernel<2><<<(unsigned)grid, 3 * 32, smem_bytes, st>>>(P); break;
-    case 4: decode_mma_kernel<4><<<(unsigned)grid, 5 * 32, smem_bytes, st>>>(P); break;
-    default: decode_mma_kernel<8><<<(unsigned)grid, 9 * 32, smem_bytes, st>>>(P); break;
+    case 1: decode_mma_kernel<1><<<(unsigned)grid, 2 * 32 * Teams<1>::V, smem_bytes, st>>>(P); break;
+    case 2: decode_mma_kernel<2><<<(unsigned)grid, 3 * 32 * Teams<2>::V, smem_bytes, st>>>(P); break;
+    case 4: decode_mma_kernel<4><<<(unsigned)grid, 5 * 32 * Teams<4>::V, smem_bytes, st>>>(P); break;
+    default: decode_mma_kernel<8><<<(unsigned)grid, 9 * 32 * Teams<8>::V, smem_bytes, st>>>(P); break;
   }
   if (g_ev_after) cudaEventRecord(g_ev_after, st);
   rc = check_launch("decode (tensor-core kernel)");
@@ -1255,6 +1284,12 @@ extern "C" int echokv_debug_phase(unsigned long long* dst, int reset) {
 extern "C" int echokv_set_decode_events(void* before, void* after) {
   echokv::g_ev_before = reinterpret_cast<cudaEvent_t>(before);
   echokv::g_ev_after = reinterpret_cast<cudaEvent_t>(after);
+  return ECHOKV_OK;
+}
+
+extern "C" int echokv_set_decode_wait_limit(int64_t limit_ns, int idle_producer) {
+  echokv::g_wait_ns = limit_ns > 0 ? (unsigned long long)limit_ns : echokv::mma::WAIT_NS;
+  echokv::g_idle_producer = idle_producer != 0;
   return ECHOKV_OK;
 }
 

@@ -23,7 +23,8 @@ def register() -> None:
     if enabled():
         from vllm.v1.attention.backends import registry
 
-        from echokv_b200 import host_slots
+        from echokv_b200 import host_slots, vllm_compat
 
         host_slots.install()
+        vllm_compat.install()  # page size on vLLM releases without AttentionBackend.customize_spec
         registry.register_backend(registry.AttentionBackendEnum.CUSTOM, BACKEND_PATH)

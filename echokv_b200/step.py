@@ -226,11 +226,31 @@ class GroupRunner:
         kref = self._kref_all if self._kref_all is not None else torch.stack(self.krefs)
         stash = self._stash_all if self._stash_all is not None else torch.stack(self.stashes)
         deltas = canary_kl_ring(stash[:, :nq], kref, pl.kref_pos, pl.kref_fill, self.layout.k_group, self.scale)
-        return tp_mean(deltas, tp_group)
+        deltas = tp_mean(deltas, tp_group)
+        # Start the copy to pinned host memory now, so that `observe` (one measurement later) only waits for an
+        # event that has long passed instead of synchronizing the stream.
+        turn = self._canary_turn = (getattr(self, "_canary_turn", 0) + 1) % 2
+        if not hasattr(self, "_canary_host"):
+            self._canary_host = [torch.zeros(deltas.shape, dtype=torch.float32).pin_memory() for _ in range(2)]
+            self._canary_done = [torch.cuda.Event() for _ in range(2)]
+            self._canary_of = [None, None]
+        self._canary_host[turn].copy_(deltas, non_blocking=True)
+        self._canary_done[turn].record()
+        self._canary_of[turn] = deltas
+        return deltas
 
     def observe(self, deltas: torch.Tensor, ctx_len: float) -> None:
-        """Feed a finished measurement to every layer's controller (reads it back to the host)."""
-        for ctl, row in zip(self.controllers, deltas.tolist()):
+        """Feed a finished measurement to every layer's controller.  A measurement that came from
+        `measure_canary` is read from its pinned host copy (the reference reads the previous measurement for
+        the same reason, backend.py:316-326); anything else is read back from the device."""
+        rows = None
+        for k in range(2 if hasattr(self, "_canary_of") else 0):
+            if self._canary_of[k] is deltas:
+                self._canary_done[k].synchronize()
+                rows = self._canary_host[k].tolist()
+        if rows is None:
+            rows = deltas.tolist()
+        for ctl, row in zip(self.controllers, rows):
             ctl.observe(dict(zip(SUPPORTED_BITS, row)), ctx_len)
 
     # -- device side, per layer ---------------------------------------------------------------

@@ -239,6 +239,13 @@ int echokv_set_prefill_path(int path);
  * the reference. */
 int echokv_kernel_status(int clear);
 
+/* How long a wait inside the tensor-core decode kernel may last before it gives up (nanoseconds; <= 0 restores the
+ * default of 2 s), and a test hook: with `idle_producer` != 0 the kernel's producer warps stage nothing, so every
+ * consumer's first wait runs out, the kernel returns normally with no copy in flight, its output is undefined and
+ * echokv_kernel_status reports bit 0.  Process-wide; meant for tests of the give-up path.  No counterpart in the
+ * reference. */
+int echokv_set_decode_wait_limit(int64_t limit_ns, int idle_producer);
+
 /* Canary attention-KL estimator, batched over layers -- canary_kl (canary.py:59-89).
  * query [L, nq, Hq, D] of q_dtype, kref float32 [L, W, H, D] oldest key first (ring
  * already unrolled: row (ring_pos + i) % W when ring_fill == W).  Scores the last

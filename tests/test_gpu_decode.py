@@ -224,3 +224,29 @@ def test_captured_graph_keeps_its_scratch_when_a_larger_eager_call_follows():
     torch.cuda.synchronize()
     assert torch.equal(out, want)
     assert torch.isfinite(big).all() and junk.numel() > 0
+
+
+def test_a_wait_that_runs_out_raises_the_status_word_and_the_next_launch_is_fine():
+    """The give-up path of the bounded waits: with the producer warps idle (a test hook) nothing is ever staged, every
+    consumer's first wait runs out after the (shortened) limit, the kernel returns by itself with no copy in flight and
+    the status word reports it once; the following ordinary launch gives the ordinary result."""
+    import torch
+    from echokv_b200 import _native as N
+    from echokv_b200.kernels.decode import decode_attention
+
+    sc = next(s for s in DEC if s.name == "decode_bs16_bf16")
+    store, q, table, lens, _ = _store_and_inputs(sc)
+    want = decode_attention(store, q, table, lens, sc.scale)
+    torch.cuda.synchronize()
+    assert N.lib.echokv_kernel_status(1) == 0
+    N.lib.echokv_set_decode_wait_limit(20_000_000, 1)  # 20 ms, idle producer
+    try:
+        decode_attention(store, q, table, lens, sc.scale)
+        torch.cuda.synchronize()
+    finally:
+        N.lib.echokv_set_decode_wait_limit(0, 0)
+    assert N.lib.echokv_kernel_status(1) & 1  # raised ...
+    assert N.lib.echokv_kernel_status(1) == 0  # ... and cleared by the read
+    got = decode_attention(store, q, table, lens, sc.scale)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want) and N.lib.echokv_kernel_status(1) == 0

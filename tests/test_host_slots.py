@@ -164,3 +164,48 @@ def test_plugin_entry_point_is_declared(tmp_path, monkeypatch):
     register = eps[0].load()
     monkeypatch.delenv("ECHOKV_ENABLE", raising=False)
     register()  # without ECHOKV_ENABLE=1 the call touches nothing (plugin.py:17-28 of the reference)
+
+
+def test_page_size_shim_for_vllm_without_customize_spec(monkeypatch):
+    """On vLLM releases that lack ``AttentionBackend.customize_spec`` the plugin makes the attention layers it serves
+    declare their page through ``TQFullAttentionSpec``: page bytes = block_size * bytes per token of the tiered store
+    (rounded up to whole slots per head), and the backend's cache shape covers exactly that page."""
+    import types
+
+    import pytest
+    import torch
+
+    vllm = pytest.importorskip("vllm")  # noqa: F841
+    from echokv_b200 import vllm_compat
+    from echokv_b200.tiered_cache import TieredLayout
+
+    if not vllm_compat.needs_spec_patch():
+        pytest.skip("this vLLM has customize_spec; the shim is not used")
+    monkeypatch.setenv("ECHOKV_MEM_BITS", "4")
+    monkeypatch.setenv("ECHOKV_K_GROUP", "32")
+    from vllm.model_executor.layers.attention.attention import Attention
+    from vllm.v1.attention.backend import AttentionType
+    from vllm.v1.kv_cache_interface import FullAttentionSpec, TQFullAttentionSpec
+
+    from echokv_b200.backend import EchoKVAttentionBackend
+
+    assert vllm_compat.install()
+    cfg = types.SimpleNamespace(cache_config=types.SimpleNamespace(block_size=64),
+                                model_config=types.SimpleNamespace(use_mla=False))
+
+    def layer(backend):
+        return types.SimpleNamespace(attn_type=AttentionType.DECODER, kv_cache_dtype="auto", sliding_window=None, num_kv_heads=8,
+                                     head_size=128, head_size_v=128, kv_cache_torch_dtype=torch.bfloat16,
+                                     get_attn_backend=lambda: backend)
+
+    ours = Attention.get_kv_cache_spec(layer(EchoKVAttentionBackend), cfg)
+    assert isinstance(ours, TQFullAttentionSpec)
+    per_token = TieredLayout.per_token_bytes(8, 128, 4, 32, 32)
+    assert per_token == 1284 and vllm_compat.slot_bytes(8, 128) == 164
+    assert ours.page_size_bytes == 64 * 8 * 164 >= 64 * per_token
+    stock = FullAttentionSpec(block_size=64, num_kv_heads=8, head_size=128, dtype=torch.bfloat16)
+    assert stock.page_size_bytes / ours.page_size_bytes > 3.0  # the capacity the reference advertises for INT4
+    shape = EchoKVAttentionBackend.get_kv_cache_shape(10, 64, 8, 128)
+    assert shape[0] == 10 and shape[1] == 1 and shape[2] == 64
+    other = Attention.get_kv_cache_spec(layer(type("Other", (), {"__module__": "vllm.somewhere"})), cfg)
+    assert type(other) is FullAttentionSpec
