@@ -140,9 +140,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
     if (global_ns() - t0 > limit_ns) return false;
   }
 }
-__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+// The pages are read once per launch: their lines are marked evict-first in L2, so that what is read again (queries,
+// block tables, split partials) stays there.
+__device__ __forceinline__ uint64_t stream_policy() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+}
+// Ask for `bytes` (a multiple of 16) at `src` (16-byte aligned) to be brought into L2.
+__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 // Compile-time loop: the index is an integral constant, so it can feed template arguments.
 template <class F, int... I>
@@ -352,15 +363,19 @@ struct Lane {
   uint32_t vs_row;    // stage offset of the V scales of token 2r (this head, all groups): 8 bytes; token 2r + 1 is H * 8 further
   uint32_t vm_ld;     // stage offset of this lane's ldmatrix row of the [v_min | ones] operand
   uint32_t km_ld;     // stage offset of this lane's ldmatrix row of the broadcast k_min operand (tile by lane & 8)
+  uint32_t vs_row8;   // INT8 stages (eight tokens in natural order): V scales of token r of the stage
+  uint32_t vm_ld8;    // INT8 stages: this lane's ldmatrix row of the [v_min | ones] operand (stage by lane & 16)
 };
 
 // This lane's ldmatrix row offset inside a stage for the K side / V side of tier BITS: lane & 7 picks the slot
 // (tokens 2p, 2p + 1), lane & 8 the odd token of the slot, lane >> 4 the second 16-byte piece of the row.
+// INT8 tiles lie in two stages of eight token rows each (tokens 0..7 and 8..15 in their natural order: MMA row r is
+// token r): there lane & 7 picks the token of the stage and lane & 8 the stage.
 template <int BITS, int H>
 __device__ __forceinline__ uint32_t code_row(const Lane& ln, bool v_side) {
   const uint32_t pr = ln.lane & 7, odd = (ln.lane >> 3) & 1, piece = (ln.lane >> 4) * 16u;
-  if constexpr (BITS == 8)  // K and V live in stages of their own: a token row there is the 128 * H bytes of one side
-    return pr * slot_bytes(H) + odd * (128u * H) + ln.h * 128u + piece;
+  if constexpr (BITS == 8)  // a stage holds eight whole token rows, one per slot; the caller picks the stage by lane & 8
+    return pr * slot_bytes(H) + ln.h * 128u + piece + (v_side ? 128u * H : 0u);
   else if constexpr (BITS == 4)
     return pr * slot_bytes(H) + odd * (128u * H) + ln.h * 64u + piece + (v_side ? 64u * H : 0u);
   else
@@ -380,11 +395,11 @@ __device__ __forceinline__ uint32_t code_row(const Lane& ln, bool v_side) {
 // query (ldmatrix over the 8 query rows).  c2[0], c2[1]: first tile, query heads 2j, 2j+1; c2[2], c2[3]: second.
 // The chains (one or two per tile, and this one) are interleaved so that no MMA waits for the one before it.
 template <int BITS, int H, int NT>
-__device__ __forceinline__ void qk_scores(const Lane& ln, const uint32_t (&sbk)[NT], float (&c)[NT][4], float (&c2)[4]) {
+__device__ __forceinline__ void qk_scores(const Lane& ln, const uint32_t (&sbk)[NT], uint32_t sb_hi, float (&c)[NT][4], float (&c2)[4]) {
   uint32_t krow[NT], ks[NT];
 #pragma unroll
   for (int t = 0; t < NT; ++t) {
-    krow[t] = sbk[t] + code_row<BITS, H>(ln, false);
+    krow[t] = (BITS == 8 && (ln.lane & 8) ? sb_hi : sbk[t]) + code_row<BITS, H>(ln, false);
     ks[t] = sbk[t] + o_ks(H) + ln.h * (D * 2);
   }
   const uint32_t km_ld = ((ln.lane & 8) ? sbk[NT - 1] : sbk[0]) + ln.km_ld;
@@ -502,12 +517,13 @@ __device__ __forceinline__ uint32_t res_pair(const ResidualDev& R, int64_t e) {
   return pack_h2(x, y);
 }
 __device__ __noinline__ float4 qk_residual(const ResidualDev R, long long res_slot, int pos0, int n_valid, uint32_t qn_lane,
-                                           int h, int lane) {
+                                           int h, int lane, int natural) {
   float c[4] = {0.f, 0.f, 0.f, 0.f};
   const int r = lane >> 2, j = lane & 3;
-  const bool v0 = 2 * r < n_valid, v1 = 2 * r + 1 < n_valid;  // MMA rows r / r + 8 are tokens 2r / 2r + 1
-  const int64_t e0 = res_slot * R.s_slot + (int64_t)(pos0 + 2 * r) * R.s_pos + h * R.s_head;
-  const int64_t e1 = e0 + R.s_pos;
+  const int t0 = natural ? r : 2 * r, t1 = natural ? r + 8 : 2 * r + 1;  // tokens of MMA rows r / r + 8
+  const bool v0 = t0 < n_valid, v1 = t1 < n_valid;
+  const int64_t e0 = res_slot * R.s_slot + (int64_t)(pos0 + t0) * R.s_pos + h * R.s_head;
+  const int64_t e1 = e0 + (int64_t)(t1 - t0) * R.s_pos;
   const uint32_t qb = qn_lane + j * 8;
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
@@ -528,29 +544,36 @@ __device__ __noinline__ float4 qk_residual(const ResidualDev R, long long res_sl
 // each, all groups), one fragment pair per group.  INT2: the scale goes into the codes, which needs it
 // per token pair (the order of the A fragments).
 template <int BITS, int H>
-__device__ __forceinline__ void pv_codes(const Lane& ln, uint32_t sb, uint32_t p_lo, uint32_t p_hi, WarpState& w) {
-  const uint32_t vrow = sb + code_row<BITS, H>(ln, true);
-  const uint32_t vs_row = sb + ln.vs_row;
+// `sb`: the tile's stage (INT8: the stage of tokens 0..7), `sb_hi`: the stage of tokens 8..15 of an INT8 tile.
+__device__ __forceinline__ void pv_codes(const Lane& ln, uint32_t sb, uint32_t sb_hi, uint32_t p_lo, uint32_t p_hi, WarpState& w) {
+  const uint32_t vrow = (BITS == 8 && (ln.lane & 8) ? sb_hi : sb) + code_row<BITS, H>(ln, true);
   const uint32_t pb0 = movm_t(p_lo), pb1 = movm_t(p_hi);
   // [v_min | ones] rows: the bias of every V group and the softmax denominator
   if constexpr (H >= 2) {
     uint32_t X[4];
-    ldsm_x4_t<0>(X, sb + ln.vm_ld);  // (v_min of even tokens, ones, v_min of odd tokens, ones): rows = groups of this pair of heads
+    // (v_min of k slots 0..7, ones, v_min of k slots 8..15, ones): rows = groups of this pair of heads
+    if constexpr (BITS == 8) ldsm_x4_t<0>(X, ((ln.lane & 16) ? sb_hi : sb) + ln.vm_ld8);
+    else ldsm_x4_t<0>(X, sb + ln.vm_ld);
     mma16816(w.bl, X[0], X[1], X[2], X[3], pb0, pb1);
   } else {
-    const uint32_t base = sb + o_vm(H) + (uint32_t)(4 * ln.j) * NG * 2 + (ln.r < NG ? ln.r : 0) * 2, tok = NG * 2;
+    // k slots 2j, 2j+1, 2j+8, 2j+9 are tokens 4j, 4j+2, 4j+1, 4j+3 (INT8: tokens 2j, 2j+1 of either stage)
+    const uint32_t g2 = (ln.r < NG ? ln.r : 0) * 2, tok = NG * 2;
+    const uint32_t base = sb + o_vm(H) + (uint32_t)((BITS == 8 ? 2 : 4) * ln.j) * tok + g2;
+    const uint32_t base_hi = BITS == 8 ? sb_hi + o_vm(H) + (uint32_t)(2 * ln.j) * tok + g2 : base + tok;
     uint32_t x0, x1, x2, x3;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x0) : "r"(base));            // token 4j     (k slot 2j)
-    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x1) : "r"(base + 2 * tok));  // token 4j + 2 (k slot 2j + 1)
-    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x2) : "r"(base + tok));      // token 4j + 1 (k slot 2j + 8)
-    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x3) : "r"(base + 3 * tok));  // token 4j + 3 (k slot 2j + 9)
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x0) : "r"(base));                                   // k slot 2j
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x1) : "r"(base + (BITS == 8 ? 1 : 2) * tok));       // k slot 2j + 1
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x2) : "r"(base_hi));                                // k slot 2j + 8
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(x3) : "r"(base_hi + (BITS == 8 ? 1 : 2) * tok));    // k slot 2j + 9
     const uint32_t keep = ln.r < NG ? 0xffffffffu : 0u;
     mma16816(w.bl, prmt(x0, x1, 0x5410u) & keep, 0x3c003c00u, prmt(x2, x3, 0x5410u) & keep, 0x3c003c00u, pb0, pb1);
   }
+  const uint32_t vs_row = sb + (BITS == 8 ? ln.vs_row8 : ln.vs_row);
   if constexpr (BITS != 2) {
     uint32_t b0[NG], b1[NG];
     {
-      const uint2 s0 = lds64<0>(vs_row), s1 = lds64<H * NG * 2>(vs_row);
+      // V scales (all four groups, 8 bytes) of this lane's two tokens: MMA rows r and r + 8
+      const uint2 s0 = lds64<0>(vs_row), s1 = BITS == 8 ? lds64<0>(sb_hi + ln.vs_row8) : lds64<H * NG * 2>(vs_row);
       b0[0] = movm_t(hmul2_lo(p_lo, s0.x)); b0[1] = movm_t(hmul2_hi(p_lo, s0.x));
       b0[2] = movm_t(hmul2_lo(p_lo, s0.y)); b0[3] = movm_t(hmul2_hi(p_lo, s0.y));
       b1[0] = movm_t(hmul2_lo(p_hi, s1.x)); b1[1] = movm_t(hmul2_hi(p_hi, s1.x));
@@ -653,12 +676,12 @@ __device__ __forceinline__ void process_group(const Params& P, const Lane& ln, c
 #pragma unroll
   for (int t = 0; t < NT; ++t) c[t][0] = c[t][1] = c[t][2] = c[t][3] = 0.f;
   if (NT == 1 && in_res) {
-    const float4 s4 = qk_residual(P.R, res_slot, pos0, n_valid, ln.qn_lane, ln.h, ln.lane);
+    const float4 s4 = qk_residual(P.R, res_slot, pos0, n_valid, ln.qn_lane, ln.h, ln.lane, BITS == 8);
     c[0][0] = s4.x; c[0][1] = s4.y; c[0][2] = s4.z; c[0][3] = s4.w;
   } else {
     // scores in code units; the k_min chain rides along
     float c2[4] = {0.f, 0.f, 0.f, 0.f};
-    qk_scores<BITS, H, NT>(ln, sbk, c, c2);
+    qk_scores<BITS, H, NT>(ln, sbk, sbv[0], c, c2);
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
 #pragma unroll
@@ -666,8 +689,9 @@ __device__ __forceinline__ void process_group(const Params& P, const Lane& ln, c
     }
   }
   if (NT == 1 && n_valid < TILE) {  // a partial tile (the sequence's last): tokens past the end do not count
-    if (2 * ln.r >= n_valid) { c[0][0] = -INFINITY; c[0][1] = -INFINITY; }      // MMA row r is token 2r
-    if (2 * ln.r + 1 >= n_valid) { c[0][2] = -INFINITY; c[0][3] = -INFINITY; }  // MMA row r + 8 is token 2r + 1
+    const int t0 = BITS == 8 ? ln.r : 2 * ln.r, t1 = BITS == 8 ? ln.r + 8 : 2 * ln.r + 1;  // tokens of MMA rows r / r + 8
+    if (t0 >= n_valid) { c[0][0] = -INFINITY; c[0][1] = -INFINITY; }
+    if (t1 >= n_valid) { c[0][2] = -INFINITY; c[0][3] = -INFINITY; }
   }
   PROF_T(f1);
   PROF_PHASE(0, f0, f1);
@@ -703,7 +727,7 @@ __device__ __forceinline__ void process_group(const Params& P, const Lane& ln, c
   PROF_T(f2);
   PROF_PHASE(1, f1, f2);
 #pragma unroll
-  for (int t = 0; t < NT; ++t) pv_codes<BITS, H>(ln, sbv[t], p_lo[t], p_hi[t], w);
+  for (int t = 0; t < NT; ++t) pv_codes<BITS, H>(ln, BITS == 8 ? sbk[t] : sbv[t], sbv[t], p_lo[t], p_hi[t], w);
   PROF_T(f3);
   PROF_PHASE(2, f2, f3);
   PROF_PHASE(3, 0, 1);  // groups
@@ -852,6 +876,14 @@ __global__ void __launch_bounds__((H + 1) * 32 * Teams<H>::V, 1) decode_mma_kern
     const int tpb = L.BS / TILE;                     // tiles per block
     const int U = tpb >= UNIT ? 1 : UNIT / tpb;      // blocks per unit
     const bool contig = L.BS == TILE && L.KG == TILE;  // a tile's four stats arrays form one run in the page
+    const uint64_t policy = stream_policy();
+    if (P.q_vec16 && A.q_s1 == D) {  // the batch's query rows into L2 now: a work item's first step is to read one
+      const int elt = 2, teams = gridDim.x * Teams<H>::V, me = blockIdx.x * Teams<H>::V + team;
+      for (int sq = me * 32 + lane; sq < P.num_seqs; sq += teams * 32) {
+        const int64_t q_row = A.q_rows ? A.q_rows[sq] : sq;
+        l2_prefetch(reinterpret_cast<const unsigned char*>(A.q) + q_row * A.q_s0 * elt, (uint32_t)(A.Hq * D * elt));
+      }
+    }
     int st = 0;                                      // next stage to fill
     uint32_t pph = 0xffffffffu;                      // per stage: parity of the `empty` phase to wait for (all ones: first use is free)
     uint32_t fills = 0;                              // stages filled so far
@@ -872,7 +904,8 @@ __global__ void __launch_bounds__((H + 1) * 32 * Teams<H>::V, 1) decode_mma_kern
       }
     };
     // Fill one stage: wait until the consumers have released it, write the header, start the copies.
-    // `rows`: 0 = no token rows (header only), 1 = whole [K | V] rows in pairs, 2 = K sides, 3 = V sides (INT8).
+    // `rows`: 1 = a whole INT4 / INT2 tile (token rows in pairs, all stats); 2 / 3 = the first / second half of an INT8
+    // tile (eight whole token rows, their V stats; the K stats with the first half).
     auto fill = [&](const TilePlan& d, int flags_extra, int rows) -> bool {
       if (!mbar_wait(empty_u + st * 8, (pph >> st) & 1, P.wait_ns)) return false;
       pph ^= 1u << st;
@@ -883,28 +916,36 @@ __global__ void __launch_bounds__((H + 1) * 32 * Teams<H>::V, 1) decode_mma_kern
       const uint32_t k_stats = 2u * H * D * 2, v_stats = 2u * TILE * H * NG * 2;
       const int rt = min((2 * L.BS) / h0.x, TILE);              // token rows per run (see TilePlan)
       auto row_src = [&](int t) { return d.run[t / rt] + (uint32_t)(t % rt) * 2u * side; };
+      const int half0 = rows == 3 ? TILE / 2 : 0;               // first token of an INT8 half
+      const int nh = rows == 1 ? nv : max(0, min(nv - half0, TILE / 2));  // token rows this stage receives
       if (lane == 0) {
         int4* hd = reinterpret_cast<int4*>(ring + (size_t)st * SB + o_hdr(H));
         hd[0] = make_int4(h0.x, h0.y, h0.z | flags_extra, h0.w);
         hd[1] = reinterpret_cast<const int4*>(&d.hdr)[1];
-        const uint32_t tx = rows == 1 ? nv * 2 * side + k_stats + v_stats : rows == 2 ? nv * side + k_stats : nv * side + v_stats;
+        const uint32_t tx = rows == 1 ? nv * 2 * side + k_stats + v_stats : nh * 2 * side + v_stats / 2 + (rows == 2 ? k_stats : 0u);
         mbar_expect_tx(bar, tx);
       }
       __syncwarp();
       if (rows == 1) {
         // lane p < 8 copies tokens 2p and 2p + 1 in one piece (neighbours in their chunk: a chunk holds an even number of tokens)
-        if (lane < 8) { if (2 * lane < nv) bulk_copy(st_u + lane * slot_bytes(H), row_src(2 * lane), (2 * lane + 1 < nv ? 4u : 2u) * side, bar); }
+        if (lane < 8) { if (2 * lane < nv) bulk_copy(st_u + lane * slot_bytes(H), row_src(2 * lane), (2 * lane + 1 < nv ? 4u : 2u) * side, bar, policy); }
+        if (contig) {
+          if (lane == 16) bulk_copy(st_u + o_vs(H), d.stats[0], v_stats + k_stats, bar, policy);
+        } else if (lane >= 16 && lane < 20) {
+          const int which = lane - 16;  // vs, vm, ks, km
+          const int dst_off = which == 0 ? o_vs(H) : which == 1 ? o_vm(H) : which == 2 ? o_ks(H) : o_km(H);
+          bulk_copy(st_u + dst_off, d.stats[which], which < 2 ? v_stats / 2 : k_stats / 2, bar, policy);
+        }
       } else {
-        // lane t < 16 copies one side of token t to its half of slot t / 2
-        if (lane < TILE && lane < nv) bulk_copy(st_u + (lane >> 1) * slot_bytes(H) + (lane & 1) * side, row_src(lane) + (rows == 3 ? side : 0u), side, bar);
-      }
-      if (contig) {
-        if (lane == 16 && rows != 2) bulk_copy(st_u + o_vs(H), d.stats[0], v_stats, bar);
-        if (lane == 17 && rows != 3) bulk_copy(st_u + o_ks(H), d.stats[2], k_stats, bar);
-      } else if (lane >= 16 && lane < 20) {
-        const int which = lane - 16;  // vs, vm, ks, km
-        const int dst_off = which == 0 ? o_vs(H) : which == 1 ? o_vm(H) : which == 2 ? o_ks(H) : o_km(H);
-        if (which < 2 ? rows != 2 : rows != 3) bulk_copy(st_u + dst_off, d.stats[which], which < 2 ? v_stats / 2 : k_stats / 2, bar);
+        // lane t < 8 copies the whole row [K | V] of token half0 + t to slot t
+        if (lane < nh) bulk_copy(st_u + lane * slot_bytes(H), row_src(half0 + lane), 2u * side, bar, policy);
+        // the V stats of the half's eight tokens; with the first half the K group's stats
+        if (lane == 16) bulk_copy(st_u + o_vs(H), d.stats[0] + half0 * (H * NG * 2), v_stats / 4, bar, policy);
+        if (lane == 17) bulk_copy(st_u + o_vm(H), d.stats[1] + half0 * (H * NG * 2), v_stats / 4, bar, policy);
+        if (rows == 2) {
+          if (contig) { if (lane == 18) bulk_copy(st_u + o_ks(H), d.stats[2], k_stats, bar, policy); }
+          else if (lane == 18 || lane == 19) bulk_copy(st_u + (lane == 18 ? o_ks(H) : o_km(H)), d.stats[lane - 16], k_stats / 2, bar, policy);
+        }
       }
       ++fills;
       st = ring_next(st, NS);
@@ -1016,6 +1057,8 @@ __global__ void __launch_bounds__((H + 1) * 32 * Teams<H>::V, 1) decode_mma_kern
                           : (uint32_t)o_vm(H) + (uint32_t)((2 * (lane & 7) + (lane >> 4)) * H + (ln.h & ~1)) * NG * 2;
     // broadcast k_min operand: matrices 0 / 1 = channels [0, 8) of the k-step for the first / second tile, 2 / 3 = channels [8, 16)
     ln.km_ld = (uint32_t)o_km(H) + ln.h * (D * 2) + (lane >> 4) * 16u;
+    ln.vs_row8 = o_vs(H) + (uint32_t)(ln.r * H + ln.h) * NG * 2;
+    ln.vm_ld8 = (lane & 8) ? (uint32_t)o_ones(H) : (uint32_t)o_vm(H) + (uint32_t)((lane & 7) * H + (ln.h & ~1)) * NG * 2;
     int c_st = 0;                  // stage being consumed
     uint32_t cph = 0;              // per stage: parity of the `full` phase to wait for
     WarpState w;

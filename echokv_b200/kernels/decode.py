@@ -15,30 +15,31 @@ MAX_DECODE_SPLITS = 32  # upper bound of the split grid (backend.py:67-69 of the
 
 
 class _Scratch:
-    """Per-device split-partials buffer.
+    """Per-device split-partials buffer, grown on demand.
 
-    The buffer grows on demand until a call arrives while its stream is being captured: from then on
-    a CUDA graph may hold the buffer's address, so it is never replaced or freed.  A later eager call
-    that needs more bytes than the pinned buffer holds (more sequences than the captured sizes, or the
-    row path of a long prefill) gets a temporary of its own for that call instead.
+    A CUDA graph holds the address of the buffer it was captured with, so a buffer that a capture has
+    used is never freed: when a later call needs more bytes (more sequences than the captured sizes, the
+    row path of a long prefill, another model in the same process) a larger buffer takes over and the old
+    one is kept alive for the graphs that point at it.
     """
 
     def __init__(self) -> None:
         self.buf: dict[torch.device, torch.Tensor] = {}
-        self.pinned: set[torch.device] = set()
+        self.captured: set[torch.device] = set()
+        self.retired: list[torch.Tensor] = []
 
     def get(self, device, nbytes: int) -> torch.Tensor:
         cur = self.buf.get(device)
         capturing = torch.cuda.is_current_stream_capturing()
-        if cur is not None and cur.numel() >= nbytes:
+        if cur is None or cur.numel() < nbytes:
             if capturing:
-                self.pinned.add(device)
-            return cur
+                raise RuntimeError("decode scratch must be sized before CUDA-graph capture (run one eager step first)")
+            if cur is not None and device in self.captured:
+                self.retired.append(cur)
+                self.captured.discard(device)
+            cur = self.buf[device] = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         if capturing:
-            raise RuntimeError("decode scratch must be sized before CUDA-graph capture (run one eager step first)")
-        if device in self.pinned:
-            return torch.empty(nbytes, dtype=torch.uint8, device=device)  # this call only; the pinned buffer stays
-        cur = self.buf[device] = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            self.captured.add(device)
         return cur
 
 
