@@ -44,6 +44,9 @@ sys.path.insert(0, str(ROOT))
 HQ, H, D, BS, KG, VG, MEM_BITS = 32, 8, 128, 16, 16, 32, 8
 METRIC = "decode tokens/s/GPU at INT4 KV; paged-decode attention HBM GB/s vs peak"
 CPU_LAYERS = 2  # layers of the workload the CPU legs run (the step has --layers of them)
+# dram__bytes_read.sum + dram__bytes_write.sum of one INT4 decode launch at batch 64 x ctx 4096 from the ncu capture
+# summarised under profiles/ (reads 373.5 MB of pages, writes 7.3 MB of split partials)
+DRAM_TRAFFIC_INT4 = 380_800_000
 
 
 def parse():
@@ -834,7 +837,7 @@ def run_b200(a) -> None:
                        "host_cores": cores, "timing": f"median of {len(windows)} windows of {a.steps} steps",
                        "window_ms": [round(w, 3) for w in windows]},
             "roofline": {"bound": "hbm", "achieved": main["gbs"], "peak": peak, "unit": "GB/s", "frac": main["frac"],
-                         "traffic": None,
+                         "traffic": DRAM_TRAFFIC_INT4 if (S, ctx, world) == (64, 4096, 1) else None,
                          "kernel": "decode_mma_kernel (the split kernel of paged decode attention), INT4 layers; call_* = whole "
                                    "decode call (counter memset + split kernel + merge), back to back",
                          "peak_source": peak_src,
