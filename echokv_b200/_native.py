@@ -76,6 +76,8 @@ _SIGS = {
     "echokv_gather": [_LP, _PP, _RP, _P, _P, _I64, _P, _P, _P],
     "echokv_decode": [_LP, _PP, _RP, _P, _I64, _I64, _I32, _P, _P, _I64, _P, _P, _P, _I64, _P, _I64, _I64, _I32,
                       _F, _I32, _I32, _I64, _I32, _P],
+    "echokv_decode_ex": [_LP, _PP, _RP, _P, _I64, _I64, _I32, _P, _P, _I64, _P, _P, _P, _I64, _P, _I64, _I64, _I32,
+                         _F, _I32, _I32, _P, _I64, _I32, _P],
     "echokv_decode_static": [_LP, _PP, _RP, _P, _I64, _I64, _I32, _P, _P, _I64, _P, _P, _P, _I64, _I64, _I32,
                              _F, _I32, _I32, _I64, _I32, _P],
     "echokv_dequant_dense": [_LP, _PP, _RP, _P, _I64, _P, _I64, _P, _P, _I64, _I64, _I32, _P],
@@ -95,10 +97,12 @@ lib.echokv_set_decode_path.argtypes = [C.c_int]
 lib.echokv_set_decode_path.restype = C.c_int
 lib.echokv_set_decode_wait_limit.argtypes = [C.c_int64, C.c_int]
 lib.echokv_set_decode_wait_limit.restype = C.c_int
+lib.echokv_decode_parallelism.argtypes = [_LP, C.c_int32]
+lib.echokv_decode_parallelism.restype = C.c_int32
 lib.echokv_kernel_status.argtypes = [C.c_int]
 lib.echokv_kernel_status.restype = C.c_int
 
-EXPORTS = sorted(list(_SIGS) + ["echokv_set_decode_path", "echokv_set_decode_wait_limit", "echokv_kernel_status", "echokv_set_prefill_path", "echokv_decode_static_scratch_bytes", "echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
+EXPORTS = sorted(list(_SIGS) + ["echokv_set_decode_path", "echokv_set_decode_wait_limit", "echokv_kernel_status", "echokv_set_prefill_path", "echokv_decode_static_scratch_bytes", "echokv_decode_parallelism", "echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
                                 "echokv_demote_scratch_bytes"])
 
 

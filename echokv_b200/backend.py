@@ -115,6 +115,8 @@ class EchoKVMetadata:
     decode_reqs: torch.Tensor | None = None  # [nd] their block-table rows
     decode_lens: torch.Tensor | None = None  # [nd] their cache lengths (0 = CUDA-graph padding)
     num_splits: int = 1  # fixed decode split grid, so a graph can replay it
+    split_floor: int = 1  # smallest number of blocks per decode split
+    bps_dev: torch.Tensor | None = None  # blocks per decode split chosen for this step (read by the kernels at run time)
     prefill: list = field(default_factory=list)  # (q_start, q_end, ctx, dense_start) per chunk
     prefill_reqs: list = field(default_factory=list)  # block-table row of each chunk
     prefill_rows: tuple | None = None  # row path: per query token (row, request, causal limit), max limit
@@ -262,6 +264,7 @@ class EchoKVMetadataBuilder(AttentionMetadataBuilder[EchoKVMetadata]):
             rows, md.fire = self.canary.rows_for(dummy, last_rows, last_ctx)
             step: StepMeta = self.runner.plan_step(slots_cpu, decode=(d_rows, d_reqs, d_lens), canary=rows)
             md.write, md.canary_rows, md.num_splits = step.write, step.canary_rows, step.num_splits
+            md.split_floor, md.bps_dev = self.runner.split_floor, step.bps_dev
             md.decode_rows, md.decode_reqs, md.decode_lens = step.decode_rows, step.decode_reqs, step.decode_lens
         if prefill:
             if max(qe - qs for qs, qe, _, _ in prefill) <= ROW_PATH_MAX_CHUNK:
@@ -363,9 +366,10 @@ class EchoKVAttentionImpl(AttentionImpl[EchoKVMetadata]):
             prefill_attention(self.store, query, output, md.prefill, md.prefill_reqs, md.block_table, self.scale,
                               dense=md.prefill_dense, rows=md.prefill_rows)
         if md.decode_rows is not None:
-            decode_attention(self.store, query, md.block_table, md.decode_lens, self.scale, q_rows=md.decode_rows,
-                             bt_rows=md.decode_reqs, out=output.view(output.shape[0], -1, query.shape[-1]),
-                             num_splits=md.num_splits)
+            decode_attention(self.store, query, md.block_table, md.decode_lens, self.scale, md.split_floor,
+                             q_rows=md.decode_rows, bt_rows=md.decode_reqs,
+                             out=output.view(output.shape[0], -1, query.shape[-1]), num_splits=md.num_splits,
+                             bps_dev=md.bps_dev)
         # A graph captures the copy unconditionally: its row indices are valid either way.
         if md.fire or _capturing(query):
             gather_rows(query, md.canary_rows, self.stash)

@@ -108,20 +108,6 @@ __device__ __forceinline__ uint32_t quant_code(float x, float mn, float scale, f
   return static_cast<uint32_t>(q);
 }
 
-// The same code from a precomputed reciprocal of the scale, for loops that quantize many values under one
-// scale: d * (1 / scale) differs from the correctly rounded d / scale by less than 2^-14 for quotients
-// below 256 (and larger ones clamp alike), so both round to the same integer unless the quotient lies
-// within that distance of a half-integer; those rare values take the exact division.
-__device__ __forceinline__ uint32_t quant_code_r(float x, float mn, float scale, float rscale, float levels) {
-  const float d = __fsub_rn(x, mn);
-  float t = __fmul_rn(d, rscale);
-  const float f = t - floorf(t);
-  if (fabsf(f - 0.5f) < 0.000244140625f || !(fabsf(t) < 512.f)) t = __fdiv_rn(d, scale);  // 2^-12; NaN / huge: exact path
-  float q = rintf(t);
-  q = fminf(fmaxf(q, 0.0f), levels);
-  return static_cast<uint32_t>(q);
-}
-
 // Pack 8 codes at `bits` into the low bits*8 bits of a 64-bit word (element i at bit i*bits).
 __device__ __forceinline__ uint64_t pack8(const uint32_t (&c)[8], int bits) {
   uint64_t w = 0;

@@ -6,6 +6,7 @@ using namespace echokv;
 namespace echokv {
 int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
                       int64_t num_seqs, int* counter, int* status, cudaStream_t st, bool* handled);
+int decode_mma_teams(int H, int D, int VG, int KG, int BS, int gqa);
 int decode_status_take(bool clear);
 int prefill_status_take(bool clear);
 
@@ -21,7 +22,7 @@ __global__ void decode_merge_kernel(DecodeArgs A, int BS, int D) {
   const int64_t seq_len = A.lens[seq];
   if (seq_len == 0) return;  // CUDA-graph padding: leave the row alone
   const int n_blocks = (int)((seq_len + BS - 1) / BS);
-  const int bps = max(A.bps_min, (n_blocks + A.num_splits - 1) / A.num_splits);
+  const int bps = max(bps_floor(A), (n_blocks + A.num_splits - 1) / A.num_splits);
   const int used = (n_blocks + bps - 1) / bps;
   const int64_t base = ((int64_t)seq * A.Hq + head) * A.num_splits;
   const int64_t o_row = A.q_rows ? A.q_rows[seq] : seq;
@@ -111,12 +112,12 @@ int64_t echokv_decode_scratch_bytes(int64_t num_seqs, int32_t num_q_heads, int32
   return (partials + 15) / 16 * 16 + 256;
 }
 
-int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
-                  const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype, const int64_t* q_rows,
-                  const int32_t* block_table, int64_t bt_s0, const int64_t* bt_rows, const int64_t* lens,
-                  void* scratch, int64_t scratch_bytes, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
-                  float softmax_scale, int32_t num_splits, int32_t blocks_per_split, int64_t num_seqs,
-                  int32_t num_q_heads, void* stream) {
+int echokv_decode_ex(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                     const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype, const int64_t* q_rows,
+                     const int32_t* block_table, int64_t bt_s0, const int64_t* bt_rows, const int64_t* lens,
+                     void* scratch, int64_t scratch_bytes, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
+                     float softmax_scale, int32_t num_splits, int32_t blocks_per_split,
+                     const int32_t* blocks_per_split_dev, int64_t num_seqs, int32_t num_q_heads, void* stream) {
   if (num_seqs <= 0) return ECHOKV_OK;
   LayoutDev L;
   ResidualDev R;
@@ -142,6 +143,7 @@ int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const 
   A.out = out; A.o_s0 = o_s0; A.o_s1 = o_s1; A.out_dt = out_dtype;
   A.scale_log2e = softmax_scale * 1.4426950408889634f;
   A.num_splits = num_splits; A.bps_min = blocks_per_split; A.gqa = gqa; A.Hq = num_q_heads;
+  A.bps_dev = blocks_per_split_dev;
   cudaStream_t st = (cudaStream_t)stream;
   const uint8_t* pg = (const uint8_t*)pages->base;
 
@@ -164,6 +166,25 @@ int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const 
   dim3 mgrid((unsigned)num_seqs, (unsigned)num_q_heads);
   decode_merge_kernel<<<mgrid, L.D < 128 ? L.D : 128, 0, st>>>(A, L.BS, L.D);
   return check_launch("decode merge");
+}
+
+int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                  const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype, const int64_t* q_rows,
+                  const int32_t* block_table, int64_t bt_s0, const int64_t* bt_rows, const int64_t* lens,
+                  void* scratch, int64_t scratch_bytes, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
+                  float softmax_scale, int32_t num_splits, int32_t blocks_per_split, int64_t num_seqs,
+                  int32_t num_q_heads, void* stream) {
+  return echokv_decode_ex(layout, pages, residual, query, q_s0, q_s1, q_dtype, q_rows, block_table, bt_s0, bt_rows, lens,
+                          scratch, scratch_bytes, out, o_s0, o_s1, out_dtype, softmax_scale, num_splits, blocks_per_split,
+                          nullptr, num_seqs, num_q_heads, stream);
+}
+
+// Work items the tensor-core split kernel processes at the same time on the current device for this shape (its
+// teams: one per group of H consumer warps), or 0 when the shape takes the generic kernel.
+int32_t echokv_decode_parallelism(const echokv_layout* layout, int32_t num_q_heads) {
+  if (!layout || layout->num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % layout->num_kv_heads) return 0;
+  return decode_mma_teams(layout->num_kv_heads, layout->head_size, layout->v_group, layout->k_group, layout->block_size,
+                          num_q_heads / layout->num_kv_heads);
 }
 
 

@@ -26,7 +26,13 @@ struct DecodeArgs {
   void* out; int64_t o_s0, o_s1; int out_dt;
   float scale_log2e;
   int num_splits, bps_min, gqa, Hq;
+  const int32_t* bps_dev;  // optional: blocks per split chosen by the host for this step, read at run time
 };
+
+// Lower bound of a split's size in blocks: the call's argument, raised by the run-time value when there is one.
+__device__ __forceinline__ int bps_floor(const DecodeArgs& A) {
+  return A.bps_dev ? max(A.bps_min, (int)__ldg(A.bps_dev)) : A.bps_min;
+}
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -57,7 +63,7 @@ decode_generic_kernel(LayoutDev L, ResidualDev R, const uint8_t* __restrict__ pa
   const int seq = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
   const int64_t seq_len = A.lens[seq];
   int b_start, b_end;
-  if (!split_range(seq_len, L.BS, A.num_splits, A.bps_min, split, b_start, b_end)) return;
+  if (!split_range(seq_len, L.BS, A.num_splits, bps_floor(A), split, b_start, b_end)) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t q_row = A.q_rows ? A.q_rows[seq] : seq;
   const int64_t bt_row = A.bt_rows ? A.bt_rows[seq] : seq;

@@ -734,12 +734,12 @@ __device__ __forceinline__ void process_group(const Params& P, const Lane& ln, c
 }
 
 // ---- the kernel ------------------------------------------------------------------------------
-__device__ __forceinline__ bool item_range(const Params& P, int item, int& seq, int& split, int64_t& seq_len,
-                                           int& b_start, int& b_end) {
+__device__ __forceinline__ bool item_range(const Params& P, int bps_min, int item, int& seq, int& split,
+                                           int64_t& seq_len, int& b_start, int& b_end) {
   seq = item % P.num_seqs;
   split = item / P.num_seqs;
   seq_len = P.A.lens[seq];
-  return split_range(seq_len, P.L.BS, P.A.num_splits, P.A.bps_min, split, b_start, b_end);
+  return split_range(seq_len, P.L.BS, P.A.num_splits, bps_min, split, b_start, b_end);
 }
 
 // Block metadata the producer warp prefetches for up to 32 blocks at a time (one block per lane).
@@ -822,13 +822,17 @@ __device__ __forceinline__ void write_partial(const Params& P, const WarpState& 
 __device__ __forceinline__ int ring_next(int st, int NS) { return st + 1 == NS ? 0 : st + 1; }
 
 // Teams per CTA: a CTA is V independent teams of H consumer warps + 1 producer warp, each with its own barriers,
-// plans, query copy and stage ring in its slice of the CTA's shared memory.  One CTA per SM: registers are handed
-// out per CTA for an even number of warps, so 18 warps in one CTA get 112 registers each where two CTAs of 9
-// warps (allocated as 10) would get 96.
-template <int H> struct Teams { static constexpr int V = H == 8 ? 2 : (H == 4 ? 3 : (H == 2 ? 5 : 8)); };
+// plans, query copy and stage ring in its slice of the CTA's shared memory.  One CTA per SM.  Registers are handed
+// out per SM sub-partition (16,384 each): with 17 to 20 warps per SM (5 on a sub-partition) a thread gets 96, so
+// V is chosen to use those 18 to 20 warps for every H.  The smaller V of each H is for shapes whose per-team shared
+// memory (many query heads per KV head) does not fit V times.
+template <int H> struct Teams {
+  static constexpr int V = H == 8 ? 2 : (H == 4 ? 4 : (H == 2 ? 6 : 10));   // 18 / 20 / 18 / 20 warps
+  static constexpr int V_SMALL = H == 8 ? 1 : (H == 4 ? 3 : (H == 2 ? 4 : 7));
+};
 
-template <int H>
-__global__ void __launch_bounds__((H + 1) * 32 * Teams<H>::V, 1) decode_mma_kernel(const Params P) {
+template <int H, int V>
+__global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const Params P) {
   extern __shared__ __align__(128) unsigned char smem_all[];
   constexpr int TEAM_THREADS = (H + 1) * 32;
   const LayoutDev& L = P.L;
@@ -878,7 +882,7 @@ __global__ void __launch_bounds__((H + 1) * 32 * Teams<H>::V, 1) decode_mma_kern
     const bool contig = L.BS == TILE && L.KG == TILE;  // a tile's four stats arrays form one run in the page
     const uint64_t policy = stream_policy();
     if (P.q_vec16 && A.q_s1 == D) {  // the batch's query rows into L2 now: a work item's first step is to read one
-      const int elt = 2, teams = gridDim.x * Teams<H>::V, me = blockIdx.x * Teams<H>::V + team;
+      const int elt = 2, teams = gridDim.x * V, me = blockIdx.x * V + team;
       for (int sq = me * 32 + lane; sq < P.num_seqs; sq += teams * 32) {
         const int64_t q_row = A.q_rows ? A.q_rows[sq] : sq;
         l2_prefetch(reinterpret_cast<const unsigned char*>(A.q) + q_row * A.q_s0 * elt, (uint32_t)(A.Hq * D * elt));
@@ -890,6 +894,7 @@ __global__ void __launch_bounds__((H + 1) * 32 * Teams<H>::V, 1) decode_mma_kern
     int seq = 0, split = 0, b_start = 0, b_end = 0, base = 0;
     int64_t seq_len = 0, bt_row = 0;
     bool have = false;
+    const int bps_min = bps_floor(A);
     auto advance = [&]() {  // move to the next unit (claiming a new item when needed); false when there is no work left
       if (have && base + U < b_end) { base += U; return true; }
       for (;;) {
@@ -897,7 +902,7 @@ __global__ void __launch_bounds__((H + 1) * 32 * Teams<H>::V, 1) decode_mma_kern
         if (lane == 0) it = atomicAdd(P.counter, 1);
         it = __shfl_sync(0xffffffffu, it, 0);
         if (it >= n_items) { have = false; return false; }
-        if (item_range(P, it, seq, split, seq_len, b_start, b_end)) {
+        if (item_range(P, bps_min, it, seq, split, seq_len, b_start, b_end)) {
           base = b_start; bt_row = A.bt_rows ? A.bt_rows[seq] : seq; have = true;
           return true;
         }
@@ -1201,8 +1206,8 @@ __global__ void __launch_bounds__((H + 1) * 32 * Teams<H>::V, 1) decode_mma_kern
   }
   if (!ok && lane == 0 && P.status) atomicExch(P.status, 1);
 #ifdef ECHOKV_PROFILE
-  if (tid == 0 && blockIdx.x * Teams<H>::V + team < 1024) {
-    const int slot = blockIdx.x * Teams<H>::V + team;
+  if (tid == 0 && blockIdx.x * V + team < 1024) {
+    const int slot = blockIdx.x * V + team;
     unsigned int smid;
     asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
     g_cta[slot * 4 + 0] = cta_t0; g_cta[slot * 4 + 1] = global_ns();
@@ -1237,6 +1242,20 @@ struct DecodeDevice {
   int max_smem = 0, num_sms = 0;
   int* status_word = nullptr;
 };
+template <int H>
+static cudaError_t allow_smem(int bytes) {
+  using namespace mma;
+  cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<H, Teams<H>::V>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(decode_mma_kernel<H, Teams<H>::V_SMALL>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  return e;
+}
+template <int H>
+static void launch_teams(bool small, unsigned grid, int smem_bytes, cudaStream_t st, const mma::Params& P) {
+  using namespace mma;
+  if (small) decode_mma_kernel<H, Teams<H>::V_SMALL><<<grid, (H + 1) * 32 * Teams<H>::V_SMALL, smem_bytes, st>>>(P);
+  else decode_mma_kernel<H, Teams<H>::V><<<grid, (H + 1) * 32 * Teams<H>::V, smem_bytes, st>>>(P);
+}
 static int decode_device(DecodeDevice** out) {
   using namespace mma;
   constexpr int MAX_DEVICES = 64;
@@ -1248,16 +1267,53 @@ static int decode_device(DecodeDevice** out) {
   if (!d.ready) {
     e = cudaDeviceGetAttribute(&d.max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.max_smem);
+    if (e == cudaSuccess) e = allow_smem<1>(d.max_smem);
+    if (e == cudaSuccess) e = allow_smem<2>(d.max_smem);
+    if (e == cudaSuccess) e = allow_smem<4>(d.max_smem);
+    if (e == cudaSuccess) e = allow_smem<8>(d.max_smem);
     if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status_word), g_decode_status);
     if (e != cudaSuccess) return set_error(ECHOKV_E_CUDA, "decode: device %d set-up: %s", dev, cudaGetErrorString(e));
     d.ready = true;
   }
   *out = &d;
   return ECHOKV_OK;
+}
+
+// Teams per CTA and ring stages per team for H KV heads with gqa query heads each: every team gets an equal slice
+// of the SM's shared memory; false when not even the smaller team count leaves room for four stages (a group of
+// two stages in work and one in flight at the least).
+struct TeamShape { int V, ns, fixed; bool small; };
+static bool team_shape(const DecodeDevice& dv, int H, int gqa, TeamShape* out) {
+  using namespace mma;
+  const int fixed = HDR_BYTES + UNIT * (int)sizeof(TilePlan) + REMAP_BYTES + (q_copy_bytes(H, gqa) + 127) / 128 * 128;
+  const int sbytes = stage_bytes(H);
+  int V = H == 8 ? Teams<8>::V : H == 4 ? Teams<4>::V : H == 2 ? Teams<2>::V : Teams<1>::V;
+  bool small = false;
+  int ns = ((dv.max_smem / V) / 128 * 128 - fixed) / sbytes;
+  if (ns < 4) {
+    small = true;
+    V = H == 8 ? Teams<8>::V_SMALL : H == 4 ? Teams<4>::V_SMALL : H == 2 ? Teams<2>::V_SMALL : Teams<1>::V_SMALL;
+    ns = ((dv.max_smem / V) / 128 * 128 - fixed) / sbytes;
+  }
+  if (ns > MAX_NS) ns = MAX_NS;
+  if (ns < 4) return false;
+  out->V = V; out->ns = ns; out->fixed = fixed; out->small = small;
+  return true;
+}
+
+static bool mma_shape_ok(int H, int D_, int VG, int KG, int BS, int gqa) {
+  using namespace mma;
+  return D_ == D && VG == 32 && KG % TILE == 0 && BS % TILE == 0 && gqa <= 8 && (H == 1 || H == 2 || H == 4 || H == 8);
+}
+
+// Teams of the tensor-core kernel on the current device for this shape (0: the generic kernel takes it, or no device).
+int decode_mma_teams(int H, int D_, int VG, int KG, int BS, int gqa) {
+  if (g_decode_path == 1 || !mma_shape_ok(H, D_, VG, KG, BS, gqa)) return 0;
+  DecodeDevice* dv = nullptr;
+  if (decode_device(&dv)) return 0;
+  TeamShape ts;
+  if (!team_shape(*dv, H, gqa, &ts)) return 0;
+  return dv->num_sms * ts.V;
 }
 
 // Chooses the tensor-core kernel when the shape fits; otherwise leaves `handled` false.
@@ -1267,8 +1323,7 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   *handled = false;
   if (g_decode_path == 1) return ECHOKV_OK;
   const int H = L.H;
-  if (L.D != D || L.VG != 32 || L.KG % TILE || L.BS % TILE || A.gqa > 8) return ECHOKV_OK;
-  if (!(H == 1 || H == 2 || H == 4 || H == 8)) return ECHOKV_OK;
+  if (!mma_shape_ok(H, L.D, L.VG, L.KG, L.BS, A.gqa)) return ECHOKV_OK;
   if ((R.s_slot | R.s_pos | R.s_head) & 3) return ECHOKV_OK;                 // 8-byte residual loads
   if ((reinterpret_cast<uintptr_t>(R.base) & 15) != 0) return ECHOKV_OK;
   if (num_seqs * (int64_t)A.num_splits > (1 << 30)) return ECHOKV_OK;
@@ -1282,14 +1337,10 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   P.status = status ? status : dv->status_word;
   P.wait_ns = g_wait_ns;
   P.idle_producer = g_idle_producer;
-  const int fixed = HDR_BYTES + UNIT * (int)sizeof(TilePlan) + REMAP_BYTES + (q_copy_bytes(H, A.gqa) + 127) / 128 * 128;
-  const int sbytes = stage_bytes(H);
-  // One CTA per SM holding V teams; every team gets an equal slice of the SM's shared memory.
-  const int V = H == 8 ? Teams<8>::V : H == 4 ? Teams<4>::V : H == 2 ? Teams<2>::V : Teams<1>::V;
-  const int budget = (dv->max_smem / V) / 128 * 128;
-  int ns = (budget - fixed) / sbytes;
-  if (ns > MAX_NS) ns = MAX_NS;
-  if (ns < 4) return ECHOKV_OK;  // a group of two stages in work and one in flight at the least
+  TeamShape ts;
+  if (!team_shape(*dv, H, A.gqa, &ts)) return ECHOKV_OK;
+  const int V = ts.V, ns = ts.ns, fixed = ts.fixed, sbytes = stage_bytes(H);
+  const bool small = ts.small;
   P.NS = ns;
   P.team_bytes = (fixed + ns * sbytes + 127) / 128 * 128;
   const int smem_bytes = P.team_bytes * V;
@@ -1299,10 +1350,10 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   if (cudaMemsetAsync(counter, 0, sizeof(int), st) != cudaSuccess) return check_launch("decode (work counter)");
   if (g_ev_before) cudaEventRecord(g_ev_before, st);
   switch (H) {
-    case 1: decode_mma_kernel<1><<<(unsigned)grid, 2 * 32 * Teams<1>::V, smem_bytes, st>>>(P); break;
-    case 2: decode_mma_kernel<2><<<(unsigned)grid, 3 * 32 * Teams<2>::V, smem_bytes, st>>>(P); break;
-    case 4: decode_mma_kernel<4><<<(unsigned)grid, 5 * 32 * Teams<4>::V, smem_bytes, st>>>(P); break;
-    default: decode_mma_kernel<8><<<(unsigned)grid, 9 * 32 * Teams<8>::V, smem_bytes, st>>>(P); break;
+    case 1: launch_teams<1>(small, (unsigned)grid, smem_bytes, st, P); break;
+    case 2: launch_teams<2>(small, (unsigned)grid, smem_bytes, st, P); break;
+    case 4: launch_teams<4>(small, (unsigned)grid, smem_bytes, st, P); break;
+    default: launch_teams<8>(small, (unsigned)grid, smem_bytes, st, P); break;
   }
   if (g_ev_after) cudaEventRecord(g_ev_after, st);
   rc = check_launch("decode (tensor-core kernel)");

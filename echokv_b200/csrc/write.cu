@@ -3,6 +3,8 @@
 // first, IEEE fp32 divide, round-half-to-even, clamp after rounding.
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace echokv {
 
 constexpr int WT_WARPS = 4;
@@ -30,39 +32,205 @@ __global__ void scatter_i64_kernel(int64_t* dst, const int64_t* idx, const int64
   if (i < n) dst[idx[i]] = val[i];
 }
 
-// Token rows (kernels/write.py:171-229 does one program per (row, head)).  WIDE: one CTA of four warps
-// per row, a thread per 8 channels, the V group's min / max reduced over its VG / 8 neighbouring lanes
-// by shuffles (needs VG / 8 to be a power of two <= 32); otherwise one warp per row, a lane per V group.
-// Both produce the same bytes: min and max do not depend on the order of reduction.
-template <typename T, bool WIDE>
+// ---- the quantizer, many values under one reciprocal ---------------------------------------------
+// code = clamp(rne((x - mn) / scale), 0, levels) from a precomputed reciprocal of the scale.  The product
+// (x - mn) * (1 / scale), clamped to [0, levels] first (0 and levels are integers, so clamping before or after
+// the rounding gives the same code), differs from the correctly rounded quotient by at most three roundings of
+// 2^-24 relative each, under 1.8e-7 * (levels + 0.5); adding 1.5 * 2^23 rounds it to the nearest-even integer
+// in the float's low mantissa bits.  Both round alike unless the product lies within levels * 2^-21 (2.6 times
+// that bound) of a half-integer: `risky` collects those, and the caller redoes the 8 values with the IEEE
+// divide.  NaN clamps to 0 on both routes.
+constexpr float QMAGIC = 12582912.f;            // 1.5 * 2^23
+constexpr uint32_t QMAGIC_BITS = 0x4B400000u;   // its bit pattern; QMAGIC + code has bit pattern QMAGIC_BITS + code
+
+__device__ __forceinline__ uint32_t quant_u(float x, float mn, float rscale, float levels, float near_half,
+                                            bool& risky) {
+  const float d = __fsub_rn(x, mn);
+  const float t = fminf(fmaxf(__fmul_rn(d, rscale), 0.0f), levels);
+  const float u = __fadd_rn(t, QMAGIC);
+  const float r = __fsub_rn(__fsub_rn(u, QMAGIC), t);
+  risky |= fabsf(r) > near_half;
+  return __float_as_uint(u);
+}
+
+// 8 values of QMAGIC_BITS + code -> the 8 codes packed at BITS (element k at bit k * BITS): the shifted sum of
+// the words minus the shifted sum of the constant, modulo 2^32.
+template <int BITS>
+__device__ __forceinline__ uint64_t pack_u8(const uint32_t (&u)[8]) {
+  if constexpr (BITS == 8) {
+    constexpr uint32_t C = QMAGIC_BITS * 0x01010101u;
+    const uint32_t lo = u[0] + (u[1] << 8) + (u[2] << 16) + (u[3] << 24) - C;
+    const uint32_t hi = u[4] + (u[5] << 8) + (u[6] << 16) + (u[7] << 24) - C;
+    return (uint64_t)lo | ((uint64_t)hi << 32);
+  } else if constexpr (BITS == 4) {
+    constexpr uint32_t C = QMAGIC_BITS * 0x11111111u;
+    return u[0] + (u[1] << 4) + (u[2] << 8) + (u[3] << 12) + (u[4] << 16) + (u[5] << 20) + (u[6] << 24) +
+           (u[7] << 28) - C;
+  } else {
+    constexpr uint32_t C = QMAGIC_BITS * 0x5555u;
+    return (u[0] + (u[1] << 2) + (u[2] << 4) + (u[3] << 6) + (u[4] << 8) + (u[5] << 10) + (u[6] << 12) +
+            (u[7] << 14) - C) & 0xffffu;
+  }
+}
+
+// Quantize 8 values and store their codes at `dst`.  PER_CH: value k has its own stats m[k], sc[k], rsc[k]
+// (K: per channel); otherwise all 8 share m[0], sc[0], rsc[0] (V: one group).
+template <int BITS, bool PER_CH>
+__device__ __forceinline__ void quant_store8(uint8_t* dst, const float (&x)[8], const float* m, const float* sc,
+                                             const float* rsc) {
+  constexpr float levels = (float)((1 << BITS) - 1);
+  constexpr float near_half = 0.5f - levels * 4.76837158203125e-07f;  // 2^-21
+  uint32_t u[8];
+  bool risky = false;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) u[k] = quant_u(x[k], m[PER_CH ? k : 0], rsc[PER_CH ? k : 0], levels, near_half, risky);
+  if (risky) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) u[k] = QMAGIC_BITS + quant_code(x[k], m[PER_CH ? k : 0], sc[PER_CH ? k : 0], levels);
+  }
+  store_packed8(dst, pack_u8<BITS>(u), BITS);
+}
+template <bool PER_CH>
+__device__ __forceinline__ void quant_store8(int bits, uint8_t* dst, const float (&x)[8], const float* m,
+                                             const float* sc, const float* rsc) {
+  if (bits == 4) quant_store8<4, PER_CH>(dst, x, m, sc, rsc);
+  else if (bits == 8) quant_store8<8, PER_CH>(dst, x, m, sc, rsc);
+  else quant_store8<2, PER_CH>(dst, x, m, sc, rsc);
+}
+
+// 8 consecutive 16-bit elements as loaded (one 16-byte word) -> float
+template <typename T>
+__device__ __forceinline__ void cvt8(const uint4& raw, float (&x)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if constexpr (sizeof(T) == 2 && !std::is_same<T, __half>::value) {
+      x[2 * k] = __uint_as_float(w[k] << 16);
+      x[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+    } else {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+      x[2 * k] = f.x;
+      x[2 * k + 1] = f.y;
+    }
+  }
+}
+
+// Running minimum / maximum of 8 channels over many rows, kept packed in the rows' own 16-bit type (two channels
+// per register, one instruction per pair and row); minima and maxima of values of that type are exact in it.
+template <typename T>
+struct MinMax8 {
+  uint32_t mn[4], mx[4];
+  __device__ __forceinline__ void init() {
+    const uint32_t pinf = std::is_same<T, __half>::value ? 0x7C007C00u : 0x7F807F80u;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { mn[k] = pinf; mx[k] = pinf | 0x80008000u; }
+  }
+  __device__ __forceinline__ void update(const uint4& raw) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if constexpr (std::is_same<T, __half>::value) {
+        const __half2 v = *reinterpret_cast<const __half2*>(&w[k]);
+        __half2 a = __hmin2(*reinterpret_cast<__half2*>(&mn[k]), v), b = __hmax2(*reinterpret_cast<__half2*>(&mx[k]), v);
+        mn[k] = *reinterpret_cast<uint32_t*>(&a);
+        mx[k] = *reinterpret_cast<uint32_t*>(&b);
+      } else {
+        const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&w[k]);
+        __nv_bfloat162 a = __hmin2(*reinterpret_cast<__nv_bfloat162*>(&mn[k]), v);
+        __nv_bfloat162 b = __hmax2(*reinterpret_cast<__nv_bfloat162*>(&mx[k]), v);
+        mn[k] = *reinterpret_cast<uint32_t*>(&a);
+        mx[k] = *reinterpret_cast<uint32_t*>(&b);
+      }
+    }
+  }
+  __device__ __forceinline__ void finish(float (&lo)[8], float (&hi)[8]) const {
+    cvt8<T>(make_uint4(mn[0], mn[1], mn[2], mn[3]), lo);
+    cvt8<T>(make_uint4(mx[0], mx[1], mx[2], mx[3]), hi);
+  }
+};
+
+// Division and remainder by a layout constant that is usually a power of two: `sh` is its log2, or -1.
+struct Shifts { int D, VG, BS, KG; };
+__device__ __forceinline__ int qdiv(int x, int d, int sh) { return sh >= 0 ? x >> sh : x / d; }
+__device__ __forceinline__ int qmod(int x, int d, int sh) { return sh >= 0 ? x & (d - 1) : x % d; }
+static int log2_or_neg(int v) {
+  if (v <= 0 || (v & (v - 1))) return -1;
+  int s = 0;
+  while ((1 << s) < v) ++s;
+  return s;
+}
+static Shifts make_shifts(const LayoutDev& L) { return {log2_or_neg(L.D), log2_or_neg(L.VG), log2_or_neg(L.BS), log2_or_neg(L.KG)}; }
+
+// Byte offsets (from the pool base) of consecutive token rows of one block stored at `bits`: the chunk of a row is
+// looked up once per chunk, not once per row.
+struct RowWalk {
+  int64_t base, row_bytes;
+  int r, tpc, j;
+  int64_t blk;
+  __device__ __forceinline__ int64_t chunk_base(const uint8_t* pages, const LayoutDev& L) const {
+    int64_t page = blk, slot = 0;
+    if (j > 0) {
+      const int id = reinterpret_cast<const int32_t*>(pages + blk * L.PS + 4)[j - 1];
+      page = id / L.KC;
+      slot = id % L.KC;
+    }
+    return page * L.PS + L.o_data + slot * L.CB;
+  }
+  __device__ __forceinline__ void start(const uint8_t* pages, const LayoutDev& L, int sh_bs, int64_t block, int off,
+                                        int bits) {
+    blk = block;
+    const int sh_bits = bits == 2 ? 1 : (bits == 4 ? 2 : 3);
+    tpc = (2 * L.BS) >> sh_bits;
+    j = qdiv(off, tpc, sh_bs >= 0 ? sh_bs + 1 - sh_bits : -1);
+    r = off - j * tpc;
+    row_bytes = (int64_t)(2 * L.H * L.D * bits) / 8;
+    base = chunk_base(pages, L);
+  }
+  __device__ __forceinline__ int64_t offset() const { return base + (int64_t)r * row_bytes; }
+  __device__ __forceinline__ void next(const uint8_t* pages, const LayoutDev& L) {
+    if (++r == tpc) { r = 0; ++j; base = chunk_base(pages, L); }
+  }
+};
+
+// Token rows (kernels/write.py:171-229 does one program per (row, head)).  MODE 2: one CTA of four warps per
+// row (few rows, a decode step: the shortest dependent chain); MODE 1: one warp per row (many rows); in both a
+// thread owns 8 channels at a time and the V group's min / max is reduced over its VG / 8 neighbouring lanes by
+// shuffles (needs VG / 8 to be a power of two <= 32).  MODE 0: one warp per row, a lane per V group, for the
+// other group sizes.  All produce the same bytes: min and max do not depend on the order of reduction.
+// `res_raw`: the residual buffer has the rows' own 16-bit type and 16-byte aligned rows, so an open group's key
+// goes there as loaded; `kref_vec`: 16-byte aligned K_ref rows.
+template <typename T, int MODE>
 __global__ void __launch_bounds__(WT_WARPS * 32)
 write_tokens_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restrict__ key, int64_t k_s0, int64_t k_s1,
                     const T* __restrict__ value, int64_t v_s0, int64_t v_s1, const int64_t* __restrict__ tok,
                     int64_t tok_s0, void* res, int res_dt, int64_t r_s0, int64_t r_s1, int64_t r_s2,
-                    float* __restrict__ kref, int64_t kref_s0, int64_t kref_s1, int64_t n_rows, bool vec_in) {
+                    float* __restrict__ kref, int64_t kref_s0, int64_t kref_s1, int64_t n_rows, bool vec_in,
+                    bool res_raw, bool kref_vec, Shifts sh) {
   const int lane = threadIdx.x & 31;
-  const int64_t row = WIDE ? (int64_t)blockIdx.x : blockIdx.x * (int64_t)WT_WARPS + (threadIdx.x >> 5);
+  const int64_t row = MODE == 2 ? (int64_t)blockIdx.x : blockIdx.x * (int64_t)WT_WARPS + (threadIdx.x >> 5);
   if (row >= n_rows) return;
   const int64_t slot = tok[row];
   if (slot < 0) return;  // padding, or a token that is not stored
-  const int64_t blk = slot / L.BS;
-  const int off = (int)(slot % L.BS);
+  const int64_t blk = sh.BS >= 0 ? slot >> sh.BS : slot / L.BS;
+  const int off = (int)(slot - blk * L.BS);
   const int bits = block_bits(pages, L, blk);
   const float levels = (float)((1 << bits) - 1);
-  const int64_t rowoff = row_offset(pages, L, blk, off, bits);
+  RowWalk walk;
+  walk.start(pages, L, sh.BS, blk, off, bits);
+  const int64_t rowoff = walk.offset();
   const int side_bytes = (L.H * L.D * bits) / 8;
   const int head_bytes = (L.D * bits) / 8;
   uint8_t* page = pages + blk * L.PS;
   const int units = (L.H * L.D) / 8;  // 8-channel pieces of a row
-  const int first = WIDE ? threadIdx.x : lane, step = WIDE ? WT_WARPS * 32 : 32;
+  const int first = MODE == 2 ? threadIdx.x : lane, step = MODE == 2 ? WT_WARPS * 32 : 32;
 
-  if constexpr (WIDE) {
+  if constexpr (MODE != 0) {
     // V: per token, groups of VG along head_dim; VG / 8 neighbouring threads share a group.
     const int upg = L.VG / 8;
-    for (int base = (threadIdx.x >> 5) * 32; base < units; base += step) {
+    for (int base = first - lane; base < units; base += step) {
       const int u = base + lane;
       const bool on = u < units;
-      const int h = on ? (u * 8) / L.D : 0, d0 = on ? (u * 8) % L.D : 0;
+      const int h = on ? qdiv(u * 8, L.D, sh.D) : 0, d0 = on ? qmod(u * 8, L.D, sh.D) : 0;
       float x[8];
       float mn = INFINITY, mx = -INFINITY;
       if (on) {
@@ -78,16 +246,13 @@ write_tokens_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restric
       __half s16, m16;
       group_stats(mn, mx, levels, s16, m16);
       const float sc = __half2float(s16), m = __half2float(m16);
-      if (d0 % L.VG == 0) {
-        const int64_t e = ((int64_t)off * L.H + h) * L.NG + d0 / L.VG;
+      if (qmod(d0, L.VG, sh.VG) == 0) {
+        const int64_t e = ((int64_t)off * L.H + h) * L.NG + qdiv(d0, L.VG, sh.VG);
         reinterpret_cast<__half*>(page + L.o_vs)[e] = s16;
         reinterpret_cast<__half*>(page + L.o_vm)[e] = m16;
       }
       const float rsc = __frcp_rn(sc);
-      uint32_t q[8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k) q[k] = quant_code_r(x[k], m, sc, rsc, levels);
-      store_packed8(pages + rowoff + side_bytes + h * head_bytes + (d0 * bits) / 8, pack8(q, bits), bits);
+      quant_store8<false>(bits, pages + rowoff + side_bytes + h * head_bytes + (d0 * bits) / 8, x, &m, &sc, &rsc);
     }
   } else {
     // V: per token, groups of VG along head_dim; one lane per group.
@@ -111,10 +276,7 @@ write_tokens_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restric
       const float rsc = __frcp_rn(sc);
       for (int c = 0; c < L.VG; c += 8) {
         ld8<T>(value, src + c, vec_in, x);
-        uint32_t q[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) q[k] = quant_code_r(x[k], m, sc, rsc, levels);
-        store_packed8(dst + (c * bits) / 8, pack8(q, bits), bits);
+        quant_store8<false>(bits, dst + (c * bits) / 8, x, &m, &sc, &rsc);
       }
     }
   }
@@ -124,13 +286,19 @@ write_tokens_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restric
   const bool sealed = tok[2 * tok_s0 + row] != 0;
   const int64_t kidx = kref ? tok[3 * tok_s0 + row] : -1;
   if (rslot < 0 && !sealed && kidx < 0) return;
-  const int grp = off / L.KG;
+  const int grp = qdiv(off, L.KG, sh.KG), gpos = off - grp * L.KG;
   for (int c = first; c < units; c += step) {
-    const int h = (c * 8) / L.D, d0 = (c * 8) % L.D;
+    const int h = qdiv(c * 8, L.D, sh.D), d0 = qmod(c * 8, L.D, sh.D);
+    const int64_t src = row * k_s0 + h * k_s1 + d0;
+    if (rslot >= 0 && res_raw) {
+      const int64_t ro = rslot * r_s0 + (int64_t)gpos * r_s1 + h * r_s2 + d0;
+      *reinterpret_cast<uint4*>(reinterpret_cast<T*>(res) + ro) = *reinterpret_cast<const uint4*>(key + src);
+      if (!sealed && kidx < 0) continue;
+    }
     float x[8];
-    ld8<T>(key, row * k_s0 + h * k_s1 + d0, vec_in, x);
-    if (rslot >= 0) {
-      const int64_t ro = rslot * r_s0 + (int64_t)(off % L.KG) * r_s1 + h * r_s2 + d0;
+    ld8<T>(key, src, vec_in, x);
+    if (rslot >= 0 && !res_raw) {
+      const int64_t ro = rslot * r_s0 + (int64_t)gpos * r_s1 + h * r_s2 + d0;
 #pragma unroll
       for (int k = 0; k < 8; ++k) st_dt(res, res_dt, ro + k, x[k]);
     }
@@ -145,21 +313,27 @@ write_tokens_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restric
     }
     if (kidx >= 0) {
       float* dst = kref + kidx * kref_s0 + h * kref_s1 + d0;
+      if (kref_vec) {
+        reinterpret_cast<float4*>(dst)[0] = make_float4(x[0], x[1], x[2], x[3]);
+        reinterpret_cast<float4*>(dst)[1] = make_float4(x[4], x[5], x[6], x[7]);
+      } else {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) dst[k] = x[k];
+        for (int k = 0; k < 8; ++k) dst[k] = x[k];
+      }
     }
   }
 }
 
 // One CTA per completed K group; each thread owns 8 channels of one head over the KG tokens
 // (kernels/write.py:231-287).  SEAL: the group's first `fill` tokens come from residual slot
-// `seal_slot` and header byte 1 is set (tiered_cache.py:379-394).
+// `seal_slot` and header byte 1 is set (tiered_cache.py:379-394).  `raw16`: key rows and residual rows are
+// 16-byte aligned rows of the same 16-bit type T, so both passes work on 16-byte words as loaded.
 template <typename T, bool SEAL>
 __global__ void __launch_bounds__(256)
 finalize_k_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restrict__ key, int64_t k_s0, int64_t k_s1,
                   const int64_t* __restrict__ fin, const int64_t* __restrict__ fin_count, const void* res, int res_dt,
-                  int64_t r_s0, int64_t r_s1, int64_t r_s2, bool vec_in, int64_t seal_slot, int64_t seal_block,
-                  int seal_group, int seal_fill, int seal_bits, int seal_mask) {
+                  int64_t r_s0, int64_t r_s1, int64_t r_s2, bool vec_in, bool raw16, Shifts sh, int64_t seal_slot,
+                  int64_t seal_block, int seal_group, int seal_fill, int seal_bits, int seal_mask) {
   int64_t blk, rslot;
   int grp, ntok, bits;
   const int64_t* rows = nullptr;
@@ -178,10 +352,8 @@ finalize_k_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restrict_
   const int64_t rs = rslot < 0 ? 0 : rslot;
 
   for (int c = threadIdx.x; c < (L.H * L.D) / 8; c += blockDim.x) {
-    const int h = (c * 8) / L.D, d0 = (c * 8) % L.D;
+    const int h = qdiv(c * 8, L.D, sh.D), d0 = qmod(c * 8, L.D, sh.D);
     float mn[8], mx[8], x[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) { mn[k] = INFINITY; mx[k] = -INFINITY; }
     auto load = [&](int p) {
       const int64_t r = SEAL ? -1 : rows[p];
       if (r >= 0) {
@@ -192,10 +364,29 @@ finalize_k_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restrict_
         for (int k = 0; k < 8; ++k) x[k] = ld_dt(res, res_dt, ro + k);
       }
     };
-    for (int p = 0; p < ntok; ++p) {
-      load(p);
+    auto load_raw = [&](int p) -> uint4 {
+      const int64_t r = SEAL ? -1 : rows[p];
+      const T* src = r >= 0 ? key + (r * k_s0 + h * k_s1 + d0)
+                            : reinterpret_cast<const T*>(res) + (rs * r_s0 + (int64_t)p * r_s1 + h * r_s2 + d0);
+      return *reinterpret_cast<const uint4*>(src);
+    };
+    if constexpr (sizeof(T) == 2) {
+      if (raw16) {
+        MinMax8<T> acc;
+        acc.init();
+#pragma unroll 4
+        for (int p = 0; p < ntok; ++p) acc.update(load_raw(p));
+        acc.finish(mn, mx);
+      }
+    }
+    if (sizeof(T) != 2 || !raw16) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) { mn[k] = fminf(mn[k], x[k]); mx[k] = fmaxf(mx[k], x[k]); }
+      for (int k = 0; k < 8; ++k) { mn[k] = INFINITY; mx[k] = -INFINITY; }
+      for (int p = 0; p < ntok; ++p) {
+        load(p);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { mn[k] = fminf(mn[k], x[k]); mx[k] = fmaxf(mx[k], x[k]); }
+      }
     }
     __align__(16) __half s16[8], m16[8];
     float sc[8], m[8], rsc[8];
@@ -208,13 +399,17 @@ finalize_k_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restrict_
     const int64_t e = ((int64_t)grp * L.H + h) * L.D + d0;
     *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(page + L.o_ks) + e) = *reinterpret_cast<uint4*>(s16);
     *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(page + L.o_km) + e) = *reinterpret_cast<uint4*>(m16);
+    RowWalk walk;
+    walk.start(pages, L, sh.BS, blk, grp * L.KG, bits);
     for (int p = 0; p < ntok; ++p) {
-      load(p);
-      uint32_t q[8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k) q[k] = quant_code_r(x[k], m[k], sc[k], rsc[k], levels);
-      const int64_t ro = row_offset(pages, L, blk, grp * L.KG + p, bits);
-      store_packed8(pages + ro + h * head_bytes + (d0 * bits) / 8, pack8(q, bits), bits);
+      if constexpr (sizeof(T) == 2) {
+        if (raw16) cvt8<T>(load_raw(p), x);
+        else load(p);
+      } else {
+        load(p);
+      }
+      quant_store8<true>(bits, pages + walk.offset() + h * head_bytes + (d0 * bits) / 8, x, m, sc, rsc);
+      if (p + 1 < ntok) walk.next(pages, L);
     }
   }
   if constexpr (SEAL) {
@@ -226,10 +421,19 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 template <typename T>
 static bool vec_ok(const void* a, int64_t s0, int64_t s1) {
-  const int64_t q = 16 / (int64_t)sizeof(T) * (sizeof(T) == 4 ? 2 : 1);  // elements per 8-chunk alignment unit
-  (void)q;
   const int64_t unit = 16 / (int64_t)sizeof(T);  // elements per 16 bytes
   return aligned16(a) && s0 % unit == 0 && s1 % unit == 0;
+}
+
+template <typename T> constexpr int dtype_code() {
+  return std::is_same<T, float>::value ? ECHOKV_DT_F32 : (std::is_same<T, __half>::value ? ECHOKV_DT_F16 : ECHOKV_DT_BF16);
+}
+
+// The residual buffer holds rows of the 16-bit type T, every one on a 16-byte boundary.
+template <typename T>
+static bool residual_raw(const ResidualDev& R) {
+  return sizeof(T) == 2 && R.base && R.dtype == dtype_code<T>() && aligned16(R.base) && R.s_slot % 8 == 0 &&
+         R.s_pos % 8 == 0 && R.s_head % 8 == 0;
 }
 
 }  // namespace echokv
@@ -282,18 +486,22 @@ int echokv_write_tokens(const echokv_layout* layout, const echokv_pages* pages, 
   if (rc) return rc;
   if (!key || !value || !tok) return set_error(ECHOKV_E_ARGUMENT, "write_tokens: null pointer");
   const int upg = L.VG / 8;  // 8-channel pieces per V group
+  const bool shuffle = L.VG % 8 == 0 && upg <= 32 && (upg & (upg - 1)) == 0 && L.D % L.VG == 0;
   // few rows (a decode step): spread each row over a CTA to shorten the dependent chain; many rows
   // (prefill chunks): one warp per row keeps more rows in flight per SM
-  const bool wide = n_rows <= 1024 && L.VG % 8 == 0 && upg <= 32 && (upg & (upg - 1)) == 0 && L.D % L.VG == 0;
-  const unsigned grid = wide ? (unsigned)n_rows : (unsigned)((n_rows + WT_WARPS - 1) / WT_WARPS);
+  const int mode = !shuffle ? 0 : (n_rows <= 1024 ? 2 : 1);
+  const unsigned grid = mode == 2 ? (unsigned)n_rows : (unsigned)((n_rows + WT_WARPS - 1) / WT_WARPS);
+  const bool kref_vec = kref && aligned16(kref) && kref_s0 % 4 == 0 && kref_s1 % 4 == 0;
   cudaStream_t st = (cudaStream_t)stream;
 #define ARGS(T)                                                                                                \
       L, (uint8_t*)pages->base, (const T*)key, k_s0, k_s1, (const T*)value, v_s0, v_s1, tok, tok_s0,            \
       const_cast<void*>(R.base), R.dtype, R.s_slot, R.s_pos, R.s_head, kref, kref_s0, kref_s1, n_rows,          \
-      vec_ok<T>(key, k_s0, k_s1) && vec_ok<T>(value, v_s0, v_s1)
-#define LAUNCH(T)                                                                       \
-  if (wide) write_tokens_kernel<T, true><<<grid, WT_WARPS * 32, 0, st>>>(ARGS(T));      \
-  else write_tokens_kernel<T, false><<<grid, WT_WARPS * 32, 0, st>>>(ARGS(T))
+      vec_ok<T>(key, k_s0, k_s1) && vec_ok<T>(value, v_s0, v_s1), residual_raw<T>(R) && vec_ok<T>(key, k_s0, k_s1), \
+      kref_vec, make_shifts(L)
+#define LAUNCH(T)                                                                                   \
+  if (mode == 2) write_tokens_kernel<T, 2><<<grid, WT_WARPS * 32, 0, st>>>(ARGS(T));                \
+  else if (mode == 1) write_tokens_kernel<T, 1><<<grid, WT_WARPS * 32, 0, st>>>(ARGS(T));           \
+  else write_tokens_kernel<T, 0><<<grid, WT_WARPS * 32, 0, st>>>(ARGS(T))
   switch (kv_dtype) {
     case ECHOKV_DT_F32: LAUNCH(float); break;
     case ECHOKV_DT_F16: LAUNCH(__half); break;
@@ -321,7 +529,8 @@ int echokv_finalize_k(const echokv_layout* layout, const echokv_pages* pages, co
 #define LAUNCH(T)                                                                                            \
   finalize_k_kernel<T, false><<<(unsigned)n_launch, threads, 0, st>>>(                                       \
       L, (uint8_t*)pages->base, (const T*)key, k_s0, k_s1, fin, fin_count, R.base, R.dtype, R.s_slot, R.s_pos, \
-      R.s_head, vec_ok<T>(key, k_s0, k_s1), 0, 0, 0, 0, 0, 0)
+      R.s_head, vec_ok<T>(key, k_s0, k_s1), vec_ok<T>(key, k_s0, k_s1) && residual_raw<T>(R), make_shifts(L), 0, 0, 0, 0, \
+      0, 0)
   switch (kv_dtype) {
     case ECHOKV_DT_F32: LAUNCH(float); break;
     case ECHOKV_DT_F16: LAUNCH(__half); break;
@@ -348,7 +557,7 @@ int echokv_seal_group(const echokv_layout* layout, const echokv_pages* pages, co
   const int threads = (L.H * L.D / 8) < 256 ? ((L.H * L.D / 8 + 31) / 32 * 32) : 256;
   finalize_k_kernel<float, true><<<1, threads, 0, (cudaStream_t)stream>>>(
       L, (uint8_t*)pages->base, nullptr, 0, 0, nullptr, nullptr, R.base, R.dtype, R.s_slot, R.s_pos, R.s_head, false,
-      slot, block, group, fill, bits, sealed_mask);
+      false, make_shifts(L), slot, block, group, fill, bits, sealed_mask);
   return check_launch("seal_group");
 }
 

@@ -11,7 +11,43 @@ import torch
 from echokv_b200 import _native as N
 
 BLOCKS_PER_SPLIT = 16
-MAX_DECODE_SPLITS = 32  # upper bound of the split grid (backend.py:67-69 of the reference caps its fixed grid alike)
+MAX_DECODE_SPLITS = 64  # upper bound of the split grid (backend.py:67-69 of the reference caps its fixed grid alike)
+MIN_SPLIT_TOKENS = 64   # smallest split `choose_blocks_per_split` proposes
+ITEM_COST_TILES = 4     # fixed cost of a (sequence, split) work item in units of one 16-token tile's work
+
+
+def decode_parallelism(store, num_q_heads: int) -> int:
+    """Work items the split kernel has in work at once on the current device (0: generic kernel)."""
+    return int(N.lib.echokv_decode_parallelism(store.c_layout, int(num_q_heads)))
+
+
+def choose_blocks_per_split(lens, block_size: int, num_splits: int, slots: int) -> int:
+    """Blocks per split for one decode step of sequences with cache lengths ``lens``.
+
+    The split kernel works on ``slots`` (sequence, split) items at a time, so the step takes
+    ``ceil(items / slots)`` waves of one item's time each: a split of b blocks costs ``b * block_size / 16 +
+    ITEM_COST_TILES``.  Every split count up to ``num_splits`` is tried on the mean sequence and the
+    cheapest wins (ties: fewer, larger splits, which leave less to merge).  The value is a launch
+    parameter shared by all sequences of the step, so for a given value results stay batch-invariant.
+    """
+    import numpy as np
+
+    lens = np.asarray(lens)
+    live = lens[lens > 0]
+    if live.size == 0 or slots <= 0:
+        return BLOCKS_PER_SPLIT
+    nb = int(np.ceil(np.mean(-(-live // block_size))))
+    tiles = max(1, block_size // 16)
+    floor = max(1, MIN_SPLIT_TOKENS // block_size)
+    best = None
+    for s in range(1, max(1, num_splits) + 1):
+        b = max(floor, -(-nb // s))
+        used = -(-nb // b)
+        waves = -(-(int(live.size) * used) // slots)
+        cost = waves * (b * tiles + ITEM_COST_TILES)
+        if best is None or cost < best[0] or (cost == best[0] and b > best[1]):
+            best = (cost, b)
+    return best[1]
 
 
 class _Scratch:
@@ -50,7 +86,7 @@ def decode_attention(store, query: torch.Tensor, block_table: torch.Tensor, seq_
                      softmax_scale: float, blocks_per_split: int = BLOCKS_PER_SPLIT,
                      q_rows: torch.Tensor | None = None, bt_rows: torch.Tensor | None = None,
                      out: torch.Tensor | None = None, max_len: int | None = None,
-                     num_splits: int | None = None) -> torch.Tensor:
+                     num_splits: int | None = None, bps_dev: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of one query token per sequence over each sequence's cache.
 
     Sequence ``i`` uses query row ``q_rows[i]`` and block-table row ``bt_rows[i]``
@@ -59,7 +95,9 @@ def decode_attention(store, query: torch.Tensor, block_table: torch.Tensor, seq_
     ``out[q_rows[i]]`` in ``out``'s dtype; length-0 sequences (CUDA-graph padding)
     leave their row untouched.  Each sequence is cut into at most ``num_splits``
     splits of ``max(blocks_per_split, ceil(blocks / num_splits))`` blocks -- a
-    function of the sequence alone, so results are batch-invariant.
+    function of the sequence alone, so results are batch-invariant.  ``bps_dev`` (one int32 on the
+    device, or the low half of an int64) raises ``blocks_per_split`` at run time: a captured graph
+    keeps reading it, so the host can size the splits for every replayed step.
     """
     L = store.layout
     N.require_cuda(query, block_table, seq_lens, out)
@@ -89,11 +127,15 @@ def decode_attention(store, query: torch.Tensor, block_table: torch.Tensor, seq_
         return out
     nbytes = N.lib.echokv_decode_scratch_bytes(s, hq, L.head_size, num_splits)
     scratch = _scratch.get(dev, nbytes)
-    N.check(N.lib.echokv_decode(
+    if bps_dev is not None:
+        N.require_cuda(bps_dev)
+        if bps_dev.dtype not in (torch.int32, torch.int64) or bps_dev.numel() < 1:
+            raise TypeError("bps_dev must hold one int32 / int64 on the device")
+    N.check(N.lib.echokv_decode_ex(
         store.c_layout, store.c_pages, store.c_res,
         query.data_ptr(), query.stride(0), query.stride(1), N.dtype_code(query.dtype), N.ptr(q_rows),
         block_table.data_ptr(), block_table.stride(0), N.ptr(bt_rows), lens.data_ptr(),
         scratch.data_ptr(), scratch.numel(),
         out.data_ptr(), out.stride(0), out.stride(1), N.dtype_code(out.dtype),
-        float(softmax_scale), int(num_splits), int(blocks_per_split), s, hq, N.stream_ptr(dev)))
+        float(softmax_scale), int(num_splits), int(blocks_per_split), N.ptr(bps_dev), s, hq, N.stream_ptr(dev)))
     return out

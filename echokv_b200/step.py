@@ -23,7 +23,8 @@ import torch
 from echokv_b200.canary import canary_kl_ring, tp_mean
 from echokv_b200.controller import LayerController
 from echokv_b200.quant import SUPPORTED_BITS
-from echokv_b200.kernels.decode import BLOCKS_PER_SPLIT, MAX_DECODE_SPLITS, decode_attention
+from echokv_b200.kernels.decode import (BLOCKS_PER_SPLIT, MAX_DECODE_SPLITS, MIN_SPLIT_TOKENS, choose_blocks_per_split,
+                                        decode_attention, decode_parallelism)
 from echokv_b200.kernels.write import gather_rows
 from echokv_b200.tiered_cache import TieredKVCache, TieredLayout
 from echokv_b200.write_plan import SharedState, WriteMeta
@@ -34,7 +35,7 @@ class Staging:
 
     Element layout (every region starts at an even element = 16-byte boundary):
 
-        [0] n_fin  [1] 0 | canary rows (nq) | decode rows, requests, lengths (3 x cap)
+        [0] n_fin  [1] blocks per decode split | canary rows (nq) | decode rows, requests, lengths (3 x cap)
         | token arrays slot, residual, sealed, kref (4 x cap) | completed groups (cap x w) | tail
 
     Steps with at most ``cap`` rows / groups use the persistent buffer, whose
@@ -64,8 +65,9 @@ class Staging:
         o_tail = o_fin + cf * self.w
         return o_tok, o_fin, o_tail + (o_tail & 1)
 
-    def stage(self, n_fin: int, canary: np.ndarray, decode, tok, fin: np.ndarray, tail: list[np.ndarray]):
-        """Upload a step; returns device views ``(fin_count, canary, [3 decode], tok [4, t], fin, tail views)``."""
+    def stage(self, n_fin: int, canary: np.ndarray, decode, tok, fin: np.ndarray, tail: list[np.ndarray], bps: int = 0):
+        """Upload a step; returns device views ``(fin_count, canary, [3 decode], tok [4, t], fin, tail views,
+        blocks per split)``."""
         s, t = decode[0].size, tok[0].size
         fits = max(s, t, n_fin) <= self.cap
         tail_sizes = [a.size + (a.size & 1) for a in tail]
@@ -83,7 +85,7 @@ class Staging:
             hbuf = torch.zeros(total, dtype=torch.long).pin_memory()
             h = hbuf.numpy()
         o_tok, o_fin, o_tail = self._offsets(cd, ct, cf)
-        h[0], h[1] = n_fin, 0
+        h[0], h[1] = n_fin, bps
         h[2: 2 + self.nq] = canary
         for k, a in enumerate(decode):
             h[self.o_dec + k * cd: self.o_dec + k * cd + s] = a
@@ -124,6 +126,7 @@ class Staging:
             dev[o_tok: o_tok + 4 * ct].view(4, ct)[:, :t],
             dev[o_fin: o_fin + cf * self.w].view(cf, self.w),
             views,
+            dev[1:2],
         )
 
 
@@ -137,6 +140,7 @@ class StepMeta:
     decode_reqs: torch.Tensor | None
     decode_lens: torch.Tensor | None
     num_splits: int
+    bps_dev: torch.Tensor | None = None  # blocks per decode split of this step (one int64 on the device)
 
 
 class GroupRunner:
@@ -172,8 +176,13 @@ class GroupRunner:
         self.cap = cap
         tail = cap * (4 + 3 * len(caches)) + 64
         self.staging = Staging(cap, canary_max_q, 3 + g, tail, dev)
+        # The split grid is fixed (a graph replays it); how many of its splits a step uses follows from the
+        # blocks per split chosen for that step in `plan_step`, never less than `split_floor` blocks.
         max_blocks = -(-max_model_len // layout.block_size)
-        self.num_splits = max(1, min(-(-max_blocks // BLOCKS_PER_SPLIT), MAX_DECODE_SPLITS))
+        self.split_floor = max(1, MIN_SPLIT_TOKENS // layout.block_size)
+        self.num_splits = max(1, min(-(-max_blocks // self.split_floor), MAX_DECODE_SPLITS))
+        with torch.cuda.device(dev):
+            self.decode_slots = decode_parallelism(self.stores[0], num_q_heads)
 
     # -- host side, once per step ---------------------------------------------------------
     def plan_step(self, slots_cpu, decode=None, canary: np.ndarray | None = None) -> StepMeta:
@@ -201,15 +210,18 @@ class GroupRunner:
         empty = np.zeros(0, dtype=np.int64)
         dec = decode if decode is not None else (empty, empty, empty)
         can = np.zeros(self.canary_max_q, dtype=np.int64) if canary is None else canary
-        fin_count, canary_rows, dviews, tok, fin, views = self.staging.stage(
-            plan.n_fin, can, dec, (plan.tok_slot, plan.tok_res, plan.tok_sealed, plan.tok_kref), plan.fin, tail)
+        bps = BLOCKS_PER_SPLIT
+        if self.decode_slots and dec[2].size:
+            bps = choose_blocks_per_split(dec[2], self.layout.block_size, self.num_splits, self.decode_slots)
+        fin_count, canary_rows, dviews, tok, fin, views, bps_dev = self.staging.stage(
+            plan.n_fin, can, dec, (plan.tok_slot, plan.tok_res, plan.tok_sealed, plan.tok_kref), plan.fin, tail, bps)
         shared.apply_res_map(*views[:4])
         for st, ids, hdr in zip(self.stores, views[4::2], views[5::2]):
             st.write_headers(ids, hdr.view(torch.uint8).view(-1, 16))
         write = WriteMeta(tok=tok, fin=fin, fin_count=fin_count, n_rows=plan.n_rows, n_fin=plan.n_fin)
         has_dec = decode is not None and dec[0].size > 0
         return StepMeta(write, canary_rows, dviews[0] if has_dec else None, dviews[1] if has_dec else None,
-                        dviews[2] if has_dec else None, self.num_splits)
+                        dviews[2] if has_dec else None, self.num_splits, bps_dev)
 
     # -- canary (reference: EchoKVMetadataBuilder._run_canary, backend.py:314-333) --------------
     def stash_queries(self, layer: int, query: torch.Tensor, meta: StepMeta) -> None:
@@ -259,5 +271,6 @@ class GroupRunner:
 
     def decode(self, layer: int, query: torch.Tensor, block_table: torch.Tensor, out: torch.Tensor,
                meta: StepMeta) -> None:
-        decode_attention(self.stores[layer], query, block_table, meta.decode_lens, self.scale,
-                         q_rows=meta.decode_rows, bt_rows=meta.decode_reqs, out=out, num_splits=meta.num_splits)
+        decode_attention(self.stores[layer], query, block_table, meta.decode_lens, self.scale, self.split_floor,
+                         q_rows=meta.decode_rows, bt_rows=meta.decode_reqs, out=out, num_splits=meta.num_splits,
+                         bps_dev=meta.bps_dev)

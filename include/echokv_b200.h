@@ -162,6 +162,26 @@ int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const 
                   float softmax_scale, int32_t num_splits, int32_t blocks_per_split,
                   int64_t num_seqs, int32_t num_q_heads, void* stream);
 
+/* echokv_decode with the blocks per split also given at run time: when `blocks_per_split_dev` is not NULL
+ * the kernels read one int32 from that device address and use max(blocks_per_split, that value) in the split
+ * rule above.  A CUDA graph bakes the by-value arguments of a captured call; a host that replays such a
+ * graph writes the value for the coming step into that word (on the same stream) and so keeps choosing the
+ * split size per step.  The reference fixes BLOCKS_PER_SPLIT per process (kernels/decode.py:41); for a given
+ * value the results are the same bits as echokv_decode's with blocks_per_split = max(both). */
+int echokv_decode_ex(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                     const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype, const int64_t* q_rows,
+                     const int32_t* block_table, int64_t bt_s0, const int64_t* bt_rows, const int64_t* lens,
+                     void* scratch, int64_t scratch_bytes,
+                     void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
+                     float softmax_scale, int32_t num_splits, int32_t blocks_per_split,
+                     const int32_t* blocks_per_split_dev, int64_t num_seqs, int32_t num_q_heads, void* stream);
+
+/* How many work items (sequence, split) the split kernel works on at the same time on the current device for
+ * this layout and number of query heads, or 0 when the shape takes the generic kernel (one CTA per item and KV
+ * head).  A host that picks the split size per step sizes the splits so that the items fill this many slots
+ * in whole waves.  No counterpart in the reference (Triton sizes its grid from the item count). */
+int32_t echokv_decode_parallelism(const echokv_layout* layout, int32_t num_q_heads);
+
 /* echokv_decode for callers that cannot allocate scratch (it has no counterpart in the reference,
  * which allocates its split buffers with torch on every call).  Meant for hosts that are not
  * allowed to allocate device memory where they call this: a plugin running inside another
