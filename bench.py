@@ -477,9 +477,8 @@ def config5_probe(a, dev, world: int, rank: int, peaks: dict) -> dict | None:
     def device_step(meta, capturing=False):
         for it in range(L5):
             l = it % R
-            runner.write(l, kn[l], vn[l], meta, capturing=capturing)
+            runner.write(l, kn[l], vn[l], meta, capturing=capturing, query=q[l])  # + the canary's query rows
             runner.decode(l, q[l], table, out[l], meta)
-            runner.stash_queries(l, q[l], meta)
 
     meta = host_plan()
     device_step(meta)
@@ -663,12 +662,13 @@ def run_b200(a) -> None:
 
     def device_step(meta, capturing=False):
         for l in range(Lr):
-            runner.write(l, k_dev[l], v_dev[l], meta, capturing=capturing)
+            # quantize-on-write + the canary's query rows (captured unconditionally) in one launch, then decode
+            runner.write(l, k_dev[l], v_dev[l], meta, capturing=capturing, query=q_dev[l])
             runner.decode(l, q_dev[l], table, out_dev[l], meta)
-            runner.stash_queries(l, q_dev[l], meta)  # the canary's query rows (captured unconditionally)
 
-    # kernels launched per step: finalize_k, write_tokens, decode (split + merge), canary stash per layer
-    launches_per_step = 5 * Lr
+    # kernels launched per step and layer: write_step (completed K groups + token rows + canary stash), the decode
+    # split kernel and its merge (a memset node zeroes the split kernel's work counter before it)
+    launches_per_step = 3 * Lr
     graph = None
     meta = host_plan()
     device_step(meta)  # eager step: sizes the decode scratch, touches every kernel

@@ -71,6 +71,8 @@ _SIGS = {
     "echokv_scatter_i64": [_P, _P, _P, _I64, _P],
     "echokv_write_tokens": [_LP, _PP, _P, _I64, _I64, _P, _I64, _I64, _I32, _P, _I64, _RP, _P, _I64, _I64, _I64, _P],
     "echokv_finalize_k": [_LP, _PP, _P, _I64, _I64, _I32, _P, _P, _RP, _I64, _P],
+    "echokv_write_step": [_LP, _PP, _P, _I64, _I64, _P, _I64, _I64, _I32, _P, _I64, _RP, _P, _I64, _I64, _I64, _P, _P, _I64,
+                          _P, _I64, _P, _I64, _P, _I64, _P],
     "echokv_seal_group": [_LP, _PP, _RP, _I64, _I64, _I32, _I32, _I32, _I32, _P],
     "echokv_demote_blocks": [_LP, _PP, _RP, _P, _I64, _P, _I64, _P],
     "echokv_gather": [_LP, _PP, _RP, _P, _P, _I64, _P, _P, _P],

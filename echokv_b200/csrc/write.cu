@@ -199,16 +199,37 @@ struct RowWalk {
 // other group sizes.  All produce the same bytes: min and max do not depend on the order of reduction.
 // `res_raw`: the residual buffer has the rows' own 16-bit type and 16-byte aligned rows, so an open group's key
 // goes there as loaded; `kref_vec`: 16-byte aligned K_ref rows.
+template <typename T>
+struct TokArgs {
+  LayoutDev L;
+  uint8_t* pages;
+  const T* key; int64_t k_s0, k_s1;
+  const T* value; int64_t v_s0, v_s1;
+  const int64_t* tok; int64_t tok_s0;
+  void* res; int res_dt; int64_t r_s0, r_s1, r_s2;
+  float* kref; int64_t kref_s0, kref_s1;
+  int64_t n_rows;
+  bool vec_in, res_raw, kref_vec;
+  Shifts sh;
+};
+
+// One token row.  `row_in_cta`: row index this CTA / warp works on; `skip_residual`: the row's open-group key is
+// stored by someone else (see write_step_kernel).
 template <typename T, int MODE>
-__global__ void __launch_bounds__(WT_WARPS * 32)
-write_tokens_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restrict__ key, int64_t k_s0, int64_t k_s1,
-                    const T* __restrict__ value, int64_t v_s0, int64_t v_s1, const int64_t* __restrict__ tok,
-                    int64_t tok_s0, void* res, int res_dt, int64_t r_s0, int64_t r_s1, int64_t r_s2,
-                    float* __restrict__ kref, int64_t kref_s0, int64_t kref_s1, int64_t n_rows, bool vec_in,
-                    bool res_raw, bool kref_vec, Shifts sh) {
+__device__ __forceinline__ void token_row(const TokArgs<T>& A, int64_t row, bool skip_residual) {
+  const LayoutDev& L = A.L;
+  uint8_t* __restrict__ pages = A.pages;
+  const T* __restrict__ key = A.key;
+  const T* __restrict__ value = A.value;
+  const int64_t* __restrict__ tok = A.tok;
+  const int64_t k_s0 = A.k_s0, k_s1 = A.k_s1, v_s0 = A.v_s0, v_s1 = A.v_s1, tok_s0 = A.tok_s0;
+  void* res = A.res;
+  const int res_dt = A.res_dt;
+  const int64_t r_s0 = A.r_s0, r_s1 = A.r_s1, r_s2 = A.r_s2, kref_s0 = A.kref_s0, kref_s1 = A.kref_s1;
+  float* __restrict__ kref = A.kref;
+  const bool vec_in = A.vec_in, res_raw = A.res_raw, kref_vec = A.kref_vec;
+  const Shifts sh = A.sh;
   const int lane = threadIdx.x & 31;
-  const int64_t row = MODE == 2 ? (int64_t)blockIdx.x : blockIdx.x * (int64_t)WT_WARPS + (threadIdx.x >> 5);
-  if (row >= n_rows) return;
   const int64_t slot = tok[row];
   if (slot < 0) return;  // padding, or a token that is not stored
   const int64_t blk = sh.BS >= 0 ? slot >> sh.BS : slot / L.BS;
@@ -282,7 +303,7 @@ write_tokens_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restric
   }
 
   // K: residual row (open group), codes under stored stats (sealed group), K_ref ring row.
-  const int64_t rslot = tok[tok_s0 + row];
+  const int64_t rslot = skip_residual ? -1 : tok[tok_s0 + row];
   const bool sealed = tok[2 * tok_s0 + row] != 0;
   const int64_t kidx = kref ? tok[3 * tok_s0 + row] : -1;
   if (rslot < 0 && !sealed && kidx < 0) return;
@@ -324,25 +345,48 @@ write_tokens_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restric
   }
 }
 
+template <typename T, int MODE>
+__global__ void __launch_bounds__(WT_WARPS * 32) write_tokens_kernel(const TokArgs<T> A) {
+  const int64_t row = MODE == 2 ? (int64_t)blockIdx.x : blockIdx.x * (int64_t)WT_WARPS + (threadIdx.x >> 5);
+  if (row >= A.n_rows) return;
+  token_row<T, MODE>(A, row, false);
+}
+
 // One CTA per completed K group; each thread owns 8 channels of one head over the KG tokens
 // (kernels/write.py:231-287).  SEAL: the group's first `fill` tokens come from residual slot
 // `seal_slot` and header byte 1 is set (tiered_cache.py:379-394).  `raw16`: key rows and residual rows are
 // 16-byte aligned rows of the same 16-bit type T, so both passes work on 16-byte words as loaded.
+template <typename T>
+struct FinArgs {
+  LayoutDev L;
+  uint8_t* pages;
+  const T* key; int64_t k_s0, k_s1;
+  const int64_t* fin; const int64_t* fin_count;
+  const void* res; int res_dt; int64_t r_s0, r_s1, r_s2;
+  bool vec_in, raw16;
+  Shifts sh;
+  int64_t seal_slot, seal_block;
+  int seal_group, seal_fill, seal_bits, seal_mask;
+};
+
+// One K group: line `f` of the completed-group list, or (SEAL) the group the arguments name.
 template <typename T, bool SEAL>
-__global__ void __launch_bounds__(256)
-finalize_k_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restrict__ key, int64_t k_s0, int64_t k_s1,
-                  const int64_t* __restrict__ fin, const int64_t* __restrict__ fin_count, const void* res, int res_dt,
-                  int64_t r_s0, int64_t r_s1, int64_t r_s2, bool vec_in, bool raw16, Shifts sh, int64_t seal_slot,
-                  int64_t seal_block, int seal_group, int seal_fill, int seal_bits, int seal_mask) {
+__device__ __forceinline__ void finalize_group(const FinArgs<T>& A, int64_t f) {
+  const LayoutDev& L = A.L;
+  uint8_t* __restrict__ pages = A.pages;
+  const T* __restrict__ key = A.key;
+  const int64_t k_s0 = A.k_s0, k_s1 = A.k_s1, r_s0 = A.r_s0, r_s1 = A.r_s1, r_s2 = A.r_s2;
+  const void* res = A.res;
+  const int res_dt = A.res_dt;
+  const bool vec_in = A.vec_in, raw16 = A.raw16;
+  const Shifts sh = A.sh;
   int64_t blk, rslot;
   int grp, ntok, bits;
   const int64_t* rows = nullptr;
   if constexpr (SEAL) {
-    blk = seal_block; grp = seal_group; rslot = seal_slot; ntok = seal_fill; bits = seal_bits;
+    blk = A.seal_block; grp = A.seal_group; rslot = A.seal_slot; ntok = A.seal_fill; bits = A.seal_bits;
   } else {
-    const int64_t f = blockIdx.x;
-    if (f >= *fin_count) return;
-    const int64_t* line = fin + f * (3 + L.KG);
+    const int64_t* line = A.fin + f * (3 + L.KG);
     blk = line[0]; grp = (int)line[1]; rslot = line[2]; rows = line + 3; ntok = L.KG;
     bits = block_bits(pages, L, blk);
   }
@@ -413,8 +457,91 @@ finalize_k_kernel(LayoutDev L, uint8_t* __restrict__ pages, const T* __restrict_
     }
   }
   if constexpr (SEAL) {
-    if (threadIdx.x == 0) page[1] = (uint8_t)seal_mask;
+    if (threadIdx.x == 0) page[1] = (uint8_t)A.seal_mask;
   }
+}
+
+template <typename T, bool SEAL>
+__global__ void __launch_bounds__(256) finalize_k_kernel(const FinArgs<T> A) {
+  if constexpr (!SEAL) {
+    if ((int64_t)blockIdx.x >= *A.fin_count) return;
+  }
+  finalize_group<T, SEAL>(A, blockIdx.x);
+}
+
+// A step's writes of one layer in one launch: CTAs [0, n_rows) store the token rows, the next n_fin_launch CTAs
+// quantize the completed K groups (masked by the device-side count), the rest copy `stash_n` rows of `stash_src`
+// (the canary's query rows) to `stash_dst`.  Run one after the other, the group pass comes first because a
+// residual slot a completing group gives up may be taken by a new group in the same step; here the two run at
+// once, so the CTA of a token row whose slot a completing group still reads leaves that key alone, and the
+// group's CTA stores it after its own last read of the slot.
+struct StashArgs {
+  const uint4* src; int64_t src_stride16;
+  const int64_t* rows; int64_t n;
+  uint4* dst; int row16;
+};
+constexpr int STEP_MAX_ROWS = 1024;
+
+template <typename T>
+__global__ void __launch_bounds__(WT_WARPS * 32)
+write_step_kernel(const TokArgs<T> TA, const FinArgs<T> FA, int64_t n_fin_launch, const StashArgs SA) {
+  __shared__ int take[STEP_MAX_ROWS];
+  __shared__ int n_take;
+  const LayoutDev& L = TA.L;
+  const int64_t b = blockIdx.x;
+  const int w = 3 + L.KG;
+  if (b < TA.n_rows) {
+    if (TA.tok[b] < 0) return;  // padding, or a token that is not stored
+    const int64_t rslot = TA.tok[TA.tok_s0 + b];
+    bool skip = false;
+    if (rslot >= 0) {
+      const int64_t n_fin = n_fin_launch > 0 ? min(*FA.fin_count, n_fin_launch) : 0;  // no list, no pointer
+      int hit = 0;
+      for (int64_t f = threadIdx.x; f < n_fin; f += blockDim.x) hit |= FA.fin[f * w + 2] == rslot;
+      skip = __syncthreads_or(hit) != 0;
+    }
+    token_row<T, 2>(TA, b, skip);
+    return;
+  }
+  if (b < TA.n_rows + n_fin_launch) {
+    const int64_t f = b - TA.n_rows;
+    if (f >= *FA.fin_count) return;
+    const int64_t slot = FA.fin[f * w + 2];
+    if (threadIdx.x == 0) n_take = 0;
+    __syncthreads();
+    if (slot >= 0) {
+      for (int r = threadIdx.x; r < (int)TA.n_rows; r += blockDim.x)
+        if (TA.tok[r] >= 0 && TA.tok[TA.tok_s0 + r] == slot) take[atomicAdd(&n_take, 1)] = r;
+    }
+    __syncthreads();
+    finalize_group<T, false>(FA, f);
+    // Keys of the group that takes the slot over: each thread stores the channels it has just read for the last time.
+    const int units = (L.H * L.D) / 8;
+    for (int i = 0; i < n_take; ++i) {
+      const int64_t row = take[i];
+      const int64_t tslot = TA.tok[row];
+      const int off = (int)(tslot - (TA.sh.BS >= 0 ? tslot >> TA.sh.BS : tslot / L.BS) * L.BS);
+      const int gpos = qmod(off, L.KG, TA.sh.KG);
+      for (int c = threadIdx.x; c < units; c += blockDim.x) {
+        const int h = qdiv(c * 8, L.D, TA.sh.D), d0 = qmod(c * 8, L.D, TA.sh.D);
+        const int64_t src = row * TA.k_s0 + h * TA.k_s1 + d0;
+        const int64_t ro = slot * TA.r_s0 + (int64_t)gpos * TA.r_s1 + h * TA.r_s2 + d0;
+        if (TA.res_raw) {
+          *reinterpret_cast<uint4*>(reinterpret_cast<T*>(TA.res) + ro) = *reinterpret_cast<const uint4*>(TA.key + src);
+        } else {
+          float x[8];
+          ld8<T>(TA.key, src, TA.vec_in, x);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) st_dt(TA.res, TA.res_dt, ro + k, x[k]);
+        }
+      }
+    }
+    return;
+  }
+  const int64_t i = (b - TA.n_rows - n_fin_launch) * blockDim.x + threadIdx.x;
+  if (i >= SA.n * SA.row16) return;
+  const int64_t r = i / SA.row16;
+  SA.dst[i] = SA.src[SA.rows[r] * SA.src_stride16 + (i - r * SA.row16)];
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -434,6 +561,46 @@ template <typename T>
 static bool residual_raw(const ResidualDev& R) {
   return sizeof(T) == 2 && R.base && R.dtype == dtype_code<T>() && aligned16(R.base) && R.s_slot % 8 == 0 &&
          R.s_pos % 8 == 0 && R.s_head % 8 == 0;
+}
+
+static bool shuffle_ok(const LayoutDev& L) {  // the V group's min / max can be reduced over VG / 8 neighbouring lanes
+  const int upg = L.VG / 8;
+  return L.VG % 8 == 0 && upg <= 32 && (upg & (upg - 1)) == 0 && L.D % L.VG == 0;
+}
+
+template <typename T>
+static TokArgs<T> tok_args(const LayoutDev& L, const echokv_pages* pages, const ResidualDev& R, const void* key,
+                           int64_t k_s0, int64_t k_s1, const void* value, int64_t v_s0, int64_t v_s1,
+                           const int64_t* tok, int64_t tok_s0, float* kref, int64_t kref_s0, int64_t kref_s1,
+                           int64_t n_rows) {
+  TokArgs<T> A;
+  A.L = L; A.pages = (uint8_t*)pages->base;
+  A.key = (const T*)key; A.k_s0 = k_s0; A.k_s1 = k_s1;
+  A.value = (const T*)value; A.v_s0 = v_s0; A.v_s1 = v_s1;
+  A.tok = tok; A.tok_s0 = tok_s0;
+  A.res = const_cast<void*>(R.base); A.res_dt = R.dtype; A.r_s0 = R.s_slot; A.r_s1 = R.s_pos; A.r_s2 = R.s_head;
+  A.kref = kref; A.kref_s0 = kref_s0; A.kref_s1 = kref_s1;
+  A.n_rows = n_rows;
+  A.vec_in = vec_ok<T>(key, k_s0, k_s1) && vec_ok<T>(value, v_s0, v_s1);
+  A.res_raw = residual_raw<T>(R) && vec_ok<T>(key, k_s0, k_s1);
+  A.kref_vec = kref && aligned16(kref) && kref_s0 % 4 == 0 && kref_s1 % 4 == 0;
+  A.sh = make_shifts(L);
+  return A;
+}
+
+template <typename T>
+static FinArgs<T> fin_args(const LayoutDev& L, const echokv_pages* pages, const ResidualDev& R, const void* key,
+                           int64_t k_s0, int64_t k_s1, const int64_t* fin, const int64_t* fin_count) {
+  FinArgs<T> A;
+  A.L = L; A.pages = (uint8_t*)pages->base;
+  A.key = (const T*)key; A.k_s0 = k_s0; A.k_s1 = k_s1;
+  A.fin = fin; A.fin_count = fin_count;
+  A.res = R.base; A.res_dt = R.dtype; A.r_s0 = R.s_slot; A.r_s1 = R.s_pos; A.r_s2 = R.s_head;
+  A.vec_in = key && vec_ok<T>(key, k_s0, k_s1);
+  A.raw16 = A.vec_in && residual_raw<T>(R);
+  A.sh = make_shifts(L);
+  A.seal_slot = 0; A.seal_block = 0; A.seal_group = 0; A.seal_fill = 0; A.seal_bits = 0; A.seal_mask = 0;
+  return A;
 }
 
 }  // namespace echokv
@@ -485,23 +652,19 @@ int echokv_write_tokens(const echokv_layout* layout, const echokv_pages* pages, 
   rc = make_residual(residual, &R);
   if (rc) return rc;
   if (!key || !value || !tok) return set_error(ECHOKV_E_ARGUMENT, "write_tokens: null pointer");
-  const int upg = L.VG / 8;  // 8-channel pieces per V group
-  const bool shuffle = L.VG % 8 == 0 && upg <= 32 && (upg & (upg - 1)) == 0 && L.D % L.VG == 0;
   // few rows (a decode step): spread each row over a CTA to shorten the dependent chain; many rows
   // (prefill chunks): one warp per row keeps more rows in flight per SM
-  const int mode = !shuffle ? 0 : (n_rows <= 1024 ? 2 : 1);
+  const int mode = !shuffle_ok(L) ? 0 : (n_rows <= STEP_MAX_ROWS ? 2 : 1);
   const unsigned grid = mode == 2 ? (unsigned)n_rows : (unsigned)((n_rows + WT_WARPS - 1) / WT_WARPS);
-  const bool kref_vec = kref && aligned16(kref) && kref_s0 % 4 == 0 && kref_s1 % 4 == 0;
   cudaStream_t st = (cudaStream_t)stream;
-#define ARGS(T)                                                                                                \
-      L, (uint8_t*)pages->base, (const T*)key, k_s0, k_s1, (const T*)value, v_s0, v_s1, tok, tok_s0,            \
-      const_cast<void*>(R.base), R.dtype, R.s_slot, R.s_pos, R.s_head, kref, kref_s0, kref_s1, n_rows,          \
-      vec_ok<T>(key, k_s0, k_s1) && vec_ok<T>(value, v_s0, v_s1), residual_raw<T>(R) && vec_ok<T>(key, k_s0, k_s1), \
-      kref_vec, make_shifts(L)
-#define LAUNCH(T)                                                                                   \
-  if (mode == 2) write_tokens_kernel<T, 2><<<grid, WT_WARPS * 32, 0, st>>>(ARGS(T));                \
-  else if (mode == 1) write_tokens_kernel<T, 1><<<grid, WT_WARPS * 32, 0, st>>>(ARGS(T));           \
-  else write_tokens_kernel<T, 0><<<grid, WT_WARPS * 32, 0, st>>>(ARGS(T))
+#define LAUNCH(T)                                                                                                   \
+  {                                                                                                                 \
+    const TokArgs<T> A = tok_args<T>(L, pages, R, key, k_s0, k_s1, value, v_s0, v_s1, tok, tok_s0, kref, kref_s0,   \
+                                     kref_s1, n_rows);                                                              \
+    if (mode == 2) write_tokens_kernel<T, 2><<<grid, WT_WARPS * 32, 0, st>>>(A);                                    \
+    else if (mode == 1) write_tokens_kernel<T, 1><<<grid, WT_WARPS * 32, 0, st>>>(A);                               \
+    else write_tokens_kernel<T, 0><<<grid, WT_WARPS * 32, 0, st>>>(A);                                              \
+  }
   switch (kv_dtype) {
     case ECHOKV_DT_F32: LAUNCH(float); break;
     case ECHOKV_DT_F16: LAUNCH(__half); break;
@@ -509,7 +672,6 @@ int echokv_write_tokens(const echokv_layout* layout, const echokv_pages* pages, 
     default: return set_error(ECHOKV_E_ARGUMENT, "write_tokens: bad dtype %d", kv_dtype);
   }
 #undef LAUNCH
-#undef ARGS
   return check_launch("write_tokens");
 }
 
@@ -526,11 +688,8 @@ int echokv_finalize_k(const echokv_layout* layout, const echokv_pages* pages, co
   if (!key || !fin || !fin_count) return set_error(ECHOKV_E_ARGUMENT, "finalize_k: null pointer");
   const int threads = (L.H * L.D / 8) < 256 ? ((L.H * L.D / 8 + 31) / 32 * 32) : 256;
   cudaStream_t st = (cudaStream_t)stream;
-#define LAUNCH(T)                                                                                            \
-  finalize_k_kernel<T, false><<<(unsigned)n_launch, threads, 0, st>>>(                                       \
-      L, (uint8_t*)pages->base, (const T*)key, k_s0, k_s1, fin, fin_count, R.base, R.dtype, R.s_slot, R.s_pos, \
-      R.s_head, vec_ok<T>(key, k_s0, k_s1), vec_ok<T>(key, k_s0, k_s1) && residual_raw<T>(R), make_shifts(L), 0, 0, 0, 0, \
-      0, 0)
+#define LAUNCH(T) \
+  finalize_k_kernel<T, false><<<(unsigned)n_launch, threads, 0, st>>>(fin_args<T>(L, pages, R, key, k_s0, k_s1, fin, fin_count))
   switch (kv_dtype) {
     case ECHOKV_DT_F32: LAUNCH(float); break;
     case ECHOKV_DT_F16: LAUNCH(__half); break;
@@ -555,10 +714,59 @@ int echokv_seal_group(const echokv_layout* layout, const echokv_pages* pages, co
       block >= L.NB || slot < 0)
     return set_error(ECHOKV_E_ARGUMENT, "seal_group: bad slot/block/group/fill/bits");
   const int threads = (L.H * L.D / 8) < 256 ? ((L.H * L.D / 8 + 31) / 32 * 32) : 256;
-  finalize_k_kernel<float, true><<<1, threads, 0, (cudaStream_t)stream>>>(
-      L, (uint8_t*)pages->base, nullptr, 0, 0, nullptr, nullptr, R.base, R.dtype, R.s_slot, R.s_pos, R.s_head, false,
-      false, make_shifts(L), slot, block, group, fill, bits, sealed_mask);
+  FinArgs<float> A = fin_args<float>(L, pages, R, nullptr, 0, 0, nullptr, nullptr);
+  A.vec_in = false; A.raw16 = false;
+  A.seal_slot = slot; A.seal_block = block; A.seal_group = group; A.seal_fill = fill; A.seal_bits = bits;
+  A.seal_mask = sealed_mask;
+  finalize_k_kernel<float, true><<<1, threads, 0, (cudaStream_t)stream>>>(A);
   return check_launch("seal_group");
+}
+
+int echokv_write_step(const echokv_layout* layout, const echokv_pages* pages, const void* key, int64_t k_s0,
+                      int64_t k_s1, const void* value, int64_t v_s0, int64_t v_s1, int32_t kv_dtype,
+                      const int64_t* tok, int64_t tok_s0, const echokv_residual* residual, float* kref,
+                      int64_t kref_s0, int64_t kref_s1, int64_t n_rows, const int64_t* fin, const int64_t* fin_count,
+                      int64_t n_fin_launch, const void* stash_src, int64_t stash_src_row_stride_bytes,
+                      const int64_t* stash_rows, int64_t stash_n, void* stash_dst, int64_t stash_row_bytes,
+                      void* stream) {
+  LayoutDev L;
+  ResidualDev R;
+  int rc = make_layout(layout, pages, &L);
+  if (rc) return rc;
+  rc = make_residual(residual, &R);
+  if (rc) return rc;
+  if (n_fin_launch < 0) n_fin_launch = 0;
+  if (stash_n < 0 || !stash_src) stash_n = 0;
+  const bool stash_vec = stash_n == 0 || (stash_rows && stash_dst && stash_row_bytes > 0 && stash_row_bytes % 16 == 0 &&
+                                          stash_src_row_stride_bytes % 16 == 0 && aligned16(stash_src) && aligned16(stash_dst));
+  if (n_rows <= 0 || n_rows > STEP_MAX_ROWS || !shuffle_ok(L) || !stash_vec || (n_fin_launch > 0 && (!fin || !fin_count))) {
+    // shapes the one-launch kernel does not take: the same work as three launches
+    rc = echokv_finalize_k(layout, pages, key, k_s0, k_s1, kv_dtype, fin, fin_count, residual, n_fin_launch, stream);
+    if (rc) return rc;
+    rc = echokv_write_tokens(layout, pages, key, k_s0, k_s1, value, v_s0, v_s1, kv_dtype, tok, tok_s0, residual, kref,
+                             kref_s0, kref_s1, n_rows, stream);
+    if (rc) return rc;
+    return echokv_gather_rows(stash_src, stash_src_row_stride_bytes, stash_rows, stash_n, stash_dst, stash_row_bytes, stream);
+  }
+  if (!key || !value || !tok) return set_error(ECHOKV_E_ARGUMENT, "write_step: null pointer");
+  StashArgs SA;
+  SA.src = (const uint4*)stash_src; SA.src_stride16 = stash_src_row_stride_bytes / 16; SA.rows = stash_rows;
+  SA.n = stash_n; SA.dst = (uint4*)stash_dst; SA.row16 = (int)(stash_row_bytes / 16);
+  const int64_t stash_ctas = (stash_n * SA.row16 + WT_WARPS * 32 - 1) / (WT_WARPS * 32);
+  const unsigned grid = (unsigned)(n_rows + n_fin_launch + stash_ctas);
+  cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH(T)                                                                                                  \
+  write_step_kernel<T><<<grid, WT_WARPS * 32, 0, st>>>(                                                            \
+      tok_args<T>(L, pages, R, key, k_s0, k_s1, value, v_s0, v_s1, tok, tok_s0, kref, kref_s0, kref_s1, n_rows),   \
+      fin_args<T>(L, pages, R, key, k_s0, k_s1, fin, fin_count), n_fin_launch, SA)
+  switch (kv_dtype) {
+    case ECHOKV_DT_F32: LAUNCH(float); break;
+    case ECHOKV_DT_F16: LAUNCH(__half); break;
+    case ECHOKV_DT_BF16: LAUNCH(__nv_bfloat16); break;
+    default: return set_error(ECHOKV_E_ARGUMENT, "write_step: bad dtype %d", kv_dtype);
+  }
+#undef LAUNCH
+  return check_launch("write_step");
 }
 
 }  // extern "C"

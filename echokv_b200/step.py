@@ -266,8 +266,12 @@ class GroupRunner:
             ctl.observe(dict(zip(SUPPORTED_BITS, row)), ctx_len)
 
     # -- device side, per layer ---------------------------------------------------------------
-    def write(self, layer: int, key: torch.Tensor, value: torch.Tensor, meta: StepMeta, capturing: bool = False) -> None:
-        self.stores[layer].apply(meta.write, key, value, self.krefs[layer], capturing=capturing)
+    def write(self, layer: int, key: torch.Tensor, value: torch.Tensor, meta: StepMeta, capturing: bool = False,
+              query: torch.Tensor | None = None) -> None:
+        """Store the step's keys and values of one layer; with ``query`` also keep its canary rows (what
+        ``stash_queries`` does) in the same launch."""
+        stash = None if query is None else (query, meta.canary_rows, self.stashes[layer])
+        self.stores[layer].apply(meta.write, key, value, self.krefs[layer], capturing=capturing, stash=stash)
 
     def decode(self, layer: int, query: torch.Tensor, block_table: torch.Tensor, out: torch.Tensor,
                meta: StepMeta) -> None:

@@ -365,18 +365,14 @@ class TieredKVCache:
         return self.open_blocks(opens, target_bits, protect=plan.touched_np)
 
     def apply(self, meta: WriteMeta, key: torch.Tensor, value: torch.Tensor, kref: torch.Tensor | None = None,
-              capturing: bool = False) -> None:
-        """Device side: quantize and store ``key`` / ``value`` ``[*, H, D]`` as ``meta`` says.
-        ``capturing`` launches the finalize kernel at its full grid, masked by the device count."""
-        from echokv_b200.kernels.write import finalize_k, write_tokens
+              capturing: bool = False, stash: tuple | None = None) -> None:
+        """Device side: quantize and store ``key`` / ``value`` ``[*, H, D]`` as ``meta`` says, in one launch
+        (completed K groups, token rows and, with ``stash`` = (query, row indices, destination), the canary's
+        query rows).  ``capturing`` gives the group pass its full grid, masked by the device count."""
+        from echokv_b200.kernels.write import write_step
 
-        # finalize first: a slot freed by a completing group may be reused in the same step
-        if capturing or meta.n_fin:
-            with record_function("echokv.write.k_finalize"):
-                finalize_k(self, key, meta, full_grid=capturing)
-        if meta.n_rows:
-            with record_function("echokv.write.tokens"):
-                write_tokens(self, key, value, meta, kref)
+        with record_function("echokv.write.step"):
+            write_step(self, key, value, meta, kref, full_grid=capturing, stash=stash)
 
     def write(self, key: torch.Tensor, value: torch.Tensor, slots: torch.Tensor, target_bits: int,
               kref: torch.Tensor | None = None) -> None:

@@ -128,6 +128,23 @@ int echokv_seal_group(const echokv_layout* layout, const echokv_pages* pages,
                       const echokv_residual* residual, int64_t slot, int64_t block, int32_t group,
                       int32_t fill, int32_t bits, int32_t sealed_mask, void* stream);
 
+/* One layer's writes of a step in ONE launch: echokv_finalize_k (n_fin_launch CTAs masked by *fin_count),
+ * echokv_write_tokens and echokv_gather_rows (the canary's query rows: stash_dst[i] = stash_src[stash_rows[i]],
+ * skipped when stash_src is NULL or stash_n is 0) with the same arguments and the same stored bytes as the three
+ * calls made in that order.  The reference launches them one after the other (tiered_cache.py:404-416,
+ * backend.py:612-614); the group pass must come first there because a residual slot a completing group gives up
+ * may be taken by a new group in the same step.  In the single launch the CTA of such a token row leaves the key
+ * to the CTA of the completing group, which stores it after its own last read of the slot.  Steps of more than
+ * 1,024 rows, and layouts or stash rows the single kernel does not take, run as the three launches. */
+int echokv_write_step(const echokv_layout* layout, const echokv_pages* pages,
+                      const void* key, int64_t k_s0, int64_t k_s1,
+                      const void* value, int64_t v_s0, int64_t v_s1, int32_t kv_dtype,
+                      const int64_t* tok, int64_t tok_s0, const echokv_residual* residual,
+                      float* kref, int64_t kref_s0, int64_t kref_s1, int64_t n_rows,
+                      const int64_t* fin, const int64_t* fin_count, int64_t n_fin_launch,
+                      const void* stash_src, int64_t stash_src_row_stride_bytes, const int64_t* stash_rows,
+                      int64_t stash_n, void* stash_dst, int64_t stash_row_bytes, void* stream);
+
 /* Requantize full INT4/INT8 blocks to INT2 in place -- TieredKVCache._demote_lru
  * (tiered_cache.py:309-346).  `victims` int64 [n] on the device; `scratch` holds the blocks'
  * dequantized contents between the read and the rewrite (echokv_demote_scratch_bytes). */
