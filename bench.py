@@ -68,6 +68,9 @@ def parse():
     ap.add_argument("--no-config5", action="store_true", help="skip the 70B-shape run with the live controller")
     ap.add_argument("--config5-layers", type=int, default=4, help="resident layers cycled to stand for the 80 of the 70B shape")
     ap.add_argument("--config5-steps", type=int, default=4)
+    ap.add_argument("--one-rank-of", type=int, default=1, metavar="N",
+                    help="diagnostic: run the share of one rank of an N-times larger tensor-parallel job (KV heads / N); "
+                         "the line it prints is not a whole-job figure")
     ap.add_argument("--tiers", default="", help="comma list of tiers cycled over the layers instead of the seeded draw "
                                                 "(small profiling cases, e.g. --layers 2 --tiers 4)")
     return ap.parse_args()
@@ -574,9 +577,10 @@ def run_b200(a) -> None:
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    if H % world:
-        raise SystemExit(f"{H} KV heads cannot be sharded over {world} ranks")
-    h, hq = H // world, HQ // world
+    shards = world * max(1, a.one_rank_of)
+    if H % shards:
+        raise SystemExit(f"{H} KV heads cannot be sharded over {shards} ranks")
+    h, hq = H // shards, HQ // shards
     peaks = {}
     try:
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
@@ -832,7 +836,7 @@ def run_b200(a) -> None:
             "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload_string(a),
-                       "tiers": {str(b): tiers.count(b) for b in (8, 4, 2)}, "parallelism": f"tp{world} by KV head",
+                       "tiers": {str(b): tiers.count(b) for b in (8, 4, 2)}, "parallelism": f"tp{world} by KV head" + (f" (one rank of tp{shards} only)" if shards != world else ""),
                        "cuda_graph": not a.no_graph, "l2": "each layer's pool is larger than L2; layers alternate",
                        "host_cores": cores, "timing": f"median of {len(windows)} windows of {a.steps} steps",
                        "window_ms": [round(w, 3) for w in windows]},

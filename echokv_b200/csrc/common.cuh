@@ -36,6 +36,27 @@ int check_launch(const char* what);
 
 #ifdef __CUDACC__
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// A kernel launched with `launch_pdl` may be scheduled while the kernel before it on the stream still runs: its
+// CTAs take their places as SMs free up and run whatever precedes `pdl_wait()`, which returns once the earlier
+// kernel has completed and its writes are visible.  Every CTA calls `pdl_wait()` before it reads or writes
+// anything another kernel touches (so completion of this kernel implies completion of the one before it), and
+// `pdl_launch_dependents()` lets the next such kernel start being scheduled.  Launched the ordinary way, or after
+// something that is not a kernel, both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---- element access by runtime dtype ----------------------------------------------------
 template <typename T> struct Elem;
 template <> struct Elem<float> {

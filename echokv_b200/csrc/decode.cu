@@ -5,7 +5,7 @@ using namespace echokv;
 
 namespace echokv {
 int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
-                      int64_t num_seqs, int* counter, int* status, cudaStream_t st, bool* handled);
+                      int64_t num_seqs, int* counter, bool zero_counter, int* status, cudaStream_t st, bool* handled);
 int decode_mma_teams(int H, int D, int VG, int KG, int BS, int gqa);
 int decode_status_take(bool clear);
 int prefill_status_take(bool clear);
@@ -19,6 +19,9 @@ __global__ void decode_merge_kernel(DecodeArgs A, int BS, int D) {
   __shared__ float wgt[MERGE_MAX_SPLITS], den[MERGE_MAX_SPLITS];
   __shared__ float red[2];
   const int seq = blockIdx.x, head = blockIdx.y;
+  pdl_launch_dependents();
+  pdl_wait();  // the split kernel has completed
+  if (seq == 0 && head == 0 && threadIdx.x == 0) A.state[0] = 0;  // its item counter, for the next call
   const int64_t seq_len = A.lens[seq];
   if (seq_len == 0) return;  // CUDA-graph padding: leave the row alone
   const int n_blocks = (int)((seq_len + BS - 1) / BS);
@@ -107,17 +110,18 @@ extern "C" {
 
 int64_t echokv_decode_scratch_bytes(int64_t num_seqs, int32_t num_q_heads, int32_t head_size, int32_t num_splits) {
   if (num_seqs <= 0 || num_q_heads <= 0 || head_size <= 0 || num_splits <= 0) return 0;
-  // split partials (accumulators + running max / sum), then 256 bytes of work-queue state
+  // 256 bytes of work-queue state, then the split partials (accumulators + running max / sum)
   const int64_t partials = num_seqs * num_q_heads * (int64_t)num_splits * (head_size + 2) * (int64_t)sizeof(float);
   return (partials + 15) / 16 * 16 + 256;
 }
 
-int echokv_decode_ex(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
-                     const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype, const int64_t* q_rows,
-                     const int32_t* block_table, int64_t bt_s0, const int64_t* bt_rows, const int64_t* lens,
-                     void* scratch, int64_t scratch_bytes, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
-                     float softmax_scale, int32_t num_splits, int32_t blocks_per_split,
-                     const int32_t* blocks_per_split_dev, int64_t num_seqs, int32_t num_q_heads, void* stream) {
+static int decode_impl(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                       const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype, const int64_t* q_rows,
+                       const int32_t* block_table, int64_t bt_s0, const int64_t* bt_rows, const int64_t* lens,
+                       void* scratch, int64_t scratch_bytes, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
+                       float softmax_scale, int32_t num_splits, int32_t blocks_per_split,
+                       const int32_t* blocks_per_split_dev, bool zero_state, int64_t num_seqs, int32_t num_q_heads,
+                       void* stream) {
   if (num_seqs <= 0) return ECHOKV_OK;
   LayoutDev L;
   ResidualDev R;
@@ -138,7 +142,9 @@ int echokv_decode_ex(const echokv_layout* layout, const echokv_pages* pages, con
   DecodeArgs A;
   A.q = query; A.q_s0 = q_s0; A.q_s1 = q_s1; A.q_dt = q_dtype; A.q_rows = q_rows;
   A.bt = block_table; A.bt_s0 = bt_s0; A.bt_rows = bt_rows; A.lens = lens;
-  A.acc = (float*)scratch;
+  // scratch = [256 bytes of work-queue state][split partials: accumulators, then running max / sum]
+  A.state = reinterpret_cast<int*>(scratch);
+  A.acc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(scratch) + 256);
   A.ml = A.acc + num_seqs * num_q_heads * (int64_t)num_splits * L.D;
   A.out = out; A.o_s0 = o_s0; A.o_s1 = o_s1; A.out_dt = out_dtype;
   A.scale_log2e = softmax_scale * 1.4426950408889634f;
@@ -148,9 +154,7 @@ int echokv_decode_ex(const echokv_layout* layout, const echokv_pages* pages, con
   const uint8_t* pg = (const uint8_t*)pages->base;
 
   bool handled = false;
-  int* counter = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(scratch) +
-                                        echokv_decode_scratch_bytes(num_seqs, num_q_heads, L.D, num_splits) - 256);
-  rc = launch_decode_mma(L, R, pg, A, num_seqs, counter, nullptr, st, &handled);
+  rc = launch_decode_mma(L, R, pg, A, num_seqs, A.state, zero_state, nullptr, st, &handled);
   if (rc) return rc;
   if (!handled) {
     dim3 grid((unsigned)num_seqs, (unsigned)L.H, (unsigned)num_splits);
@@ -164,8 +168,20 @@ int echokv_decode_ex(const echokv_layout* layout, const echokv_pages* pages, con
     if (rc) return rc;
   }
   dim3 mgrid((unsigned)num_seqs, (unsigned)num_q_heads);
-  decode_merge_kernel<<<mgrid, L.D < 128 ? L.D : 128, 0, st>>>(A, L.BS, L.D);
+  if (launch_pdl(decode_merge_kernel, mgrid, dim3(L.D < 128 ? L.D : 128), 0, st, A, L.BS, L.D) != cudaSuccess)
+    return check_launch("decode merge");
   return check_launch("decode merge");
+}
+
+int echokv_decode_ex(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
+                     const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype, const int64_t* q_rows,
+                     const int32_t* block_table, int64_t bt_s0, const int64_t* bt_rows, const int64_t* lens,
+                     void* scratch, int64_t scratch_bytes, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
+                     float softmax_scale, int32_t num_splits, int32_t blocks_per_split,
+                     const int32_t* blocks_per_split_dev, int64_t num_seqs, int32_t num_q_heads, void* stream) {
+  return decode_impl(layout, pages, residual, query, q_s0, q_s1, q_dtype, q_rows, block_table, bt_s0, bt_rows, lens, scratch,
+                     scratch_bytes, out, o_s0, o_s1, out_dtype, softmax_scale, num_splits, blocks_per_split,
+                     blocks_per_split_dev, false, num_seqs, num_q_heads, stream);
 }
 
 int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
@@ -174,9 +190,9 @@ int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const 
                   void* scratch, int64_t scratch_bytes, void* out, int64_t o_s0, int64_t o_s1, int32_t out_dtype,
                   float softmax_scale, int32_t num_splits, int32_t blocks_per_split, int64_t num_seqs,
                   int32_t num_q_heads, void* stream) {
-  return echokv_decode_ex(layout, pages, residual, query, q_s0, q_s1, q_dtype, q_rows, block_table, bt_s0, bt_rows, lens,
-                          scratch, scratch_bytes, out, o_s0, o_s1, out_dtype, softmax_scale, num_splits, blocks_per_split,
-                          nullptr, num_seqs, num_q_heads, stream);
+  return decode_impl(layout, pages, residual, query, q_s0, q_s1, q_dtype, q_rows, block_table, bt_s0, bt_rows, lens, scratch,
+                     scratch_bytes, out, o_s0, o_s1, out_dtype, softmax_scale, num_splits, blocks_per_split, nullptr, true,
+                     num_seqs, num_q_heads, stream);
 }
 
 // Work items the tensor-core split kernel processes at the same time on the current device for this shape (its

@@ -27,6 +27,7 @@ struct DecodeArgs {
   float scale_log2e;
   int num_splits, bps_min, gqa, Hq;
   const int32_t* bps_dev;  // optional: blocks per split chosen by the host for this step, read at run time
+  int* state;              // work-queue state at the start of the scratch: [0] = the split kernel's item counter
 };
 
 // Lower bound of a split's size in blocks: the call's argument, raised by the run-time value when there is one.

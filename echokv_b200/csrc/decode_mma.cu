@@ -834,6 +834,7 @@ template <int H> struct Teams {
 template <int H, int V>
 __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const Params P) {
   extern __shared__ __align__(128) unsigned char smem_all[];
+  pdl_launch_dependents();  // the merge may take its place behind this kernel; it waits for this kernel to complete
   constexpr int TEAM_THREADS = (H + 1) * 32;
   const LayoutDev& L = P.L;
   const DecodeArgs& A = P.A;
@@ -873,6 +874,7 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the bulk copies write the same bytes later
   }
   __syncthreads();
+  pdl_wait();  // barriers and ring are set up; from here on this kernel reads what the kernels before it wrote
 
   bool ok = true;
   if (warp == H) {
@@ -1253,8 +1255,8 @@ static cudaError_t allow_smem(int bytes) {
 template <int H>
 static void launch_teams(bool small, unsigned grid, int smem_bytes, cudaStream_t st, const mma::Params& P) {
   using namespace mma;
-  if (small) decode_mma_kernel<H, Teams<H>::V_SMALL><<<grid, (H + 1) * 32 * Teams<H>::V_SMALL, smem_bytes, st>>>(P);
-  else decode_mma_kernel<H, Teams<H>::V><<<grid, (H + 1) * 32 * Teams<H>::V, smem_bytes, st>>>(P);
+  if (small) launch_pdl(decode_mma_kernel<H, Teams<H>::V_SMALL>, dim3(grid), dim3((H + 1) * 32 * Teams<H>::V_SMALL), smem_bytes, st, P);
+  else launch_pdl(decode_mma_kernel<H, Teams<H>::V>, dim3(grid), dim3((H + 1) * 32 * Teams<H>::V), smem_bytes, st, P);
 }
 static int decode_device(DecodeDevice** out) {
   using namespace mma;
@@ -1318,7 +1320,7 @@ int decode_mma_teams(int H, int D_, int VG, int KG, int BS, int gqa) {
 
 // Chooses the tensor-core kernel when the shape fits; otherwise leaves `handled` false.
 int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* pages, const DecodeArgs& A,
-                      int64_t num_seqs, int* counter, int* status, cudaStream_t st, bool* handled) {
+                      int64_t num_seqs, int* counter, bool zero_counter, int* status, cudaStream_t st, bool* handled) {
   using namespace mma;
   *handled = false;
   if (g_decode_path == 1) return ECHOKV_OK;
@@ -1347,7 +1349,9 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   const int64_t n_items = num_seqs * (int64_t)A.num_splits;
   int64_t grid = dv->num_sms;
   if (grid * V > n_items) grid = (n_items + V - 1) / V;
-  if (cudaMemsetAsync(counter, 0, sizeof(int), st) != cudaSuccess) return check_launch("decode (work counter)");
+  // The merge kernel leaves the counter at zero for the next call; a caller that cannot promise a zeroed state
+  // gets it zeroed here.
+  if (zero_counter && cudaMemsetAsync(counter, 0, sizeof(int), st) != cudaSuccess) return check_launch("decode (work counter)");
   if (g_ev_before) cudaEventRecord(g_ev_before, st);
   switch (H) {
     case 1: launch_teams<1>(small, (unsigned)grid, smem_bytes, st, P); break;

@@ -487,6 +487,8 @@ __global__ void __launch_bounds__(WT_WARPS * 32)
 write_step_kernel(const TokArgs<T> TA, const FinArgs<T> FA, int64_t n_fin_launch, const StashArgs SA) {
   __shared__ int take[STEP_MAX_ROWS];
   __shared__ int n_take;
+  pdl_launch_dependents();
+  pdl_wait();
   const LayoutDev& L = TA.L;
   const int64_t b = blockIdx.x;
   const int w = 3 + L.KG;
@@ -756,9 +758,9 @@ int echokv_write_step(const echokv_layout* layout, const echokv_pages* pages, co
   const unsigned grid = (unsigned)(n_rows + n_fin_launch + stash_ctas);
   cudaStream_t st = (cudaStream_t)stream;
 #define LAUNCH(T)                                                                                                  \
-  write_step_kernel<T><<<grid, WT_WARPS * 32, 0, st>>>(                                                            \
-      tok_args<T>(L, pages, R, key, k_s0, k_s1, value, v_s0, v_s1, tok, tok_s0, kref, kref_s0, kref_s1, n_rows),   \
-      fin_args<T>(L, pages, R, key, k_s0, k_s1, fin, fin_count), n_fin_launch, SA)
+  launch_pdl(write_step_kernel<T>, dim3(grid), dim3(WT_WARPS * 32), 0, st,                                         \
+             tok_args<T>(L, pages, R, key, k_s0, k_s1, value, v_s0, v_s1, tok, tok_s0, kref, kref_s0, kref_s1, n_rows), \
+             fin_args<T>(L, pages, R, key, k_s0, k_s1, fin, fin_count), n_fin_launch, SA)
   switch (kv_dtype) {
     case ECHOKV_DT_F32: LAUNCH(float); break;
     case ECHOKV_DT_F16: LAUNCH(__half); break;

@@ -53,7 +53,8 @@ def choose_blocks_per_split(lens, block_size: int, num_splits: int, slots: int) 
 class _Scratch:
     """Per-device split-partials buffer, grown on demand.
 
-    A CUDA graph holds the address of the buffer it was captured with, so a buffer that a capture has
+    The buffer starts zeroed: its first 256 bytes are the split kernel's work-queue state, which every
+    call leaves at zero.  A CUDA graph holds the address of the buffer it was captured with, so a buffer that a capture has
     used is never freed: when a later call needs more bytes (more sequences than the captured sizes, the
     row path of a long prefill, another model in the same process) a larger buffer takes over and the old
     one is kept alive for the graphs that point at it.
@@ -73,7 +74,7 @@ class _Scratch:
             if cur is not None and device in self.captured:
                 self.retired.append(cur)
                 self.captured.discard(device)
-            cur = self.buf[device] = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            cur = self.buf[device] = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         if capturing:
             self.captured.add(device)
         return cur

@@ -158,11 +158,11 @@ int echokv_demote_blocks(const echokv_layout* layout, const echokv_pages* pages,
 int echokv_gather(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
                   const int64_t* blk, const int64_t* off, int64_t n, float* k_out, float* v_out, void* stream);
 
-/* Bytes of scratch echokv_decode needs: the split partials, acc float32
- * [S, Hq, num_splits, D] then (m, l) float32 [S, Hq, num_splits, 2]
- * (kernels/decode.py:306-307 allocates the same two tensors per call), rounded up to 16 bytes,
- * plus 256 bytes of work-queue state (the counter persistent CTAs claim work items from; the
- * call zeroes it itself with a memset node on `stream`). */
+/* Bytes of scratch echokv_decode needs: 256 bytes of work-queue state at the start (the counter
+ * persistent CTAs claim work items from), then the split partials, acc float32
+ * [S, Hq, num_splits, D] and (m, l) float32 [S, Hq, num_splits, 2] (kernels/decode.py:306-307
+ * allocates the same two tensors per call), rounded up to 16 bytes.  echokv_decode zeroes the state
+ * itself with a memset node on `stream`; echokv_decode_ex expects it zero (see there). */
 int64_t echokv_decode_scratch_bytes(int64_t num_seqs, int32_t num_q_heads, int32_t head_size, int32_t num_splits);
 
 /* Split-K paged decode attention + merge -- decode_attention / _decode_triton
@@ -184,7 +184,11 @@ int echokv_decode(const echokv_layout* layout, const echokv_pages* pages, const 
  * rule above.  A CUDA graph bakes the by-value arguments of a captured call; a host that replays such a
  * graph writes the value for the coming step into that word (on the same stream) and so keeps choosing the
  * split size per step.  The reference fixes BLOCKS_PER_SPLIT per process (kernels/decode.py:41); for a given
- * value the results are the same bits as echokv_decode's with blocks_per_split = max(both). */
+ * value the results are the same bits as echokv_decode's with blocks_per_split = max(both).
+ * Unlike echokv_decode this call issues no memset: the first 256 bytes of `scratch` must be zero before the
+ * first call that uses it, and every call leaves them zero (the merge kernel resets the counter), so the
+ * split kernel follows the kernel before it on the stream directly and all three kernels of a layer's step
+ * (write_step, split, merge) launch as programmatic dependents of one another. */
 int echokv_decode_ex(const echokv_layout* layout, const echokv_pages* pages, const echokv_residual* residual,
                      const void* query, int64_t q_s0, int64_t q_s1, int32_t q_dtype, const int64_t* q_rows,
                      const int32_t* block_table, int64_t bt_s0, const int64_t* bt_rows, const int64_t* lens,
