@@ -623,6 +623,9 @@ def run_b200(a) -> None:
     # launches, read after the whole chunk, no host synchronisation between launches)
     chunk = 512
     write_ms, write_bytes = 0.0, 0
+    # ~100 us of device work enqueued right before the first event: the host gets ahead of the device while it
+    # runs, so the window between the events holds the write kernels' device time and not Python's launch time
+    filler = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
     for c0 in range(0, ctx, chunk):
         c1 = min(ctx, c0 + chunk)
         pos = np.arange(c0, c1)
@@ -635,6 +638,7 @@ def run_b200(a) -> None:
                 k[s * (c1 - c0):(s + 1) * (c1 - c0)] = torch.from_numpy(par[(s, l)][0][c0:c1]).to(dev).bfloat16()
                 v[s * (c1 - c0):(s + 1) * (c1 - c0)] = torch.from_numpy(par[(s, l)][1][c0:c1]).to(dev).bfloat16()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            filler.add_(1.0)
             e0.record()
             runner.write(l, k, v, meta)
             e1.record()
@@ -642,6 +646,7 @@ def run_b200(a) -> None:
             write_bytes += slots.size * (4 * h * D + bytes_per_token(tiers[l], h))
         torch.cuda.synchronize()
         write_ms += sum(x.elapsed_time(y) for x, y in evs)
+    del filler
 
     # ---- per-step inputs, resident on the device (and a pinned host copy for the e2e leg)
     q_dev = torch.randn(Lr, S, hq, D, device=dev, generator=gen).bfloat16()
@@ -751,6 +756,18 @@ def run_b200(a) -> None:
     step(True)  # touch the copies once
     ms_e2e = float(np.median([timed(n_e2e, True) / n_e2e for _ in range(3)]))
 
+    # host share of a step: wall time of plan + upload + graph launch for three steps issued onto an idle GPU (the
+    # staging ring holds four steps, so the host never waits for the device here)
+    host_ms = []
+    for _ in range(3):
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(3):
+            step(False)
+        host_ms.append((time.perf_counter() - t0) / 3 * 1e3)
+    barrier()
+    host_ms_per_step = float(np.median(host_ms))
+
     # ---- roofline of the dominant kernel: paged decode attention (split kernel + merge), timed with
     # CUDA events on the launching stream over back-to-back launches: all layers of one tier, three
     # passes, no host synchronisation in between (consecutive launches read different layers' pools,
@@ -849,6 +866,7 @@ def run_b200(a) -> None:
             "parity": parity,
             "cpu_baseline": base,
             "e2e": {"value": S / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "host_ms_per_step": host_ms_per_step,
             "gpu_launches": launches_per_step * a.steps + canary["fires"],
             "canary": {"interval": a.canary_interval, "fires": canary["fires"],
                        "last": None if canary["pending"] is None else [round(x, 6) for x in canary["pending"][0].tolist()]},

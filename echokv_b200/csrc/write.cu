@@ -33,24 +33,24 @@ __global__ void scatter_i64_kernel(int64_t* dst, const int64_t* idx, const int64
 }
 
 // ---- the quantizer, many values under one reciprocal ---------------------------------------------
-// code = clamp(rne((x - mn) / scale), 0, levels) from a precomputed reciprocal of the scale.  The product
-// (x - mn) * (1 / scale), clamped to [0, levels] first (0 and levels are integers, so clamping before or after
-// the rounding gives the same code), differs from the correctly rounded quotient by at most three roundings of
-// 2^-24 relative each, under 1.8e-7 * (levels + 0.5); adding 1.5 * 2^23 rounds it to the nearest-even integer
-// in the float's low mantissa bits.  Both round alike unless the product lies within levels * 2^-21 (2.6 times
-// that bound) of a half-integer: `risky` collects those, and the caller redoes the 8 values with the IEEE
-// divide.  NaN clamps to 0 on both routes.
+// code = clamp(rne((x - mn) / scale), 0, levels) without a divide per value.  With y = RN(1 / scale) computed once,
+// q0 = RN(d * y), r = RN(d - scale * q0) (exact: one FMA) and q1 = RN(q0 + r * y), q1 IS the correctly rounded
+// quotient RN(d / scale) (Markstein's correction step; it needs y correctly rounded and the significand of the
+// divisor not all ones, and every scale here is an fp16 value).  q0 is capped at 512 first so that infinities and
+// overflowing quotients stay ordered through the correction (anything >= 255.5 clamps to `levels` anyway; NaN
+// clamps to 0 as on the divide route).  Adding 1.5 * 2^23 to the clamped quotient rounds it to the nearest-even
+// integer in the float's low mantissa bits (0 and levels are integers, so clamping before or after the rounding
+// gives the same code).
 constexpr float QMAGIC = 12582912.f;            // 1.5 * 2^23
 constexpr uint32_t QMAGIC_BITS = 0x4B400000u;   // its bit pattern; QMAGIC + code has bit pattern QMAGIC_BITS + code
 
-__device__ __forceinline__ uint32_t quant_u(float x, float mn, float rscale, float levels, float near_half,
-                                            bool& risky) {
+__device__ __forceinline__ uint32_t quant_u(float x, float mn, float scale, float rscale, float levels) {
   const float d = __fsub_rn(x, mn);
-  const float t = fminf(fmaxf(__fmul_rn(d, rscale), 0.0f), levels);
-  const float u = __fadd_rn(t, QMAGIC);
-  const float r = __fsub_rn(__fsub_rn(u, QMAGIC), t);
-  risky |= fabsf(r) > near_half;
-  return __float_as_uint(u);
+  const float q0 = fminf(__fmul_rn(d, rscale), 512.0f);
+  const float r = __fmaf_rn(-scale, q0, d);
+  const float q1 = __fmaf_rn(r, rscale, q0);
+  const float t = fminf(fmaxf(q1, 0.0f), levels);
+  return __float_as_uint(__fadd_rn(t, QMAGIC));
 }
 
 // 8 values of QMAGIC_BITS + code -> the 8 codes packed at BITS (element k at bit k * BITS): the shifted sum of
@@ -73,22 +73,20 @@ __device__ __forceinline__ uint64_t pack_u8(const uint32_t (&u)[8]) {
   }
 }
 
-// Quantize 8 values and store their codes at `dst`.  PER_CH: value k has its own stats m[k], sc[k], rsc[k]
+// Quantize 8 values to their codes packed at BITS.  PER_CH: value k has its own stats m[k], sc[k], rsc[k]
 // (K: per channel); otherwise all 8 share m[0], sc[0], rsc[0] (V: one group).
+template <int BITS, bool PER_CH>
+__device__ __forceinline__ uint64_t quant_pack8(const float (&x)[8], const float* m, const float* sc, const float* rsc) {
+  constexpr float levels = (float)((1 << BITS) - 1);
+  uint32_t u[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) u[k] = quant_u(x[k], m[PER_CH ? k : 0], sc[PER_CH ? k : 0], rsc[PER_CH ? k : 0], levels);
+  return pack_u8<BITS>(u);
+}
 template <int BITS, bool PER_CH>
 __device__ __forceinline__ void quant_store8(uint8_t* dst, const float (&x)[8], const float* m, const float* sc,
                                              const float* rsc) {
-  constexpr float levels = (float)((1 << BITS) - 1);
-  constexpr float near_half = 0.5f - levels * 4.76837158203125e-07f;  // 2^-21
-  uint32_t u[8];
-  bool risky = false;
-#pragma unroll
-  for (int k = 0; k < 8; ++k) u[k] = quant_u(x[k], m[PER_CH ? k : 0], rsc[PER_CH ? k : 0], levels, near_half, risky);
-  if (risky) {
-#pragma unroll
-    for (int k = 0; k < 8; ++k) u[k] = QMAGIC_BITS + quant_code(x[k], m[PER_CH ? k : 0], sc[PER_CH ? k : 0], levels);
-  }
-  store_packed8(dst, pack_u8<BITS>(u), BITS);
+  store_packed8(dst, quant_pack8<BITS, PER_CH>(x, m, sc, rsc), BITS);
 }
 template <bool PER_CH>
 __device__ __forceinline__ void quant_store8(int bits, uint8_t* dst, const float (&x)[8], const float* m,
@@ -213,6 +211,53 @@ struct TokArgs {
   Shifts sh;
 };
 
+// K side of 8 channels (piece `c` of the row) of one token: the key goes to the residual row of its open group,
+// and / or is quantized under the stored statistics of a sealed group, and / or goes to the K_ref ring.
+template <typename T>
+__device__ __forceinline__ void key_chunk(const TokArgs<T>& A, int64_t row, int c, int off, int bits, int64_t rowoff,
+                                          int64_t rslot, bool sealed, int64_t kidx) {
+  const LayoutDev& L = A.L;
+  const Shifts sh = A.sh;
+  const int h = qdiv(c * 8, L.D, sh.D), d0 = qmod(c * 8, L.D, sh.D);
+  const int grp = qdiv(off, L.KG, sh.KG), gpos = off - grp * L.KG;
+  const int64_t src = row * A.k_s0 + h * A.k_s1 + d0;
+  if (rslot >= 0 && A.res_raw) {
+    const int64_t ro = rslot * A.r_s0 + (int64_t)gpos * A.r_s1 + h * A.r_s2 + d0;
+    *reinterpret_cast<uint4*>(reinterpret_cast<T*>(A.res) + ro) = *reinterpret_cast<const uint4*>(A.key + src);
+    if (!sealed && kidx < 0) return;
+  }
+  float x[8];
+  ld8<T>(A.key, src, A.vec_in, x);
+  if (rslot >= 0 && !A.res_raw) {
+    const int64_t ro = rslot * A.r_s0 + (int64_t)gpos * A.r_s1 + h * A.r_s2 + d0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) st_dt(A.res, A.res_dt, ro + k, x[k]);
+  }
+  if (sealed) {
+    const float levels = (float)((1 << bits) - 1);
+    const int64_t e = ((int64_t)grp * L.H + h) * L.D + d0;
+    const int64_t slot = A.tok[row];
+    const int64_t blk = sh.BS >= 0 ? slot >> sh.BS : slot / L.BS;
+    const uint8_t* pg = A.pages + blk * L.PS;
+    const __half* ks = reinterpret_cast<const __half*>(pg + L.o_ks) + e;
+    const __half* km = reinterpret_cast<const __half*>(pg + L.o_km) + e;
+    uint32_t q[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) q[k] = quant_code(x[k], __half2float(km[k]), __half2float(ks[k]), levels);
+    store_packed8(A.pages + rowoff + h * ((L.D * bits) / 8) + (d0 * bits) / 8, pack8(q, bits), bits);
+  }
+  if (kidx >= 0) {
+    float* dst = A.kref + kidx * A.kref_s0 + h * A.kref_s1 + d0;
+    if (A.kref_vec) {
+      reinterpret_cast<float4*>(dst)[0] = make_float4(x[0], x[1], x[2], x[3]);
+      reinterpret_cast<float4*>(dst)[1] = make_float4(x[4], x[5], x[6], x[7]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) dst[k] = x[k];
+    }
+  }
+}
+
 // One token row.  `row_in_cta`: row index this CTA / warp works on; `skip_residual`: the row's open-group key is
 // stored by someone else (see write_step_kernel).
 template <typename T, int MODE>
@@ -307,42 +352,77 @@ __device__ __forceinline__ void token_row(const TokArgs<T>& A, int64_t row, bool
   const bool sealed = tok[2 * tok_s0 + row] != 0;
   const int64_t kidx = kref ? tok[3 * tok_s0 + row] : -1;
   if (rslot < 0 && !sealed && kidx < 0) return;
-  const int grp = qdiv(off, L.KG, sh.KG), gpos = off - grp * L.KG;
-  for (int c = first; c < units; c += step) {
-    const int h = qdiv(c * 8, L.D, sh.D), d0 = qmod(c * 8, L.D, sh.D);
-    const int64_t src = row * k_s0 + h * k_s1 + d0;
-    if (rslot >= 0 && res_raw) {
-      const int64_t ro = rslot * r_s0 + (int64_t)gpos * r_s1 + h * r_s2 + d0;
-      *reinterpret_cast<uint4*>(reinterpret_cast<T*>(res) + ro) = *reinterpret_cast<const uint4*>(key + src);
-      if (!sealed && kidx < 0) continue;
-    }
-    float x[8];
-    ld8<T>(key, src, vec_in, x);
-    if (rslot >= 0 && !res_raw) {
-      const int64_t ro = rslot * r_s0 + (int64_t)gpos * r_s1 + h * r_s2 + d0;
+  for (int c = first; c < units; c += step) key_chunk<T>(A, row, c, off, bits, rowoff, rslot, sealed, kidx);
+}
+
+// Many token rows, one thread per (row, KV head, group of 32 channels): the V group's 64 bytes are loaded once,
+// its statistics computed once, and its codes leave as one 16-byte store at INT4 (two at INT8, eight bytes at
+// INT2); then the K side of the same channels.  For 16-bit rows on 16-byte boundaries with v_group 32; stores the
+// same bytes as token_row.
+template <typename T>
+__global__ void __launch_bounds__(128, 8) write_tokens_bulk_kernel(const TokArgs<T> A, int gpr, int sh_gpr, int sh_ng) {
+  const LayoutDev& L = A.L;
+  const int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  const int64_t row = sh_gpr >= 0 ? gid >> sh_gpr : gid / gpr;
+  if (row >= A.n_rows) return;
+  const int g = (int)(gid - row * gpr);
+  const int64_t slot = A.tok[row];
+  if (slot < 0) return;
+  const int64_t blk = A.sh.BS >= 0 ? slot >> A.sh.BS : slot / L.BS;
+  const int off = (int)(slot - blk * L.BS);
+  const int bits = block_bits(A.pages, L, blk);
+  RowWalk walk;
+  walk.start(A.pages, L, A.sh.BS, blk, off, bits);
+  const int h = qdiv(g, L.NG, sh_ng), gi = g - h * L.NG;
+  const uint4* src = reinterpret_cast<const uint4*>(A.value + (row * A.v_s0 + h * A.v_s1 + gi * 32));
+  const uint4 r0 = src[0], r1 = src[1], r2 = src[2], r3 = src[3];
+  float x[4][8];
+  cvt8<T>(r0, x[0]); cvt8<T>(r1, x[1]); cvt8<T>(r2, x[2]); cvt8<T>(r3, x[3]);
+  float mn = INFINITY, mx = -INFINITY;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) st_dt(res, res_dt, ro + k, x[k]);
-    }
-    if (sealed) {
-      const int64_t e = ((int64_t)grp * L.H + h) * L.D + d0;
-      const __half* ks = reinterpret_cast<const __half*>(page + L.o_ks) + e;
-      const __half* km = reinterpret_cast<const __half*>(page + L.o_km) + e;
-      uint32_t q[8];
+  for (int c = 0; c < 4; ++c) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) q[k] = quant_code(x[k], __half2float(km[k]), __half2float(ks[k]), levels);
-      store_packed8(pages + rowoff + h * head_bytes + (d0 * bits) / 8, pack8(q, bits), bits);
-    }
-    if (kidx >= 0) {
-      float* dst = kref + kidx * kref_s0 + h * kref_s1 + d0;
-      if (kref_vec) {
-        reinterpret_cast<float4*>(dst)[0] = make_float4(x[0], x[1], x[2], x[3]);
-        reinterpret_cast<float4*>(dst)[1] = make_float4(x[4], x[5], x[6], x[7]);
-      } else {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) dst[k] = x[k];
-      }
+    for (int k = 0; k < 8; k += 2) {
+      mn = fminf(mn, fminf(x[c][k], x[c][k + 1]));
+      mx = fmaxf(mx, fmaxf(x[c][k], x[c][k + 1]));
     }
   }
+  const float levels = (float)((1 << bits) - 1);
+  __half s16, m16;
+  group_stats(mn, mx, levels, s16, m16);
+  const float sc = __half2float(s16), m = __half2float(m16), rsc = __frcp_rn(sc);
+  uint8_t* page = A.pages + blk * L.PS;
+  const int64_t e = ((int64_t)off * L.H + h) * L.NG + gi;
+  reinterpret_cast<__half*>(page + L.o_vs)[e] = s16;
+  reinterpret_cast<__half*>(page + L.o_vm)[e] = m16;
+  // V codes of the row start after the K codes of all heads; this group's are 4 * bits bytes
+  uint8_t* dst = A.pages + walk.offset() + (L.H * L.D * bits) / 8 + h * ((L.D * bits) / 8) + gi * 4 * bits;
+  if (bits == 4) {
+    uint4 w;
+    w.x = (uint32_t)quant_pack8<4, false>(x[0], &m, &sc, &rsc);
+    w.y = (uint32_t)quant_pack8<4, false>(x[1], &m, &sc, &rsc);
+    w.z = (uint32_t)quant_pack8<4, false>(x[2], &m, &sc, &rsc);
+    w.w = (uint32_t)quant_pack8<4, false>(x[3], &m, &sc, &rsc);
+    *reinterpret_cast<uint4*>(dst) = w;
+  } else if (bits == 8) {
+    const uint64_t a = quant_pack8<8, false>(x[0], &m, &sc, &rsc), b = quant_pack8<8, false>(x[1], &m, &sc, &rsc);
+    const uint64_t c = quant_pack8<8, false>(x[2], &m, &sc, &rsc), d = quant_pack8<8, false>(x[3], &m, &sc, &rsc);
+    reinterpret_cast<uint4*>(dst)[0] = make_uint4((uint32_t)a, (uint32_t)(a >> 32), (uint32_t)b, (uint32_t)(b >> 32));
+    reinterpret_cast<uint4*>(dst)[1] = make_uint4((uint32_t)c, (uint32_t)(c >> 32), (uint32_t)d, (uint32_t)(d >> 32));
+  } else {
+    const uint32_t a = (uint32_t)quant_pack8<2, false>(x[0], &m, &sc, &rsc) |
+                       ((uint32_t)quant_pack8<2, false>(x[1], &m, &sc, &rsc) << 16);
+    const uint32_t b = (uint32_t)quant_pack8<2, false>(x[2], &m, &sc, &rsc) |
+                       ((uint32_t)quant_pack8<2, false>(x[3], &m, &sc, &rsc) << 16);
+    *reinterpret_cast<uint2*>(dst) = make_uint2(a, b);
+  }
+  // K side of the same 32 channels (few rows of a bulk write have any: open or sealed groups, the K_ref window)
+  const int64_t rslot = A.tok[A.tok_s0 + row];
+  const bool sealed = A.tok[2 * A.tok_s0 + row] != 0;
+  const int64_t kidx = A.kref ? A.tok[3 * A.tok_s0 + row] : -1;
+  if (rslot < 0 && !sealed && kidx < 0) return;
+#pragma unroll 1
+  for (int i = 0; i < 4; ++i) key_chunk<T>(A, row, (h * L.D + gi * 32) / 8 + i, off, bits, walk.offset(), rslot, sealed, kidx);
 }
 
 template <typename T, int MODE>
@@ -408,10 +488,14 @@ __device__ __forceinline__ void finalize_group(const FinArgs<T>& A, int64_t f) {
         for (int k = 0; k < 8; ++k) x[k] = ld_dt(res, res_dt, ro + k);
       }
     };
+    // raw16 rows: key row indices and strides fit 32 bits (checked by the launcher), so a row's offset is one
+    // 32 x 32 -> 64-bit multiply
+    const T* kcol = key + (h * k_s1 + d0);
+    const T* rcol = reinterpret_cast<const T*>(res) + (rs * r_s0 + h * r_s2 + d0);
+    const int ks0 = (int)k_s0, rs1 = (int)r_s1;
     auto load_raw = [&](int p) -> uint4 {
-      const int64_t r = SEAL ? -1 : rows[p];
-      const T* src = r >= 0 ? key + (r * k_s0 + h * k_s1 + d0)
-                            : reinterpret_cast<const T*>(res) + (rs * r_s0 + (int64_t)p * r_s1 + h * r_s2 + d0);
+      const int r = SEAL ? -1 : (int)rows[p];
+      const T* src = r >= 0 ? kcol + (int64_t)r * ks0 : rcol + (int64_t)p * rs1;
       return *reinterpret_cast<const uint4*>(src);
     };
     if constexpr (sizeof(T) == 2) {
@@ -445,15 +529,34 @@ __device__ __forceinline__ void finalize_group(const FinArgs<T>& A, int64_t f) {
     *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(page + L.o_km) + e) = *reinterpret_cast<uint4*>(m16);
     RowWalk walk;
     walk.start(pages, L, sh.BS, blk, grp * L.KG, bits);
-    for (int p = 0; p < ntok; ++p) {
-      if constexpr (sizeof(T) == 2) {
-        if (raw16) cvt8<T>(load_raw(p), x);
-        else load(p);
-      } else {
-        load(p);
+    const int col_bytes = h * head_bytes + (d0 * bits) / 8;
+    bool done = false;
+    if constexpr (sizeof(T) == 2) {
+      if (raw16) {
+        // the tier is fixed for the group: one loop per tier, the row's address advanced by additions
+        auto codes = [&](auto BITS) {
+          uint8_t* dst = pages + walk.offset() + col_bytes;
+          for (int p = 0; p < ntok; ++p) {
+            cvt8<T>(load_raw(p), x);
+            store_packed8(dst, quant_pack8<decltype(BITS)::value, true>(x, m, sc, rsc), decltype(BITS)::value);
+            if (p + 1 < ntok) {
+              if (walk.r + 1 == walk.tpc) { walk.next(pages, L); dst = pages + walk.offset() + col_bytes; }
+              else { ++walk.r; dst += walk.row_bytes; }
+            }
+          }
+        };
+        if (bits == 4) codes(std::integral_constant<int, 4>{});
+        else if (bits == 8) codes(std::integral_constant<int, 8>{});
+        else codes(std::integral_constant<int, 2>{});
+        done = true;
       }
-      quant_store8<true>(bits, pages + walk.offset() + h * head_bytes + (d0 * bits) / 8, x, m, sc, rsc);
-      if (p + 1 < ntok) walk.next(pages, L);
+    }
+    if (!done) {
+      for (int p = 0; p < ntok; ++p) {
+        load(p);
+        quant_store8<true>(bits, pages + walk.offset() + col_bytes, x, m, sc, rsc);
+        if (p + 1 < ntok) walk.next(pages, L);
+      }
     }
   }
   if constexpr (SEAL) {
@@ -462,7 +565,7 @@ __device__ __forceinline__ void finalize_group(const FinArgs<T>& A, int64_t f) {
 }
 
 template <typename T, bool SEAL>
-__global__ void __launch_bounds__(256) finalize_k_kernel(const FinArgs<T> A) {
+__global__ void __launch_bounds__(256, 4) finalize_k_kernel(const FinArgs<T> A) {
   if constexpr (!SEAL) {
     if ((int64_t)blockIdx.x >= *A.fin_count) return;
   }
@@ -599,7 +702,7 @@ static FinArgs<T> fin_args(const LayoutDev& L, const echokv_pages* pages, const 
   A.fin = fin; A.fin_count = fin_count;
   A.res = R.base; A.res_dt = R.dtype; A.r_s0 = R.s_slot; A.r_s1 = R.s_pos; A.r_s2 = R.s_head;
   A.vec_in = key && vec_ok<T>(key, k_s0, k_s1);
-  A.raw16 = A.vec_in && residual_raw<T>(R);
+  A.raw16 = A.vec_in && residual_raw<T>(R) && k_s0 < (1ll << 31) && R.s_pos < (1ll << 31);
   A.sh = make_shifts(L);
   A.seal_slot = 0; A.seal_block = 0; A.seal_group = 0; A.seal_fill = 0; A.seal_bits = 0; A.seal_mask = 0;
   return A;
@@ -661,8 +764,14 @@ int echokv_write_tokens(const echokv_layout* layout, const echokv_pages* pages, 
   cudaStream_t st = (cudaStream_t)stream;
 #define LAUNCH(T)                                                                                                   \
   {                                                                                                                 \
-    const TokArgs<T> A = tok_args<T>(L, pages, R, key, k_s0, k_s1, value, v_s0, v_s1, tok, tok_s0, kref, kref_s0,   \
-                                     kref_s1, n_rows);                                                              \
+    TokArgs<T> A = tok_args<T>(L, pages, R, key, k_s0, k_s1, value, v_s0, v_s1, tok, tok_s0, kref, kref_s0,         \
+                               kref_s1, n_rows);                                                                    \
+    if (mode == 1 && sizeof(T) == 2 && A.vec_in && L.VG == 32 && L.D % 32 == 0) {                                   \
+      const int gpr = L.H * L.NG;                                                                                   \
+      const int64_t threads = n_rows * gpr;                                                                         \
+      write_tokens_bulk_kernel<T><<<(unsigned)((threads + 127) / 128), 128, 0, st>>>(A, gpr, log2_or_neg(gpr),      \
+                                                                                      log2_or_neg(L.NG));           \
+    } else                                                                                                          \
     if (mode == 2) write_tokens_kernel<T, 2><<<grid, WT_WARPS * 32, 0, st>>>(A);                                    \
     else if (mode == 1) write_tokens_kernel<T, 1><<<grid, WT_WARPS * 32, 0, st>>>(A);                               \
     else write_tokens_kernel<T, 0><<<grid, WT_WARPS * 32, 0, st>>>(A);                                              \
