@@ -874,7 +874,10 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the bulk copies write the same bytes later
   }
   __syncthreads();
-  pdl_wait();  // barriers and ring are set up; from here on this kernel reads what the kernels before it wrote
+  // Barriers and ring are set up.  From here on the consumers read what the kernels before this one wrote (queries,
+  // pages, split partials); the producer first resolves its first work item's metadata, which no kernel of the step
+  // writes (lengths, block table, page headers and the residual map are set before the step's kernels start).
+  if (warp != H) pdl_wait();
 
   bool ok = true;
   if (warp == H) {
@@ -897,12 +900,21 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
     int64_t seq_len = 0, bt_row = 0;
     bool have = false;
     const int bps_min = bps_floor(A);
+    // A team's first work item is its own index; the counter (which the merge kernel before this one may still be
+    // resetting when this runs ahead of `pdl_wait`) hands out the items after the first round.
+    const int n_teams = gridDim.x * V;
+    bool first_claim = true;
     auto advance = [&]() {  // move to the next unit (claiming a new item when needed); false when there is no work left
       if (have && base + U < b_end) { base += U; return true; }
       for (;;) {
         int it = 0;
-        if (lane == 0) it = atomicAdd(P.counter, 1);
-        it = __shfl_sync(0xffffffffu, it, 0);
+        if (first_claim) {
+          it = blockIdx.x * V + team;
+          first_claim = false;
+        } else {
+          if (lane == 0) it = atomicAdd(P.counter, 1);
+          it = __shfl_sync(0xffffffffu, it, 0) + n_teams;
+        }
         if (it >= n_items) { have = false; return false; }
         if (item_range(P, bps_min, it, seq, split, seq_len, b_start, b_end)) {
           base = b_start; bt_row = A.bt_rows ? A.bt_rows[seq] : seq; have = true;
@@ -960,6 +972,7 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
     };
     bool more = P.idle_producer ? false : advance();
     BlockMeta nxt = more ? load_meta(P, bt_row, lane < U ? base + lane : b_end, b_end) : BlockMeta{};
+    pdl_wait();  // pages and the work counter are final from here on
     while (more && ok) {
       const BlockMeta cur = nxt;
       const int u_base = base, u_end = b_end, u_seq = seq, u_split = split;

@@ -131,8 +131,8 @@ int echokv_seal_group(const echokv_layout* layout, const echokv_pages* pages,
 /* One layer's writes of a step in ONE launch: echokv_finalize_k (n_fin_launch CTAs masked by *fin_count),
  * echokv_write_tokens and echokv_gather_rows (the canary's query rows: stash_dst[i] = stash_src[stash_rows[i]],
  * skipped when stash_src is NULL or stash_n is 0) with the same arguments and the same stored bytes as the three
- * calls made in that order.  The reference launches them one after the other (tiered_cache.py:404-416,
- * backend.py:612-614); the group pass must come first there because a residual slot a completing group gives up
+ * calls made in that order.  The reference launches them one after the other (tiered_cache.py:415-432,
+ * backend.py:632-635); the group pass must come first there because a residual slot a completing group gives up
  * may be taken by a new group in the same step.  In the single launch the CTA of such a token row leaves the key
  * to the CTA of the completing group, which stores it after its own last read of the slot.  Steps of more than
  * 1,024 rows, and layouts or stash rows the single kernel does not take, run as the three launches. */

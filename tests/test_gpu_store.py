@@ -94,7 +94,7 @@ def _takeover_scenario(dtype):
 
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 def test_slot_given_up_and_taken_over_in_one_step(dtype):
-    """tiered_cache.py:404-416 runs the group pass before the token pass because a slot a completing group gives
+    """tiered_cache.py:415-432 runs the group pass before the token pass because a slot a completing group gives
     up may be reused in the same step; the one-launch kernel must store the same bytes with both running at once."""
     from cuda_runner import run_cuda
     from echokv_b200.write_plan import WritePlanner
