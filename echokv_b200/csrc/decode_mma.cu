@@ -926,10 +926,11 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
     // `rows`: 1 = a whole INT4 / INT2 tile (token rows in pairs, all stats); 2 / 3 = the first / second half of an INT8
     // tile (eight whole token rows, their V stats; the K stats with the first half).
     auto fill = [&](const TilePlan& d, int flags_extra, int rows) -> bool {
-      if (!mbar_wait(empty_u + st * 8, (pph >> st) & 1, P.wait_ns)) return false;
-      pph ^= 1u << st;
+      // Everything that does not need the stage to be free comes first (header values, each lane's one copy: where
+      // from, where to, how long), so that the wait for the consumers' release is followed by the header store, the
+      // byte count and the copies alone.
       const int4 h0 = *reinterpret_cast<const int4*>(&d.hdr);   // bits, n_valid, flags, pos0
-      const uint32_t bar = full_u + st * 8, st_u = ring_u + (uint32_t)st * SB;
+      const int4 h1 = reinterpret_cast<const int4*>(&d.hdr)[1];
       const int nv = h0.y;
       const uint32_t side = 16u * H * h0.x;                     // bytes of one side (K or V) of a token row: H * D * bits / 8
       const uint32_t k_stats = 2u * H * D * 2, v_stats = 2u * TILE * H * NG * 2;
@@ -937,35 +938,43 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
       auto row_src = [&](int t) { return d.run[t / rt] + (uint32_t)(t % rt) * 2u * side; };
       const int half0 = rows == 3 ? TILE / 2 : 0;               // first token of an INT8 half
       const int nh = rows == 1 ? nv : max(0, min(nv - half0, TILE / 2));  // token rows this stage receives
-      if (lane == 0) {
-        int4* hd = reinterpret_cast<int4*>(ring + (size_t)st * SB + o_hdr(H));
-        hd[0] = make_int4(h0.x, h0.y, h0.z | flags_extra, h0.w);
-        hd[1] = reinterpret_cast<const int4*>(&d.hdr)[1];
-        const uint32_t tx = rows == 1 ? nv * 2 * side + k_stats + v_stats : nh * 2 * side + v_stats / 2 + (rows == 2 ? k_stats : 0u);
-        mbar_expect_tx(bar, tx);
-      }
-      __syncwarp();
+      const uint32_t tx = rows == 1 ? nv * 2 * side + k_stats + v_stats : nh * 2 * side + v_stats / 2 + (rows == 2 ? k_stats : 0u);
+      uint32_t c_dst = 0, c_bytes = 0;
+      const unsigned char* c_src = nullptr;
       if (rows == 1) {
         // lane p < 8 copies tokens 2p and 2p + 1 in one piece (neighbours in their chunk: a chunk holds an even number of tokens)
-        if (lane < 8) { if (2 * lane < nv) bulk_copy(st_u + lane * slot_bytes(H), row_src(2 * lane), (2 * lane + 1 < nv ? 4u : 2u) * side, bar, policy); }
-        if (contig) {
-          if (lane == 16) bulk_copy(st_u + o_vs(H), d.stats[0], v_stats + k_stats, bar, policy);
+        if (lane < 8) {
+          if (2 * lane < nv) { c_dst = lane * slot_bytes(H); c_src = row_src(2 * lane); c_bytes = (2 * lane + 1 < nv ? 4u : 2u) * side; }
+        } else if (contig) {
+          if (lane == 16) { c_dst = o_vs(H); c_src = d.stats[0]; c_bytes = v_stats + k_stats; }
         } else if (lane >= 16 && lane < 20) {
           const int which = lane - 16;  // vs, vm, ks, km
-          const int dst_off = which == 0 ? o_vs(H) : which == 1 ? o_vm(H) : which == 2 ? o_ks(H) : o_km(H);
-          bulk_copy(st_u + dst_off, d.stats[which], which < 2 ? v_stats / 2 : k_stats / 2, bar, policy);
+          c_dst = which == 0 ? o_vs(H) : which == 1 ? o_vm(H) : which == 2 ? o_ks(H) : o_km(H);
+          c_src = d.stats[which];
+          c_bytes = which < 2 ? v_stats / 2 : k_stats / 2;
         }
       } else {
         // lane t < 8 copies the whole row [K | V] of token half0 + t to slot t
-        if (lane < nh) bulk_copy(st_u + lane * slot_bytes(H), row_src(half0 + lane), 2u * side, bar, policy);
+        if (lane < nh) { c_dst = lane * slot_bytes(H); c_src = row_src(half0 + lane); c_bytes = 2u * side; }
         // the V stats of the half's eight tokens; with the first half the K group's stats
-        if (lane == 16) bulk_copy(st_u + o_vs(H), d.stats[0] + half0 * (H * NG * 2), v_stats / 4, bar, policy);
-        if (lane == 17) bulk_copy(st_u + o_vm(H), d.stats[1] + half0 * (H * NG * 2), v_stats / 4, bar, policy);
+        if (lane == 16) { c_dst = o_vs(H); c_src = d.stats[0] + half0 * (H * NG * 2); c_bytes = v_stats / 4; }
+        if (lane == 17) { c_dst = o_vm(H); c_src = d.stats[1] + half0 * (H * NG * 2); c_bytes = v_stats / 4; }
         if (rows == 2) {
-          if (contig) { if (lane == 18) bulk_copy(st_u + o_ks(H), d.stats[2], k_stats, bar, policy); }
-          else if (lane == 18 || lane == 19) bulk_copy(st_u + (lane == 18 ? o_ks(H) : o_km(H)), d.stats[lane - 16], k_stats / 2, bar, policy);
+          if (contig) { if (lane == 18) { c_dst = o_ks(H); c_src = d.stats[2]; c_bytes = k_stats; } }
+          else if (lane == 18 || lane == 19) { c_dst = lane == 18 ? o_ks(H) : o_km(H); c_src = d.stats[lane - 16]; c_bytes = k_stats / 2; }
         }
       }
+      if (!mbar_wait(empty_u + st * 8, (pph >> st) & 1, P.wait_ns)) return false;
+      pph ^= 1u << st;
+      const uint32_t bar = full_u + st * 8, st_u = ring_u + (uint32_t)st * SB;
+      if (lane == 0) {
+        int4* hd = reinterpret_cast<int4*>(ring + (size_t)st * SB + o_hdr(H));
+        hd[0] = make_int4(h0.x, h0.y, h0.z | flags_extra, h0.w);
+        hd[1] = h1;
+        mbar_expect_tx(bar, tx);
+      }
+      __syncwarp();
+      if (c_bytes) bulk_copy(st_u + c_dst, c_src, c_bytes, bar, policy);
       ++fills;
       st = ring_next(st, NS);
       return true;
