@@ -979,6 +979,62 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
       st = ring_next(st, NS);
       return true;
     };
+    // Two stages in one pass (the two tiles of a pair, or the two halves of an INT8 tile): lanes 0..15 prepare and
+    // issue the first stage's copies, lanes 16..31 the second's (rows from sub-lanes 0..7, statistics from 8..11).
+    auto fill2 = [&](const TilePlan& dA, int fxA, int rowsA, const TilePlan& dB, int fxB, int rowsB) -> bool {
+      const int half = lane >> 4, sl = lane & 15;
+      const TilePlan& d = half ? dB : dA;
+      const int rows = half ? rowsB : rowsA, fx = half ? fxB : fxA;
+      const int4 h0 = *reinterpret_cast<const int4*>(&d.hdr);
+      const int4 h1 = reinterpret_cast<const int4*>(&d.hdr)[1];
+      const int nv = h0.y;
+      const uint32_t side = 16u * H * h0.x;
+      const uint32_t k_stats = 2u * H * D * 2, v_stats = 2u * TILE * H * NG * 2;
+      const int rt = min((2 * L.BS) / h0.x, TILE);
+      auto row_src = [&](int t) { return d.run[t / rt] + (uint32_t)(t % rt) * 2u * side; };
+      const int half0 = rows == 3 ? TILE / 2 : 0;
+      const int nh = rows == 1 ? nv : max(0, min(nv - half0, TILE / 2));
+      const uint32_t tx = rows == 1 ? nv * 2 * side + k_stats + v_stats : nh * 2 * side + v_stats / 2 + (rows == 2 ? k_stats : 0u);
+      uint32_t c_dst = 0, c_bytes = 0;
+      const unsigned char* c_src = nullptr;
+      if (rows == 1) {
+        if (sl < 8) {
+          if (2 * sl < nv) { c_dst = sl * slot_bytes(H); c_src = row_src(2 * sl); c_bytes = (2 * sl + 1 < nv ? 4u : 2u) * side; }
+        } else if (contig) {
+          if (sl == 8) { c_dst = o_vs(H); c_src = d.stats[0]; c_bytes = v_stats + k_stats; }
+        } else if (sl < 12) {
+          const int which = sl - 8;  // vs, vm, ks, km
+          c_dst = which == 0 ? o_vs(H) : which == 1 ? o_vm(H) : which == 2 ? o_ks(H) : o_km(H);
+          c_src = d.stats[which];
+          c_bytes = which < 2 ? v_stats / 2 : k_stats / 2;
+        }
+      } else {
+        if (sl < nh && sl < 8) { c_dst = sl * slot_bytes(H); c_src = row_src(half0 + sl); c_bytes = 2u * side; }
+        if (sl == 8) { c_dst = o_vs(H); c_src = d.stats[0] + half0 * (H * NG * 2); c_bytes = v_stats / 4; }
+        if (sl == 9) { c_dst = o_vm(H); c_src = d.stats[1] + half0 * (H * NG * 2); c_bytes = v_stats / 4; }
+        if (rows == 2) {
+          if (contig) { if (sl == 10) { c_dst = o_ks(H); c_src = d.stats[2]; c_bytes = k_stats; } }
+          else if (sl == 10 || sl == 11) { c_dst = sl == 10 ? o_ks(H) : o_km(H); c_src = d.stats[sl - 8]; c_bytes = k_stats / 2; }
+        }
+      }
+      const int stB = ring_next(st, NS);
+      if (!mbar_wait(empty_u + st * 8, (pph >> st) & 1, P.wait_ns)) return false;
+      if (!mbar_wait(empty_u + stB * 8, (pph >> stB) & 1, P.wait_ns)) return false;
+      pph ^= (1u << st) | (1u << stB);
+      const int my = half ? stB : st;
+      const uint32_t bar = full_u + my * 8, st_u = ring_u + (uint32_t)my * SB;
+      if (sl == 0) {
+        int4* hd = reinterpret_cast<int4*>(ring + (size_t)my * SB + o_hdr(H));
+        hd[0] = make_int4(h0.x, h0.y, h0.z | fx, h0.w);
+        hd[1] = h1;
+        mbar_expect_tx(bar, tx);
+      }
+      __syncwarp();
+      if (c_bytes) bulk_copy(st_u + c_dst, c_src, c_bytes, bar, policy);
+      fills += 2;
+      st = ring_next(stB, NS);
+      return true;
+    };
     bool more = P.idle_producer ? false : advance();
     BlockMeta nxt = more ? load_meta(P, bt_row, lane < U ? base + lane : b_end, b_end) : BlockMeta{};
     pdl_wait();  // pages and the work counter are final from here on
@@ -1038,9 +1094,9 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
         const TilePlan& d = plan[ti];
         const int bits = d.hdr.bits;
         if (bits == 8) {  // two stages: K side with the K stats, then V side with the V stats
-          ok = fill(d, 0, 2) && fill(d, 0, 3);
+          ok = fill2(d, 0, 2, d, 0, 3);
         } else if (ti + 1 < unit_tiles && ((pair_ok >> ti) & 3) == 3 && plan[ti + 1].hdr.bits == bits) {
-          ok = fill(d, F_PAIR | (plan[ti + 1].hdr.flags & F_LAST), 1) && fill(plan[ti + 1], 0, 1);
+          ok = fill2(d, F_PAIR | (plan[ti + 1].hdr.flags & F_LAST), 1, plan[ti + 1], 0, 1);
           ++ti;
         } else {
           ok = fill(d, 0, 1);
