@@ -27,7 +27,7 @@ def choose_blocks_per_split(lens, block_size: int, num_splits: int, slots: int) 
     The split kernel works on ``slots`` (sequence, split) items at a time, so the step takes
     ``ceil(items / slots)`` waves of one item's time each: a split of b blocks costs ``b * block_size / 16 +
     ITEM_COST_TILES``.  Every split count up to ``num_splits`` is tried on the mean sequence and the
-    cheapest wins (ties: fewer, larger splits, which leave less to merge).  The value is a launch
+    cheapest wins (ties: fewer, larger splits, which leave less to merge); splits hold an even number of tiles.  The value is a launch
     parameter shared by all sequences of the step, so for a given value results stay batch-invariant.
     """
     import numpy as np
@@ -42,6 +42,8 @@ def choose_blocks_per_split(lens, block_size: int, num_splits: int, slots: int) 
     best = None
     for s in range(1, max(1, num_splits) + 1):
         b = max(floor, -(-nb // s))
+        if (b * tiles) & 1:
+            b += 1  # the kernel works a split off in pairs of tiles: an odd count leaves one tile on the slower single path
         used = -(-nb // b)
         waves = -(-(int(live.size) * used) // slots)
         cost = waves * (b * tiles + ITEM_COST_TILES)
