@@ -60,8 +60,9 @@ def summarize_requests(reqs: list[dict], wall: float) -> dict:
     return res
 
 
-def closed_loop(engine, prompts: list[dict], sampling, concurrency: int) -> dict:
-    """Keep ``concurrency`` requests in flight until every prompt has been served."""
+def closed_loop(engine, prompts: list[dict], sampling, concurrency: int, delta: bool = False) -> dict:
+    """Keep ``concurrency`` requests in flight until every prompt has been served.  ``delta``: the engine's outputs
+    carry only the tokens produced since the previous step (otherwise all tokens so far)."""
     pending = list(enumerate(prompts))
     reqs: dict[str, dict] = {}
     seen: dict[str, int] = {}
@@ -81,7 +82,7 @@ def closed_loop(engine, prompts: list[dict], sampling, concurrency: int) -> dict
         outs = engine.step()
         now = time.perf_counter()
         for o in outs:
-            n = len(o.outputs[0].token_ids)  # cumulative
+            n = len(o.outputs[0].token_ids) + (seen[o.request_id] if delta else 0)
             if n > seen[o.request_id]:
                 reqs[o.request_id]["token_times"].extend([now] * (n - seen[o.request_id]))
                 seen[o.request_id] = n
@@ -112,15 +113,21 @@ def child(args) -> None:
     cfg = llm.llm_engine.vllm_config.cache_config
     rng = random.Random(0)
     vocab = llm.llm_engine.vllm_config.model_config.get_vocab_size()
-    sp = SamplingParams(temperature=0.0, max_tokens=args.output_len, ignore_eos=True, detokenize=not args.random_init)
+    from vllm.sampling_params import RequestOutputKind
+
+    def sampling(kind):
+        return SamplingParams(temperature=0.0, max_tokens=args.output_len, ignore_eos=True,
+                              detokenize=not args.random_init, output_kind=kind)
 
     def make(n: int) -> list[dict]:
         return [{"prompt_token_ids": [rng.randrange(100, vocab - 100) for _ in range(args.input_len)]} for _ in range(n)]
 
-    llm.generate(make(2), sp)  # warm up
+    llm.generate(make(2), sampling(RequestOutputKind.FINAL_ONLY))  # warm up (`generate` reports a request once, at its end)
     res = {"kv_capacity_tokens": (cfg.num_gpu_blocks or 0) * cfg.block_size, "levels": {}}
     for c in args.concurrency:
-        res["levels"][str(c)] = closed_loop(llm.llm_engine, make(args.requests_per_user * c), sp, c)
+        # DELTA: every engine step reports the tokens it produced; parameters of their own, `generate` rewrites its
+        sp = sampling(RequestOutputKind.DELTA)
+        res["levels"][str(c)] = closed_loop(llm.llm_engine, make(args.requests_per_user * c), sp, c, delta=True)
     with open(args.child_out, "w") as f:
         json.dump(res, f)
 

@@ -59,3 +59,15 @@ def test_closed_loop_keeps_the_concurrency_and_serves_every_prompt():
     eng = Engine()
     res = latency.closed_loop(eng, [{"prompt_token_ids": [1]}] * 7, None, concurrency=3)
     assert eng.served == 7 and eng.max_running == 3 and res["completed"] == 7
+    assert res["output_tok_s"] * res["wall_s"] == pytest.approx(21)
+
+    class DeltaEngine(Engine):  # reports only the tokens of the step
+        def step(self):
+            outs = super().step()
+            for o in outs:
+                o.outputs[0].token_ids = o.outputs[0].token_ids[-1:]
+            return outs
+
+    eng = DeltaEngine()
+    res = latency.closed_loop(eng, [{"prompt_token_ids": [1]}] * 5, None, concurrency=2, delta=True)
+    assert eng.served == 5 and res["output_tok_s"] * res["wall_s"] == pytest.approx(15)
