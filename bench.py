@@ -66,6 +66,8 @@ def parse():
     ap.add_argument("--no-stock", action="store_true", help="skip the stock bf16-KV attention library on the same shape")
     ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill probe (configuration 3 shape)")
     ap.add_argument("--no-config5", action="store_true", help="skip the 70B-shape run with the live controller")
+    ap.add_argument("--no-serving-geometry", action="store_true",
+                    help="skip the split kernel's probe at block 64 / k_group 32 (the reference's serving geometry)")
     ap.add_argument("--config5-layers", type=int, default=4, help="resident layers cycled to stand for the 80 of the 70B shape")
     ap.add_argument("--config5-steps", type=int, default=4)
     ap.add_argument("--one-rank-of", type=int, default=1, metavar="N",
@@ -418,6 +420,64 @@ def stock_bf16_probe(dev, S: int, ctx: int, seed: int):
     best = min(timed, key=timed.get)
     return {"what": best + ", same batch / context / heads", "ms_per_layer": timed[best], "gbs": nbytes / timed[best] / 1e6,
             "bytes_per_layer": nbytes, "tried": tried}
+
+
+def serving_geometry_probe(a, dev, peaks: dict, S: int, ctx: int) -> dict:
+    """The split kernel at the reference's serving geometry (block 64, k_group 32, mem_bits 4: 1,280 bytes per
+    token at INT4, evaluation/serving/echokv_throughput.py:85 and echokv_vllm/config.py:43) on the benchmark's batch
+    and context: two resident INT4 layers alternate (each pool larger than L2), CUDA events right around the kernel."""
+    import torch
+
+    from echokv_b200 import _native as N
+    from echokv_b200.controller import ControllerParams, LayerController
+    from echokv_b200.step import GroupRunner
+    from echokv_b200.tiered_cache import TieredLayout
+
+    bs, kg, mem, R = 64, 32, 4, 2
+    layout = TieredLayout(num_kv_heads=H, head_size=D, block_size=bs, mem_bits=mem, k_group=kg, v_group=VG)
+    bpseq = -(-(ctx + 64) // bs)
+    nb = S * bpseq + 8
+    page = bs * TieredLayout.per_token_bytes(H, D, mem, kg, VG)
+    caches = [torch.zeros(nb, page, dtype=torch.uint8, device=dev) for _ in range(R)]
+    ctl = [LayerController(ControllerParams(fixed_bits=4)) for _ in range(R)]
+    runner = GroupRunner(layout, caches, HQ, D ** -0.5, ctl, residual_slots=S + 16, model_dtype=torch.bfloat16, cap=S,
+                         max_model_len=bpseq * bs)
+    table_np = np.random.default_rng(a.seed + 23).permutation(nb)[: S * bpseq].reshape(S, bpseq).astype(np.int32)
+    table = torch.from_numpy(table_np).to(dev)
+    gen = torch.Generator(device=dev).manual_seed(a.seed + 900)
+    for c0 in range(0, ctx, 512):
+        pos = np.arange(c0, min(ctx, c0 + 512))
+        slots = (table_np[:, pos // bs].astype(np.int64) * bs + pos % bs).reshape(-1)
+        meta = runner.plan_step(slots)
+        for l in range(R):
+            runner.write(l, torch.randn(slots.size, H, D, device=dev, generator=gen).bfloat16(),
+                         torch.randn(slots.size, H, D, device=dev, generator=gen).bfloat16(), meta)
+    rows = np.arange(S)
+    slots = table_np[:, ctx // bs].astype(np.int64) * bs + ctx % bs
+    meta = runner.plan_step(slots, decode=(rows, rows, np.full(S, ctx + 1)))
+    q = torch.randn(R, S, HQ, D, device=dev, generator=gen).bfloat16()
+    out = torch.zeros_like(q)
+    for l in range(R):
+        runner.write(l, torch.randn(S, H, D, device=dev, generator=gen).bfloat16(),
+                     torch.randn(S, H, D, device=dev, generator=gen).bfloat16(), meta)
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record(); k1.record()
+    torch.cuda.synchronize()
+    ts = []
+    N.lib.echokv_set_decode_events(k0.cuda_event, k1.cuda_event)
+    try:
+        for i in range(8):
+            runner.decode(i % R, q[i % R], table, out[i % R], meta)
+            torch.cuda.synchronize()
+            ts.append(k0.elapsed_time(k1))
+    finally:
+        N.lib.echokv_set_decode_events(None, None)
+    t = float(np.median(ts[2:]))
+    nbytes = decode_bytes(np.full(S, ctx + 1), 4, H, HQ, bs=bs, kg=kg)
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    return {"what": "decode_mma_kernel, INT4, block 64 / k_group 32 / mem_bits 4 (the reference's serving geometry)",
+            "kernel_ms": t, "bytes": nbytes, "bytes_per_token": bytes_per_token(4, H, kg), "gbs": nbytes / t / 1e6,
+            "frac": nbytes / t / 1e6 / peak, "status": int(N.lib.echokv_kernel_status(0))}
 
 
 def config5_probe(a, dev, world: int, rank: int, peaks: dict) -> dict | None:
@@ -827,6 +887,7 @@ def run_b200(a) -> None:
     stock = stock_bf16_probe(dev, S, ctx, a.seed) if (rank == 0 and world == 1 and not a.no_stock) else None
     torch.cuda.empty_cache()
     cfg5 = None if a.no_config5 else config5_probe(a, dev, world, rank, peaks)
+    serving = serving_geometry_probe(a, dev, peaks, S, ctx) if (rank == 0 and world == 1 and shards == 1 and not a.no_serving_geometry) else None
 
     if rank == 0:
         cores = os.cpu_count() or 1
@@ -875,6 +936,7 @@ def run_b200(a) -> None:
             "prefill": prefill,
             "stock_bf16_decode": stock,
             "config5": cfg5,
+            "serving_geometry": serving,
             "write": {"gbs": write_bytes / write_ms / 1e6, "frac": write_bytes / write_ms / 1e6 / peak, "ms_total": write_ms,
                       "what": "bulk quantize-on-write of the context (finalize_k + write_tokens per layer and 512-position chunk, "
                               "events around each layer's launches, no host synchronisation between them)"},

@@ -12,6 +12,7 @@ from echokv_b200 import _native as N
 
 BLOCKS_PER_SPLIT = 16
 MAX_DECODE_SPLITS = 64  # upper bound of the split grid (backend.py:67-69 of the reference caps its fixed grid alike)
+EAGER_MAX_SPLITS = 32   # calls that size their own grid (the prefill row path): their scratch grows with rows x splits
 MIN_SPLIT_TOKENS = 64   # smallest split `choose_blocks_per_split` proposes
 ITEM_COST_TILES = 4     # fixed cost of a (sequence, split) work item in units of one 16-token tile's work
 
@@ -125,7 +126,7 @@ def decode_attention(store, query: torch.Tensor, block_table: torch.Tensor, seq_
     if num_splits is None:
         width = block_table.shape[1]
         max_blocks = width if max_len is None else min(width, -(-max_len // L.block_size))
-        num_splits = max(1, min(-(-max_blocks // blocks_per_split), MAX_DECODE_SPLITS))
+        num_splits = max(1, min(-(-max_blocks // blocks_per_split), EAGER_MAX_SPLITS))
     if s == 0:
         return out
     nbytes = N.lib.echokv_decode_scratch_bytes(s, hq, L.head_size, num_splits)

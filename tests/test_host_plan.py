@@ -154,3 +154,23 @@ def test_product_controller_follows_the_reference_trace(golden):
     pinned = LayerController(ControllerParams(fixed_bits=4))
     pinned.observe({2: 0.0, 4: 0.0, 8: 0.0}, 4096.0)
     assert pinned.bits == 4 and pinned.transitions == 0
+
+
+def test_blocks_per_split_fill_whole_waves_of_the_kernels_team_slots():
+    """The per-step split size: never below 64 tokens, an even number of 16-token tiles, never more splits than the
+    grid holds, and items that fill the split kernel's slots in whole waves at the benchmark's shapes."""
+    from echokv_b200.kernels.decode import BLOCKS_PER_SPLIT, choose_blocks_per_split
+
+    lens = np.full(64, 4097)
+    for slots, want_waves in ((296, 2), (592, 1), (888, 1), (1480, 1)):
+        b = choose_blocks_per_split(lens, 16, 64, slots)
+        used = -(-257 // b)
+        assert b >= 4 and b % 2 == 0 and used <= 64
+        assert -(-(64 * used) // slots) == want_waves, (slots, b)
+    # a long context at block size 64 (four tiles per block): any block count is an even number of tiles
+    b = choose_blocks_per_split(np.full(128, 32768), 64, 64, 296)
+    assert 1 <= b <= 512 and -(-512 // b) <= 64
+    # the grid's capacity wins over the minimum, padding rows (length 0) are ignored, no live row: the default
+    assert choose_blocks_per_split(np.array([0, 0, 100000]), 16, 8, 296) >= -(-6250 // 8)
+    assert choose_blocks_per_split(np.zeros(4, dtype=np.int64), 16, 64, 296) == BLOCKS_PER_SPLIT
+    assert choose_blocks_per_split(lens, 16, 64, 0) == BLOCKS_PER_SPLIT
