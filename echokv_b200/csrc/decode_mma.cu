@@ -59,6 +59,8 @@ constexpr unsigned long long WAIT_NS = 2000000000ull;  // a wait gives up after 
 // What the producer tells the consumers about a staged group (stored at `o_hdr` of its first stage).
 constexpr int F_RES = 1, F_FIRST = 2, F_LAST = 4;  // K from the residual buffer / first / last group of a work item
 constexpr int F_PAIR = 8;                          // the next stage holds a second full tile of the same tier
+constexpr int RT_LOG_SHIFT = 8;                    // plan entries only: bits 8..11 = log2(token rows per run), 15 = not a power of two
+constexpr int F_MASK = 0xff;                       // the flag bits a stage header carries
 struct alignas(16) StageHeader {
   int bits, n_valid, flags, pos0;   // n_valid: 1..16 tokens, -1 = no more work
   long long res_slot;
@@ -72,9 +74,9 @@ struct alignas(16) TilePlan {
 };
 constexpr int UNIT = 16;         // tiles planned at a time (one per producer lane)
 constexpr int MAX_NS = 8;        // stage ring slots at most
-constexpr int HDR_BYTES = 256;   // 2 * MAX_NS mbarriers + the remap lock
+constexpr int HDR_BYTES = 256;   // 2 * MAX_NS mbarriers
 static_assert(sizeof(StageHeader) == 32 && sizeof(TilePlan) % 16 == 0, "16-byte copies of headers");
-static_assert(2 * MAX_NS * 8 + 4 <= HDR_BYTES, "barriers and lock must fit the header");
+static_assert(2 * MAX_NS * 8 <= HDR_BYTES, "barriers must fit the header");
 
 // Stage layout (bytes from the stage base), the same for every tier.
 __host__ __device__ constexpr int slot_bytes(int H) { return 256 * H + 16; }            // two INT4-sized token rows + padding
@@ -130,6 +132,10 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 // Returns false if the barrier did not flip within `limit_ns`.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned long long limit_ns) {
   if (mbar_try(bar, parity)) return true;
+#pragma unroll 1
+  for (int it = 0; it < 4; ++it) {  // the phase is usually about to complete: a few polls before backing off
+    if (mbar_try(bar, parity)) return true;
+  }
   const unsigned long long t0 = global_ns();
   for (;;) {
 #pragma unroll 1
@@ -319,6 +325,7 @@ constexpr int QN_ROW = D * 2 + 16;
 __host__ __device__ constexpr int q_copy_bytes(int H, int gqa) { return (H * gqa + 1) * QN_ROW; }
 constexpr int REMAP_ROW = D + 4;                      // floats per query head in the canonical layout
 constexpr int REMAP_BYTES = 8 * REMAP_ROW * 4;
+constexpr int CTA_SHARED_BYTES = REMAP_BYTES + 128;  // the remap buffer and its lock, shared by the CTA's teams
 
 struct WarpState {
   float acc[8][4];  // O^T tiles: [m-tile][c0..c3], channel order depends on `bits`
@@ -848,20 +855,21 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
   const long long cta_c0 = clock64();
 #endif
 
-  // shared memory of a team: [barriers | lock][tile plans][remap][query copy per head][stage ring]
-  unsigned char* smem = smem_all + (size_t)team * P.team_bytes;
+  // shared memory of the CTA: [remap buffer | its lock] once (a warp needs it only when the tier changes inside a work
+  // item), then per team: [barriers][tile plans][query copy per head][stage ring]
+  float* remap = reinterpret_cast<float*>(smem_all);
+  int* lock = reinterpret_cast<int*>(smem_all + REMAP_BYTES);
+  unsigned char* smem = smem_all + CTA_SHARED_BYTES + (size_t)team * P.team_bytes;
   uint64_t* sfull = reinterpret_cast<uint64_t*>(smem);   // stage ring: header written, copies landed
   uint64_t* sempty = sfull + MAX_NS;                     // stage ring: every consumer warp is done with the stage
-  int* lock = reinterpret_cast<int*>(sempty + MAX_NS);
   TilePlan* plan = reinterpret_cast<TilePlan*>(smem + HDR_BYTES);
-  float* remap = reinterpret_cast<float*>(smem + HDR_BYTES + UNIT * sizeof(TilePlan));
-  unsigned char* qs = reinterpret_cast<unsigned char*>(remap) + REMAP_BYTES;
+  unsigned char* qs = smem + HDR_BYTES + UNIT * sizeof(TilePlan);
   unsigned char* ring = qs + (q_copy_bytes(H, A.gqa) + 127) / 128 * 128;
   const uint32_t ring_u = smem_u32(ring), full_u = smem_u32(sfull), empty_u = smem_u32(sempty);
 
   if (tid == 0) {
     for (int s = 0; s < MAX_NS; ++s) { mbar_init(sfull + s, 1); mbar_init(sempty + s, H * 32); }
-    *lock = 0;
+    if (team == 0) *lock = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   {  // zero the ring once: rows of a partial tile that are never copied must read as finite numbers
@@ -934,8 +942,12 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
       const int nv = h0.y;
       const uint32_t side = 16u * H * h0.x;                     // bytes of one side (K or V) of a token row: H * D * bits / 8
       const uint32_t k_stats = 2u * H * D * 2, v_stats = 2u * TILE * H * NG * 2;
-      const int rt = min((2 * L.BS) / h0.x, TILE);              // token rows per run (see TilePlan)
-      auto row_src = [&](int t) { return d.run[t / rt] + (uint32_t)(t % rt) * 2u * side; };
+      const int rt_log = (h0.z >> RT_LOG_SHIFT) & 15;           // token rows per run (see TilePlan) = 1 << rt_log
+      auto row_src = [&](int t) {
+        if (rt_log != 15) return d.run[t >> rt_log] + (uint32_t)(t & ((1 << rt_log) - 1)) * 2u * side;
+        const int rt = min((2 * L.BS) / h0.x, TILE);
+        return d.run[t / rt] + (uint32_t)(t % rt) * 2u * side;
+      };
       const int half0 = rows == 3 ? TILE / 2 : 0;               // first token of an INT8 half
       const int nh = rows == 1 ? nv : max(0, min(nv - half0, TILE / 2));  // token rows this stage receives
       const uint32_t tx = rows == 1 ? nv * 2 * side + k_stats + v_stats : nh * 2 * side + v_stats / 2 + (rows == 2 ? k_stats : 0u);
@@ -969,7 +981,7 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
       const uint32_t bar = full_u + st * 8, st_u = ring_u + (uint32_t)st * SB;
       if (lane == 0) {
         int4* hd = reinterpret_cast<int4*>(ring + (size_t)st * SB + o_hdr(H));
-        hd[0] = make_int4(h0.x, h0.y, h0.z | flags_extra, h0.w);
+        hd[0] = make_int4(h0.x, h0.y, (h0.z & F_MASK) | flags_extra, h0.w);
         hd[1] = h1;
         mbar_expect_tx(bar, tx);
       }
@@ -990,8 +1002,12 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
       const int nv = h0.y;
       const uint32_t side = 16u * H * h0.x;
       const uint32_t k_stats = 2u * H * D * 2, v_stats = 2u * TILE * H * NG * 2;
-      const int rt = min((2 * L.BS) / h0.x, TILE);
-      auto row_src = [&](int t) { return d.run[t / rt] + (uint32_t)(t % rt) * 2u * side; };
+      const int rt_log = (h0.z >> RT_LOG_SHIFT) & 15;           // token rows per run (see TilePlan) = 1 << rt_log
+      auto row_src = [&](int t) {
+        if (rt_log != 15) return d.run[t >> rt_log] + (uint32_t)(t & ((1 << rt_log) - 1)) * 2u * side;
+        const int rt = min((2 * L.BS) / h0.x, TILE);
+        return d.run[t / rt] + (uint32_t)(t % rt) * 2u * side;
+      };
       const int half0 = rows == 3 ? TILE / 2 : 0;
       const int nh = rows == 1 ? nv : max(0, min(nv - half0, TILE / 2));
       const uint32_t tx = rows == 1 ? nv * 2 * side + k_stats + v_stats : nh * 2 * side + v_stats / 2 + (rows == 2 ? k_stats : 0u);
@@ -1025,7 +1041,7 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
       const uint32_t bar = full_u + my * 8, st_u = ring_u + (uint32_t)my * SB;
       if (sl == 0) {
         int4* hd = reinterpret_cast<int4*>(ring + (size_t)my * SB + o_hdr(H));
-        hd[0] = make_int4(h0.x, h0.y, h0.z | fx, h0.w);
+        hd[0] = make_int4(h0.x, h0.y, (h0.z & F_MASK) | fx, h0.w);
         hd[1] = h1;
         mbar_expect_tx(bar, tx);
       }
@@ -1079,7 +1095,9 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
           }
           const int nv = min(TILE, blk_tok - t0);
           d.hdr.bits = bits; d.hdr.n_valid = nv;
-          d.hdr.flags = (in_res ? F_RES : 0) | (u_first && lane == 0 ? F_FIRST : 0) | (u_last && lane == unit_tiles - 1 ? F_LAST : 0);
+          const int rt_log = (rt & (rt - 1)) == 0 ? 31 - __clz(rt) : 15;  // for the fills: a run's rows by shift and mask
+          d.hdr.flags = (in_res ? F_RES : 0) | (u_first && lane == 0 ? F_FIRST : 0) |
+                        (u_last && lane == unit_tiles - 1 ? F_LAST : 0) | (rt_log << RT_LOG_SHIFT);
           d.hdr.pos0 = t0 - grp * L.KG; d.hdr.res_slot = ks_slot; d.hdr.seq = u_seq; d.hdr.split = u_split;
           d.stats[0] = page + L.o_vs + (int64_t)t0 * H * NG * 2;
           d.stats[1] = page + L.o_vm + (int64_t)t0 * H * NG * 2;
@@ -1365,15 +1383,16 @@ static int decode_device(DecodeDevice** out) {
 struct TeamShape { int V, ns, fixed; bool small; };
 static bool team_shape(const DecodeDevice& dv, int H, int gqa, TeamShape* out) {
   using namespace mma;
-  const int fixed = HDR_BYTES + UNIT * (int)sizeof(TilePlan) + REMAP_BYTES + (q_copy_bytes(H, gqa) + 127) / 128 * 128;
+  const int fixed = HDR_BYTES + UNIT * (int)sizeof(TilePlan) + (q_copy_bytes(H, gqa) + 127) / 128 * 128;
   const int sbytes = stage_bytes(H);
+  const int room = dv.max_smem - CTA_SHARED_BYTES;
   int V = H == 8 ? Teams<8>::V : H == 4 ? Teams<4>::V : H == 2 ? Teams<2>::V : Teams<1>::V;
   bool small = false;
-  int ns = ((dv.max_smem / V) / 128 * 128 - fixed) / sbytes;
+  int ns = ((room / V) / 128 * 128 - fixed) / sbytes;
   if (ns < 4) {
     small = true;
     V = H == 8 ? Teams<8>::V_SMALL : H == 4 ? Teams<4>::V_SMALL : H == 2 ? Teams<2>::V_SMALL : Teams<1>::V_SMALL;
-    ns = ((dv.max_smem / V) / 128 * 128 - fixed) / sbytes;
+    ns = ((room / V) / 128 * 128 - fixed) / sbytes;
   }
   if (ns > MAX_NS) ns = MAX_NS;
   if (ns < 4) return false;
@@ -1423,7 +1442,7 @@ int launch_decode_mma(const LayoutDev& L, const ResidualDev& R, const uint8_t* p
   const bool small = ts.small;
   P.NS = ns;
   P.team_bytes = (fixed + ns * sbytes + 127) / 128 * 128;
-  const int smem_bytes = P.team_bytes * V;
+  const int smem_bytes = CTA_SHARED_BYTES + P.team_bytes * V;
   const int64_t n_items = num_seqs * (int64_t)A.num_splits;
   int64_t grid = dv->num_sms;
   if (grid * V > n_items) grid = (n_items + V - 1) / V;
