@@ -1187,10 +1187,9 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
       split = (int)ex[3];
       return true;
     };
-    // A work item starts: this head's queries -> fp16 in shared memory, pre-multiplied by softmax_scale * log2(e)
-    // (rows >= gqa are zero), and a fresh state.  All global loads are issued before the first use so the item pays
-    // one memory latency.
-    auto begin_item = [&]() {
+    // This head's queries of sequence `seq` -> fp16 in shared memory, pre-multiplied by softmax_scale * log2(e)
+    // (rows >= gqa are zero).  All global loads are issued before the first use so the item pays one memory latency.
+    auto load_queries = [&]() {
       const int64_t q_row = A.q_rows ? A.q_rows[seq] : seq;
       __syncwarp();
       if (P.q_vec16) {  // 16-bit queries, 16-byte aligned rows: lane l loads 8 channels of rows l / 16, + 2, + 4, + 6
@@ -1227,6 +1226,22 @@ __global__ void __launch_bounds__((H + 1) * 32 * V, 1) decode_mma_kernel(const P
         }
       }
       __syncwarp();
+    };
+    // The team's first work item is its own index (see the producer): its queries are loaded while the producer
+    // resolves the item's blocks and the first copies are in flight.
+    int preloaded = -1;
+    {
+      const int item0 = blockIdx.x * V + team;
+      if (item0 < n_items) {
+        seq = item0 % P.num_seqs;
+        load_queries();
+        preloaded = seq;
+      }
+    }
+    // A work item starts: its queries (unless they are the ones loaded ahead) and a fresh state.
+    auto begin_item = [&]() {
+      if (seq != preloaded) load_queries();
+      preloaded = -1;
 #pragma unroll
       for (int mt = 0; mt < 8; ++mt) { w.acc[mt][0] = w.acc[mt][1] = w.acc[mt][2] = w.acc[mt][3] = 0.f; }
       w.bl[0] = w.bl[1] = w.bl[2] = w.bl[3] = 0.f;
