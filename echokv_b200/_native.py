@@ -99,12 +99,23 @@ lib.echokv_set_decode_path.argtypes = [C.c_int]
 lib.echokv_set_decode_path.restype = C.c_int
 lib.echokv_set_decode_wait_limit.argtypes = [C.c_int64, C.c_int]
 lib.echokv_set_decode_wait_limit.restype = C.c_int
+lib.echokv_planner_create.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32]
+lib.echokv_planner_create.restype = C.c_void_p
+lib.echokv_planner_destroy.argtypes = [C.c_void_p]
+lib.echokv_planner_destroy.restype = None
+lib.echokv_planner_get.argtypes = [C.c_void_p, C.c_int32]
+lib.echokv_planner_get.restype = C.c_int64
+lib.echokv_planner_sealed_mask.argtypes = [C.c_void_p, C.c_int64, C.c_int64]
+lib.echokv_planner_sealed_mask.restype = C.c_int64
+lib.echokv_planner_plan.argtypes = [C.c_void_p, C.c_void_p, C.c_int64] + [C.c_void_p] * 12
+lib.echokv_planner_plan.restype = C.c_int
 lib.echokv_decode_parallelism.argtypes = [_LP, C.c_int32]
 lib.echokv_decode_parallelism.restype = C.c_int32
 lib.echokv_kernel_status.argtypes = [C.c_int]
 lib.echokv_kernel_status.restype = C.c_int
 
-EXPORTS = sorted(list(_SIGS) + ["echokv_set_decode_path", "echokv_set_decode_wait_limit", "echokv_kernel_status", "echokv_set_prefill_path", "echokv_decode_static_scratch_bytes", "echokv_decode_parallelism", "echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
+EXPORTS = sorted(list(_SIGS) + ["echokv_set_decode_path", "echokv_set_decode_wait_limit", "echokv_kernel_status", "echokv_set_prefill_path", "echokv_decode_static_scratch_bytes", "echokv_decode_parallelism", "echokv_planner_create", "echokv_planner_destroy", "echokv_planner_get",
+                                "echokv_planner_sealed_mask", "echokv_planner_plan", "echokv_abi_version", "echokv_last_error", "echokv_decode_scratch_bytes",
                                 "echokv_demote_scratch_bytes"])
 
 

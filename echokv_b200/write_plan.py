@@ -252,6 +252,78 @@ class WritePlanner:
         )
 
 
+class _SealedView:
+    """``planner.sealed.get(block, default)`` over the native planner's map."""
+
+    def __init__(self, owner) -> None:
+        self._owner = owner
+
+    def get(self, block: int, default: int = 0) -> int:
+        from echokv_b200 import _native as N
+
+        return int(N.lib.echokv_planner_sealed_mask(self._owner._h, int(block), int(default)))
+
+
+class NativeWritePlanner:
+    """``WritePlanner`` with the state and ``plan`` in the C++ library (``csrc/planner.cu``): the same decisions, slot
+    numbering and output order (``tests/test_host_plan.py`` compares the two on seeded traffic), a fraction of the
+    host time per step.  Exposes what the stores read of a planner: ``plan``, ``free`` (its length), ``sealed.get``,
+    ``num_slots``, ``kref_pos``, ``kref_fill``, ``step``."""
+
+    def __init__(self, block_size: int, k_group: int, residual_slots: int, kref_window: int = 64) -> None:
+        from echokv_b200 import _native as N
+
+        self._N = N
+        self.bs, self.g = int(block_size), int(k_group)
+        self.num_slots, self.kref_window = int(residual_slots), int(kref_window)
+        self._h = N.lib.echokv_planner_create(self.bs, self.g, self.num_slots, self.kref_window)
+        if not self._h:
+            raise ValueError(N.lib.echokv_last_error().decode())
+        self.sealed = _SealedView(self)
+
+    def __del__(self) -> None:
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._N.lib.echokv_planner_destroy(h)
+
+    def _get(self, what: int) -> int:
+        return int(self._N.lib.echokv_planner_get(self._h, what))
+
+    free = property(lambda self: range(self._get(0)))
+    kref_pos = property(lambda self: self._get(1))
+    kref_fill = property(lambda self: self._get(2))
+    step = property(lambda self: self._get(3))
+
+    def plan(self, slot_mapping_cpu) -> WritePlan:
+        if torch.is_tensor(slot_mapping_cpu):
+            slot_mapping_cpu = slot_mapping_cpu.numpy()
+        sm = np.ascontiguousarray(np.asarray(slot_mapping_cpu).astype(_I64).reshape(-1))
+        n, w = sm.size, 3 + self.g
+        tok = np.empty((4, max(n, 1)), dtype=_I64)
+        fin = np.empty((max(n, 1), w), dtype=_I64)
+        ev = np.empty((max(n, 1), 4), dtype=_I64)
+        small = np.empty((4, max(n, 1)), dtype=_I64)  # opened, touched, touched fill, touched count
+        maps = np.empty((4, 4 * n + 8), dtype=_I64)   # map block / value, group slot / value
+        counts = np.zeros(8, dtype=_I64)
+        tokv = tok[:, :n]
+        rc = self._N.lib.echokv_planner_plan(
+            self._h, sm.ctypes.data, n, tok.ctypes.data, fin.ctypes.data, ev.ctypes.data,
+            small[0].ctypes.data, small[1].ctypes.data, small[2].ctypes.data, small[3].ctypes.data,
+            maps[0].ctypes.data, maps[1].ctypes.data, maps[2].ctypes.data, maps[3].ctypes.data, counts.ctypes.data)
+        if rc != 0:
+            raise RuntimeError(self._N.lib.echokv_last_error().decode())
+        n_fin, n_ev, n_open, n_touched, n_mb, n_mg, step = (int(x) for x in counts[:7])
+        evictions = [Eviction(*(int(x) for x in row)) for row in ev[:n_ev]]
+        return WritePlan(
+            step=step, n_rows=n, tok_slot=sm, tok_res=tokv[1].copy(), tok_sealed=tokv[2].copy(), tok_kref=tokv[3].copy(),
+            fin=fin[:n_fin].copy(), evictions=evictions, open_np=small[0, :n_open].copy(),
+            touched_np=small[1, :n_touched].copy(), touched_fill=small[2, :n_touched].copy(),
+            touched_count=small[3, :n_touched].copy(), res_map_block=maps[0, :n_mb].copy(),
+            res_map_value=maps[1, :n_mb].copy(), res_group_slot=maps[2, :n_mg].copy(),
+            res_group_value=maps[3, :n_mg].copy(), block_size=self.bs, k_group=self.g,
+        )
+
+
 class SharedState:
     """What all layers of one KV-cache group share: the planner, the device residual map read by
     the attention kernels, and per-block host bookkeeping (fill, recency, tokens written)."""
@@ -259,7 +331,7 @@ class SharedState:
     def __init__(self, num_blocks: int, block_size: int, k_group: int, residual_slots: int,
                  kref_window: int, device) -> None:
         self.num_blocks = num_blocks
-        self.planner = WritePlanner(block_size, k_group, residual_slots, kref_window)
+        self.planner = NativeWritePlanner(block_size, k_group, residual_slots, kref_window)
         self.fill_h = np.zeros(num_blocks, dtype=_I64)
         self.last_h = np.zeros(num_blocks, dtype=_I64)
         self.cum_h = np.zeros(num_blocks, dtype=_I64)

@@ -128,6 +128,23 @@ int echokv_seal_group(const echokv_layout* layout, const echokv_pages* pages,
                       const echokv_residual* residual, int64_t slot, int64_t block, int32_t group,
                       int32_t fill, int32_t bits, int32_t sealed_mask, void* stream);
 
+/* Host-side planner of a step's KV writes (no device work) -- WritePlanner (write_plan.py:77-240): the residual-slot
+ * allocator, the K_ref ring cursor and `plan`, with the same decisions, slot numbering and output order, so its
+ * plans are interchangeable with the Python planner's.  `slots` int64 [n_rows] (-1 = row not stored).  Outputs are
+ * caller-allocated int64 arrays: tok [4, n_rows] (slot, residual slot, sealed, K_ref row), fin [n_rows, 3 + k_group],
+ * evictions [n_rows, 4] (slot, block, group, fill), opened / touched / touched_fill / touched_count [n_rows],
+ * map_block / map_value / grp_slot / grp_value [4 * n_rows + 8] (the ordered residual-map updates), counts [8] =
+ * n_fin, n_evictions, n_opened, n_touched, n_map_block, n_map_group, step.  echokv_planner_get: 0 free slots,
+ * 1 K_ref cursor, 2 K_ref fill, 3 step, 4 slots in all, 5 live slots. */
+void* echokv_planner_create(int32_t block_size, int32_t k_group, int32_t residual_slots, int32_t kref_window);
+void echokv_planner_destroy(void* planner);
+int64_t echokv_planner_get(void* planner, int32_t what);
+int64_t echokv_planner_sealed_mask(void* planner, int64_t block, int64_t otherwise);
+int echokv_planner_plan(void* planner, const int64_t* slots, int64_t n_rows, int64_t* tok, int64_t* fin,
+                        int64_t* evictions, int64_t* opened, int64_t* touched, int64_t* touched_fill,
+                        int64_t* touched_count, int64_t* map_block, int64_t* map_value, int64_t* grp_slot,
+                        int64_t* grp_value, int64_t* counts);
+
 /* One layer's writes of a step in ONE launch: echokv_finalize_k (n_fin_launch CTAs masked by *fin_count),
  * echokv_write_tokens and echokv_gather_rows (the canary's query rows: stash_dst[i] = stash_src[stash_rows[i]],
  * skipped when stash_src is NULL or stash_n is 0) with the same arguments and the same stored bytes as the three

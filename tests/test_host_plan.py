@@ -174,3 +174,63 @@ def test_blocks_per_split_fill_whole_waves_of_the_kernels_team_slots():
     assert choose_blocks_per_split(np.array([0, 0, 100000]), 16, 8, 296) >= -(-6250 // 8)
     assert choose_blocks_per_split(np.zeros(4, dtype=np.int64), 16, 64, 296) == BLOCKS_PER_SPLIT
     assert choose_blocks_per_split(lens, 16, 64, 0) == BLOCKS_PER_SPLIT
+
+
+def test_native_planner_makes_the_same_plans_as_the_python_planner():
+    """`csrc/planner.cu` against `WritePlanner` on seeded traffic: prefill chunks and decode steps of several
+    sequences, padding rows, shuffled rows, blocks rewritten from their start, and so few residual slots that groups
+    are evicted and sealed -- every array of every plan, the eviction list, the K_ref cursor and the free-slot count."""
+    import dataclasses
+
+    from echokv_b200.write_plan import NativeWritePlanner, WritePlanner
+
+    rng = np.random.default_rng(42)
+    evictions = finalized = errors = 0
+    for trial in range(60):
+        bs = int(rng.choice([16, 32, 64]))
+        g = int(rng.choice([x for x in (16, 32) if bs % x == 0]))
+        n_slots, window = int(rng.choice([2, 3, 5, 16])), int(rng.choice([0, 8, 64]))
+        py, cc = WritePlanner(bs, g, n_slots, window), NativeWritePlanner(bs, g, n_slots, window)
+        n_seq = int(rng.integers(1, 5))
+        blocks = [list(rng.permutation(12)[:3]) for _ in range(n_seq)]
+        lens = [0] * n_seq
+        for step in range(40):
+            rows = []
+            for sq in range(n_seq):
+                for _ in range(int(rng.choice([0, 1, 1, 1, 2, 7, g, bs + 3]))):
+                    if lens[sq] >= 3 * bs:
+                        lens[sq] = 0  # the sequence starts over: its blocks are reopened
+                    rows.append(blocks[sq][lens[sq] // bs] * bs + lens[sq] % bs)
+                    lens[sq] += 1
+                if rng.random() < 0.2:
+                    rows.append(-1)
+            sm = np.array(rows, dtype=np.int64)
+            if rng.random() < 0.3:
+                rng.shuffle(sm)
+            msgs = []
+            plans = []
+            for pl in (py, cc):
+                try:
+                    plans.append(pl.plan(sm))
+                    msgs.append(None)
+                except RuntimeError as e:
+                    msgs.append(str(e))
+            assert msgs[0] == msgs[1]
+            if msgs[0] is not None:
+                errors += 1
+                break
+            a, b = plans
+            for f in dataclasses.fields(a):
+                x, y = getattr(a, f.name), getattr(b, f.name)
+                if isinstance(x, np.ndarray):
+                    assert x.shape == y.shape and np.array_equal(x, y), (trial, step, f.name)
+                else:
+                    assert x == y, (trial, step, f.name)
+            assert (py.kref_pos, py.kref_fill, len(py.free), py.step) == (cc.kref_pos, cc.kref_fill, len(cc.free), cc.step)
+            for blk in range(12):
+                assert py.sealed.get(blk, 7) == cc.sealed.get(blk, 7)
+            evictions += len(a.evictions)
+            finalized += a.n_fin
+    assert evictions > 20 and finalized > 200  # the traffic does reach those paths
+    empty = NativeWritePlanner(16, 16, 4, 8).plan(np.zeros(0, dtype=np.int64))
+    assert empty.n_rows == 0 and empty.fin.shape == (0, 19) and empty.step == 1
