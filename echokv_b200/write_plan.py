@@ -283,8 +283,11 @@ class NativeWritePlanner:
 
     def __del__(self) -> None:
         h, self._h = getattr(self, "_h", None), None
-        if h:
-            self._N.lib.echokv_planner_destroy(h)
+        try:
+            if h:
+                self._N.lib.echokv_planner_destroy(h)
+        except Exception:  # interpreter shutdown: the library may already be gone
+            pass
 
     def _get(self, what: int) -> int:
         return int(self._N.lib.echokv_planner_get(self._h, what))
