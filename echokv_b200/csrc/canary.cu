@@ -3,8 +3,15 @@
 // where K~_b is the storage round trip of the K_ref window at b bits in the cache's exact K
 // format (per channel over consecutive groups of k_group tokens) -- echokv_vllm/canary.py:59-89,
 // echokv_vllm/quant.py:82-96.  One CTA per layer; the whole problem of a layer lives in shared
-// memory, so the estimator is one launch (the reference issues about a dozen small kernels).
+// memory, so the estimator is one launch (the reference issues about a dozen small kernels).  The KV heads of a layer
+// are independent until the final mean: a thread-block cluster of up to 8 CTAs per layer takes one head (or every
+// eighth) each, and the cluster's first CTA adds the per-CTA sums in CTA order through distributed shared memory, so
+// the result does not depend on timing.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace echokv {
 
@@ -33,7 +40,9 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 
 __global__ void __launch_bounds__(CK_THREADS) canary_kl_kernel(CanaryArgs A) {
   extern __shared__ __align__(16) float sm[];
-  const int layer = blockIdx.x;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int layer = blockIdx.y;
+  const int crank = (int)cluster.block_rank(), csize = (int)cluster.num_blocks();
   const int D = A.D, KG = A.KG;
   const int w = (A.ring_fill / KG) * KG;       // whole groups only; the newest w keys
   const int gqa = A.Hq / A.H;
@@ -44,10 +53,11 @@ __global__ void __launch_bounds__(CK_THREADS) canary_kl_kernel(CanaryArgs A) {
   float* lr = qs + CK_ROWS * D;      // [CK_ROWS][w] reference log-weights
   float* lq = lr + CK_ROWS * w;      // [CK_ROWS][w] quantized log-weights
   __shared__ float red[CK_THREADS / 32];
+  __shared__ float cta_total[3];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float total[3] = {0.f, 0.f, 0.f};
 
-  for (int h = 0; h < A.H; ++h) {
+  for (int h = crank; h < A.H; h += csize) {
     __syncthreads();
     for (int i = threadIdx.x; i < w * D; i += CK_THREADS) {
       const int t = i / D, d = i % D;
@@ -124,9 +134,18 @@ __global__ void __launch_bounds__(CK_THREADS) canary_kl_kernel(CanaryArgs A) {
     }
   }
   if (threadIdx.x == 0) {
-    const float inv = 1.f / (float)(A.Hq * A.nq);
-    for (int b = 0; b < 3; ++b) A.out[layer * 3 + b] = fmaxf(total[b] * inv, 0.f);
+    for (int b = 0; b < 3; ++b) cta_total[b] = total[b];
   }
+  cluster.sync();  // every CTA's sums are in its shared memory
+  if (crank == 0 && threadIdx.x == 0) {
+    const float inv = 1.f / (float)(A.Hq * A.nq);
+    for (int b = 0; b < 3; ++b) {
+      float t = 0.f;
+      for (int r = 0; r < csize; ++r) t += cluster.map_shared_rank(cta_total, r)[b];  // in CTA order = head order
+      A.out[layer * 3 + b] = fmaxf(t * inv, 0.f);
+    }
+  }
+  cluster.sync();  // no CTA leaves (and gives up its shared memory) before the first one has read it
 }
 
 }  // namespace echokv
@@ -148,11 +167,9 @@ extern "C" int echokv_canary_kl(const void* query, int32_t q_dtype, int64_t q_sl
   if (w == 0) return set_error(ECHOKV_E_ARGUMENT, "canary_kl: K_ref has %d keys, fewer than k_group=%d", ring_fill, k_group);
   if ((reinterpret_cast<uintptr_t>(kref) & 3) != 0) return set_error(ECHOKV_E_ARGUMENT, "canary_kl: misaligned K_ref");
   const size_t smem = (size_t)(2 * w * head_size + CK_ROWS * head_size + 2 * CK_ROWS * w) * sizeof(float);
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
+  if (smem > 48 * 1024) {  // per call: the attribute belongs to the current device
     cudaError_t e = cudaFuncSetAttribute(canary_kl_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return set_error(ECHOKV_E_UNSUPPORTED, "canary_kl: window %d x head %d needs %zu bytes of shared memory", w, head_size, smem);
-    configured = smem;
   }
   CanaryArgs A;
   A.q = query; A.q_dt = q_dtype; A.q_sl = q_sl; A.q_sq = q_sq; A.q_sh = q_sh;
@@ -160,6 +177,19 @@ extern "C" int echokv_canary_kl(const void* query, int32_t q_dtype, int64_t q_sl
   A.ring_pos = ring_pos; A.ring_fill = ring_fill; A.window = window;
   A.nq = nq; A.Hq = num_q_heads; A.H = num_kv_heads; A.D = head_size; A.KG = k_group;
   A.scale = softmax_scale; A.out = out;
-  canary_kl_kernel<<<num_layers, CK_THREADS, smem, (cudaStream_t)stream>>>(A);
+  const int csize = num_kv_heads < 8 ? num_kv_heads : 8;  // 8 = the portable cluster size
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)csize, (unsigned)num_layers);
+  cfg.blockDim = dim3(CK_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)csize;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, canary_kl_kernel, A) != cudaSuccess) return check_launch("canary_kl");
   return check_launch("canary_kl");
 }
